@@ -1,0 +1,183 @@
+/*
+ * pope_b200.h -- C ABI of libpope_b200.so: PoPE (polar positional embedding) attention
+ * kernels for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a binding of the reference project (lucidrains/PoPE-pytorch) loads
+ * in place of its two Triton modules.  Plain C: raw device pointers, sizes and element
+ * strides; no C++ or framework types; no exceptions cross it.
+ *
+ * Conventions shared by every entry point
+ *   - All tensor pointers are DEVICE pointers on the current CUDA device.  The caller owns
+ *     and allocates every input, output and workspace; the library never allocates or frees
+ *     device memory and never synchronises the device.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Tensors are addressed as base + b*stride.b + h*stride.h + n*stride.n + feature, strides
+ *     in ELEMENTS, innermost (feature / key) dimension contiguous.  Both the (b,h,n,d) and
+ *     the (b,n,h,d) layouts of the reference are therefore zero-copy views.
+ *   - `freqs` is an opaque fp32 table of phases, addressed as
+ *     freqs[b*sf.b + h*sf.h + pos*sf.n + c], c < r; a stride of 0 broadcasts that axis
+ *     (the encoding of PoPE_pytorch/triton_pope_flash_attn.py:237-245).  It has Nk rows;
+ *     query i uses row (Nk - Nq + i)  (PoPE_pytorch/pope.py:64).
+ *   - `bias` is fp32 (Hk, r): the per-key-head phase added to the key side only
+ *     (PoPE_pytorch/pope.py:56).  Query head h reads key/value/bias head h % Hk
+ *     (PoPE_pytorch/attention.py:44-45,118-120).
+ *   - Return value: POPE_OK or a negative PopeStatus.  Nothing is launched on error.
+ *   - Thread-safe and re-entrant; calls on different streams may overlap, except where an
+ *     entry point documents shared state.
+ */
+#ifndef POPE_B200_H_
+#define POPE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define POPE_B200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define POPE_API __attribute__((visibility("default")))
+#else
+#define POPE_API
+#endif
+
+typedef enum PopeStatus {
+  POPE_OK = 0,
+  POPE_ERR_BAD_ARG = -1,      /* null pointer, non-positive size, Nq > Nk, r > d, H % Hk != 0 ... */
+  POPE_ERR_UNSUPPORTED = -2,  /* shape / dtype outside what the kernels implement             */
+  POPE_ERR_MISALIGNED = -3,   /* a pointer or stride breaks the documented alignment          */
+  POPE_ERR_WORKSPACE = -4,    /* workspace missing or smaller than pope_b200_workspace_bytes   */
+  POPE_ERR_CUDA = -5,         /* a CUDA runtime call failed (launch, attribute, symbol lookup) */
+  POPE_ERR_ARCH = -6          /* the current device is not compute capability 10.x            */
+} PopeStatus;
+
+typedef enum PopeDtype { POPE_F32 = 0, POPE_BF16 = 1, POPE_F16 = 2 } PopeDtype;
+
+typedef enum PopeOp {
+  POPE_OP_SIM_FWD = 0, POPE_OP_SIM_BWD = 1, POPE_OP_ATTN_FWD = 2, POPE_OP_ATTN_BWD = 3
+} PopeOp;
+
+/* Element strides of the batch, head and row axes (innermost axis is contiguous). */
+typedef struct PopeStride3 { int64_t b, h, n; } PopeStride3;
+
+/* Problem geometry common to all operators. */
+typedef struct PopeShape {
+  int32_t B;   /* batch                                   */
+  int32_t H;   /* query heads                             */
+  int32_t Hk;  /* key/value heads, H % Hk == 0            */
+  int32_t Nq;  /* query rows, Nq <= Nk                    */
+  int32_t Nk;  /* key rows = rows of freqs                */
+  int32_t d;   /* head dim                                */
+  int32_t r;   /* rotated dims, 0 <= r <= d               */
+  int32_t dtype; /* PopeDtype of q, k, v and their grads  */
+} PopeShape;
+
+/* The (freqs, bias) pair every operator takes -- PolarEmbedReturn, PoPE_pytorch/pope.py:18. */
+typedef struct PopeEmbed {
+  const float* freqs; PopeStride3 sf;      /* ignored when r == 0 */
+  const float* bias;  int64_t bias_stride_h;
+} PopeEmbed;
+
+/* ---- similarity: sim[b,h,i,j] = <q'_i, k'_j> --------------------------------------------
+ * Replaces PoPESimilarityFunction.forward / _fwd_kernel, PoPE_pytorch/triton_pope.py:28-83,
+ * 260-288.  `sim` has the dtype of q (triton_pope.py:273); ss = strides of (b, h, row). */
+typedef struct PopeSimArgs {
+  uint32_t struct_bytes;     /* sizeof(PopeSimArgs), checked */
+  int32_t allow_tf32;        /* accepted; the kernels always meet the fp32 tolerance */
+  PopeShape shape;
+  PopeEmbed embed;
+  const void* q; PopeStride3 sq;
+  const void* k; PopeStride3 sk;
+  void* sim;     PopeStride3 ss;
+} PopeSimArgs;
+
+/* Replaces PoPESimilarityFunction.backward, PoPE_pytorch/triton_pope.py:290-362.
+ * dq/dk are written (dtype of q).  dfreqs / dbias are optional fp32 ACCUMULATORS the caller
+ * zero-fills: dfreqs uses the stride encoding of freqs (0 = summed over that axis),
+ * dbias is (Hk, r) contiguous rows with stride dbias_stride_h. */
+typedef struct PopeSimBwdArgs {
+  uint32_t struct_bytes;
+  int32_t allow_tf32;
+  PopeShape shape;
+  PopeEmbed embed;
+  const void* q; PopeStride3 sq;
+  const void* k; PopeStride3 sk;
+  const void* dsim; PopeStride3 sds;
+  void* dq; PopeStride3 sdq;
+  void* dk; PopeStride3 sdk;
+  float* dfreqs; PopeStride3 sdf;   /* may be NULL */
+  float* dbias; int64_t dbias_stride_h; /* may be NULL */
+} PopeSimBwdArgs;
+
+/* ---- attention ----------------------------------------------------------------------------
+ * Replaces flash_attn_forward / _fwd_kernel, PoPE_pytorch/triton_pope_flash_attn.py:23-117,
+ * 222-271.  out has q's dtype; lse is fp32 (B, H, Nq) contiguous.  mask is an optional
+ * uint8/bool key-padding mask, nonzero = keep, addressed mask[b*mask_stride_b + j*mask_stride_n]
+ * (PoPE_pytorch/attention.py:129-131).  The causal mask is top-left aligned (key j visible to
+ * query i iff j <= i); a row with no visible key gives out = 0 and lse = -inf.
+ * Small Nq against a long key range (decode) is split over the keys internally; that path
+ * and the table-driven tensor-core path need `workspace` (size from
+ * pope_b200_workspace_bytes(POPE_OP_ATTN_FWD, &args); may be NULL when that returns 0). */
+typedef struct PopeAttnArgs {
+  uint32_t struct_bytes;
+  int32_t causal;
+  float softmax_scale;
+  int32_t reserved0;
+  PopeShape shape;
+  PopeEmbed embed;
+  const void* q; PopeStride3 sq;
+  const void* k; PopeStride3 sk;
+  const void* v; PopeStride3 sv;
+  void* out;     PopeStride3 so;
+  float* lse;
+  const uint8_t* mask; int64_t mask_stride_b, mask_stride_n;
+  void* workspace; size_t workspace_bytes;
+} PopeAttnArgs;
+
+/* Replaces flash_attn_backward / _bwd_preprocess / _bwd_kernel,
+ * PoPE_pytorch/triton_pope_flash_attn.py:119-218, 273-335.  dq, dk, dv are written (q's dtype).
+ * dfreqs / dbias as in PopeSimBwdArgs (caller zero-fills; NULL = not wanted). */
+typedef struct PopeAttnBwdArgs {
+  uint32_t struct_bytes;
+  int32_t causal;
+  float softmax_scale;
+  int32_t reserved0;
+  PopeShape shape;
+  PopeEmbed embed;
+  const void* q; PopeStride3 sq;
+  const void* k; PopeStride3 sk;
+  const void* v; PopeStride3 sv;
+  const void* out; PopeStride3 so;
+  const void* dout; PopeStride3 sdo;
+  const float* lse;
+  const uint8_t* mask; int64_t mask_stride_b, mask_stride_n;
+  void* dq; PopeStride3 sdq;
+  void* dk; PopeStride3 sdk;
+  void* dv; PopeStride3 sdv;
+  float* dfreqs; PopeStride3 sdf;
+  float* dbias; int64_t dbias_stride_h;
+  void* workspace; size_t workspace_bytes;
+} PopeAttnBwdArgs;
+
+POPE_API int pope_b200_abi_version(void);
+POPE_API const char* pope_b200_status_str(int status);
+
+/* Name of the kernel family the last successful call ON THIS THREAD dispatched to
+ * ("simt", "tcgen05", ...).  Diagnostic only. */
+POPE_API const char* pope_b200_last_path(void);
+
+/* Bytes of workspace the operator needs for these arguments (`args` points at the matching
+ * Pope*Args struct; pointers inside it are not dereferenced).  0 = none. */
+POPE_API size_t pope_b200_workspace_bytes(int op, const void* args);
+
+POPE_API int pope_b200_sim_fwd(const PopeSimArgs* args, void* stream);
+POPE_API int pope_b200_sim_bwd(const PopeSimBwdArgs* args, void* stream);
+POPE_API int pope_b200_attn_fwd(const PopeAttnArgs* args, void* stream);
+POPE_API int pope_b200_attn_bwd(const PopeAttnBwdArgs* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POPE_B200_H_ */

@@ -1,0 +1,344 @@
+"""ctypes binding of libpope_b200.so (the C ABI in include/pope_b200.h) and the autograd
+functions built on it.
+
+This is the seam where the reference re-points its two Triton imports
+(PoPE_pytorch/attention.py:21-26): ``similarity`` stands in for
+``triton_compute_qk_similarity`` (PoPE_pytorch/triton_pope.py:364-372) and ``flash_attn`` for
+``flash_attn`` (PoPE_pytorch/triton_pope_flash_attn.py:364-373).  PyTorch is used for device
+memory, streams and autograd bookkeeping only; all arithmetic happens in the library.
+There is no fallback: if the library cannot be loaded every call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libpope_b200.so")
+
+OP_SIM_FWD, OP_SIM_BWD, OP_ATTN_FWD, OP_ATTN_BWD = 0, 1, 2, 3
+_DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+class Stride3(C.Structure):
+    _fields_ = [("b", C.c_int64), ("h", C.c_int64), ("n", C.c_int64)]
+
+
+class Shape(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("B", "H", "Hk", "Nq", "Nk", "d", "r", "dtype")]
+
+
+class Embed(C.Structure):
+    _fields_ = [("freqs", C.c_void_p), ("sf", Stride3), ("bias", C.c_void_p), ("bias_stride_h", C.c_int64)]
+
+
+class SimArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("allow_tf32", C.c_int32), ("shape", Shape), ("embed", Embed),
+                ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
+                ("sim", C.c_void_p), ("ss", Stride3)]
+
+
+class SimBwdArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("allow_tf32", C.c_int32), ("shape", Shape), ("embed", Embed),
+                ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
+                ("dsim", C.c_void_p), ("sds", Stride3), ("dq", C.c_void_p), ("sdq", Stride3),
+                ("dk", C.c_void_p), ("sdk", Stride3), ("dfreqs", C.c_void_p), ("sdf", Stride3),
+                ("dbias", C.c_void_p), ("dbias_stride_h", C.c_int64)]
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("causal", C.c_int32), ("softmax_scale", C.c_float),
+                ("reserved0", C.c_int32), ("shape", Shape), ("embed", Embed),
+                ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
+                ("v", C.c_void_p), ("sv", Stride3), ("out", C.c_void_p), ("so", Stride3),
+                ("lse", C.c_void_p), ("mask", C.c_void_p), ("mask_stride_b", C.c_int64),
+                ("mask_stride_n", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class AttnBwdArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("causal", C.c_int32), ("softmax_scale", C.c_float),
+                ("reserved0", C.c_int32), ("shape", Shape), ("embed", Embed),
+                ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
+                ("v", C.c_void_p), ("sv", Stride3), ("out", C.c_void_p), ("so", Stride3),
+                ("dout", C.c_void_p), ("sdo", Stride3), ("lse", C.c_void_p),
+                ("mask", C.c_void_p), ("mask_stride_b", C.c_int64), ("mask_stride_n", C.c_int64),
+                ("dq", C.c_void_p), ("sdq", Stride3), ("dk", C.c_void_p), ("sdk", Stride3),
+                ("dv", C.c_void_p), ("sdv", Stride3), ("dfreqs", C.c_void_p), ("sdf", Stride3),
+                ("dbias", C.c_void_p), ("dbias_stride_h", C.c_int64),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+EXPORTS = ("pope_b200_abi_version", "pope_b200_status_str", "pope_b200_last_path", "pope_b200_workspace_bytes",
+           "pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd")
+
+_lib = None
+_load_error: Optional[str] = None
+
+
+def load_library():
+    """dlopen the in-tree library once; raises RuntimeError when it is missing or stale."""
+    global _lib, _load_error
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        _load_error = f"{LIB_PATH} is missing: build it with `python -m pope_pytorch_b200.build`"
+        raise RuntimeError(_load_error)
+    lib = C.CDLL(LIB_PATH)
+    lib.pope_b200_abi_version.restype = C.c_int
+    lib.pope_b200_status_str.restype = C.c_char_p
+    lib.pope_b200_status_str.argtypes = [C.c_int]
+    lib.pope_b200_last_path.restype = C.c_char_p
+    lib.pope_b200_workspace_bytes.restype = C.c_size_t
+    lib.pope_b200_workspace_bytes.argtypes = [C.c_int, C.c_void_p]
+    for name in ("pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd"):
+        fn = getattr(lib, name)
+        fn.restype = C.c_int
+        fn.argtypes = [C.c_void_p, C.c_void_p]
+    if lib.pope_b200_abi_version() != 1:
+        raise RuntimeError("libpope_b200.so has an unexpected ABI version; rebuild it")
+    _lib = lib
+    return lib
+
+
+def is_available() -> bool:
+    try:
+        load_library()
+        return True
+    except (RuntimeError, OSError):
+        return False
+
+
+def last_path() -> str:
+    return load_library().pope_b200_last_path().decode()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load_library().pope_b200_status_str(rc).decode()
+        raise RuntimeError(f"{what} failed: {msg} (status {rc})")
+
+
+def _stream_ptr(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _s3(t: torch.Tensor) -> Stride3:
+    """Strides of a head-first (b, h, n, x) view; the innermost stride must be 1."""
+    return Stride3(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _inner_contig(t: torch.Tensor) -> torch.Tensor:
+    return t if t.shape[-1] <= 1 or t.stride(-1) == 1 else t.contiguous()
+
+
+def _freq_strides(freqs: torch.Tensor) -> Stride3:
+    """(batch, head, row) strides with 0 = broadcast.  A 4-D table is (b, h, n, r), the layout
+    apply_pope_to_qk and the similarity kernel of the reference use
+    (PoPE_pytorch/pope.py:53-56, triton_pope.py:267-272)."""
+    if freqs.ndim == 2:
+        return Stride3(0, 0, freqs.stride(0))
+    if freqs.ndim == 3:
+        return Stride3(freqs.stride(0) if freqs.shape[0] > 1 else 0, 0, freqs.stride(1))
+    if freqs.ndim == 4:
+        return Stride3(freqs.stride(0) if freqs.shape[0] > 1 else 0,
+                       freqs.stride(1) if freqs.shape[1] > 1 else 0, freqs.stride(2))
+    raise ValueError("freqs must have 2, 3 or 4 dimensions")
+
+
+def _prep_embed(freqs: torch.Tensor, bias: torch.Tensor, nk: int, r: int):
+    freqs = _inner_contig(freqs.float()) if freqs.dtype != torch.float32 else _inner_contig(freqs)
+    bias = _inner_contig(bias.float()) if bias.dtype != torch.float32 else _inner_contig(bias)
+    assert freqs.shape[-2] == nk or r == 0, "freqs must have one row per key position"
+    return freqs, bias
+
+
+def _embed_struct(freqs, bias, r) -> Embed:
+    if r == 0:
+        return Embed(None, Stride3(0, 0, 0), None, 0)
+    return Embed(freqs.data_ptr(), _freq_strides(freqs), bias.data_ptr(), bias.stride(0))
+
+
+def _shape(q, k, r) -> Shape:
+    b, h, nq, d = q.shape
+    hk, nk = k.shape[1], k.shape[2]
+    return Shape(b, h, hk, nq, nk, d, r, _DTYPES[q.dtype])
+
+
+def _workspace(op: int, args, device) -> Optional[torch.Tensor]:
+    need = load_library().pope_b200_workspace_bytes(op, C.addressof(args))
+    if need == 0:
+        return None
+    ws = torch.empty(need, dtype=torch.uint8, device=device)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), need
+    return ws
+
+
+def _validate(q, k, freqs, bias):
+    if not (q.is_cuda and k.is_cuda):
+        raise RuntimeError("the native PoPE kernels need CUDA tensors")
+    if q.dtype not in _DTYPES or k.dtype != q.dtype:
+        raise TypeError(f"q and k must share a dtype among fp32/bf16/fp16, got {q.dtype}, {k.dtype}")
+    assert q.shape[1] % k.shape[1] == 0, "query heads must be a multiple of key heads"
+    assert q.shape[2] <= k.shape[2] and freqs.shape[-1] <= q.shape[-1]
+
+
+# ----------------------------------------------------------------------------------------------
+# similarity
+# ----------------------------------------------------------------------------------------------
+
+def sim_forward(q, k, freqs, bias, allow_tf32=True) -> torch.Tensor:
+    """q (b,h,nq,d), k (b,hk,nk,d) head-first views -> sim (b,h,nq,nk) in q's dtype."""
+    lib = load_library()
+    r = freqs.shape[-1]
+    _validate(q, k, freqs, bias)
+    q, k = _inner_contig(q), _inner_contig(k)
+    freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
+    sim = torch.empty(q.shape[0], q.shape[1], q.shape[2], k.shape[2], dtype=q.dtype, device=q.device)
+    a = SimArgs(C.sizeof(SimArgs), int(allow_tf32), _shape(q, k, r), _embed_struct(freqs, bias, r),
+                q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), sim.data_ptr(), _s3(sim))
+    with torch.cuda.device(q.device):
+        _check(lib.pope_b200_sim_fwd(C.addressof(a), _stream_ptr(q)), "pope_b200_sim_fwd")
+    return sim
+
+
+def sim_backward(dsim, q, k, freqs, bias, need_dfreqs, need_dbias, allow_tf32=True):
+    lib = load_library()
+    r = freqs.shape[-1]
+    q, k, dsim = _inner_contig(q), _inner_contig(k), _inner_contig(dsim)
+    freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
+    dq, dk = torch.empty_like(q), torch.empty_like(k)
+    dfreqs = torch.zeros(freqs.shape, dtype=torch.float32, device=q.device) if (need_dfreqs and r > 0) else None
+    dbias = torch.zeros(bias.shape, dtype=torch.float32, device=q.device) if (need_dbias and r > 0) else None
+    a = SimBwdArgs(C.sizeof(SimBwdArgs), int(allow_tf32), _shape(q, k, r), _embed_struct(freqs, bias, r),
+                   q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), dsim.data_ptr(), _s3(dsim),
+                   dq.data_ptr(), _s3(dq), dk.data_ptr(), _s3(dk),
+                   dfreqs.data_ptr() if dfreqs is not None else None,
+                   _freq_strides(dfreqs) if dfreqs is not None else Stride3(0, 0, 0),
+                   dbias.data_ptr() if dbias is not None else None,
+                   dbias.stride(0) if dbias is not None else 0)
+    with torch.cuda.device(q.device):
+        _check(lib.pope_b200_sim_bwd(C.addressof(a), _stream_ptr(q)), "pope_b200_sim_bwd")
+    if need_dfreqs and dfreqs is None:
+        dfreqs = torch.zeros_like(freqs)
+    if need_dbias and dbias is None:
+        dbias = torch.zeros_like(bias)
+    return dq, dk, dfreqs, dbias
+
+
+class _Similarity(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, freqs, bias, allow_tf32):
+        ctx.save_for_backward(q, k, freqs, bias)
+        ctx.allow_tf32 = allow_tf32
+        return sim_forward(q, k, freqs, bias, allow_tf32)
+
+    @staticmethod
+    def backward(ctx, dsim):
+        q, k, freqs, bias = ctx.saved_tensors
+        dq, dk, dfreqs, dbias = sim_backward(dsim.to(q.dtype), q, k, freqs, bias,
+                                             ctx.needs_input_grad[2], ctx.needs_input_grad[3], ctx.allow_tf32)
+        if dfreqs is not None:
+            dfreqs = dfreqs.to(freqs.dtype)
+        if dbias is not None:
+            dbias = dbias.to(bias.dtype)
+        return dq, dk, dfreqs, dbias, None
+
+
+def similarity(q, k, freqs, bias, allow_tf32=True):
+    """Differentiable fused similarity on head-first tensors."""
+    return _Similarity.apply(q, k, freqs, bias, allow_tf32)
+
+
+# ----------------------------------------------------------------------------------------------
+# attention
+# ----------------------------------------------------------------------------------------------
+
+def _mask_u8(mask: Optional[torch.Tensor]):
+    if mask is None:
+        return None
+    m = mask if mask.dtype in (torch.bool, torch.uint8) else (mask != 0)
+    return m.view(torch.uint8) if m.dtype == torch.bool else m
+
+
+def attn_forward(q, k, v, freqs, bias, mask, causal, scale):
+    """Head-first VIEWS (b,h,n,d) of any stride with contiguous features -> (out, lse)."""
+    lib = load_library()
+    r = freqs.shape[-1]
+    _validate(q, k, freqs, bias)
+    q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
+    freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
+    # the output takes the memory layout of q, so a (b,n,h,d) caller gets a (b,n,h,d)-contiguous result
+    out = torch.empty_strided(q.shape, q.stride(), dtype=q.dtype, device=q.device) \
+        if q.is_non_overlapping_and_dense() else torch.empty_like(q)
+    lse = torch.empty(q.shape[0], q.shape[1], q.shape[2], dtype=torch.float32, device=q.device)
+    m8 = _mask_u8(mask)
+    a = AttnArgs(C.sizeof(AttnArgs), int(causal), float(scale), 0, _shape(q, k, r), _embed_struct(freqs, bias, r),
+                 q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), v.data_ptr(), _s3(v), out.data_ptr(), _s3(out),
+                 lse.data_ptr(), m8.data_ptr() if m8 is not None else None,
+                 m8.stride(0) if m8 is not None else 0, m8.stride(1) if m8 is not None else 0, None, 0)
+    ws = _workspace(OP_ATTN_FWD, a, q.device)
+    with torch.cuda.device(q.device):
+        _check(lib.pope_b200_attn_fwd(C.addressof(a), _stream_ptr(q)), "pope_b200_attn_fwd")
+    del ws
+    return out, lse
+
+
+def attn_backward(dout, q, k, v, out, lse, freqs, bias, mask, causal, scale, need_dfreqs, need_dbias):
+    lib = load_library()
+    r = freqs.shape[-1]
+    q, k, v, out, dout = (_inner_contig(t) for t in (q, k, v, out, dout))
+    freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dfreqs = torch.zeros(freqs.shape, dtype=torch.float32, device=q.device) if (need_dfreqs and r > 0) else None
+    dbias = torch.zeros(bias.shape, dtype=torch.float32, device=q.device) if (need_dbias and r > 0) else None
+    m8 = _mask_u8(mask)
+    a = AttnBwdArgs(C.sizeof(AttnBwdArgs), int(causal), float(scale), 0, _shape(q, k, r),
+                    _embed_struct(freqs, bias, r),
+                    q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), v.data_ptr(), _s3(v), out.data_ptr(), _s3(out),
+                    dout.data_ptr(), _s3(dout), lse.data_ptr(),
+                    m8.data_ptr() if m8 is not None else None,
+                    m8.stride(0) if m8 is not None else 0, m8.stride(1) if m8 is not None else 0,
+                    dq.data_ptr(), _s3(dq), dk.data_ptr(), _s3(dk), dv.data_ptr(), _s3(dv),
+                    dfreqs.data_ptr() if dfreqs is not None else None,
+                    _freq_strides(dfreqs) if dfreqs is not None else Stride3(0, 0, 0),
+                    dbias.data_ptr() if dbias is not None else None,
+                    dbias.stride(0) if dbias is not None else 0, None, 0)
+    ws = _workspace(OP_ATTN_BWD, a, q.device)
+    with torch.cuda.device(q.device):
+        _check(lib.pope_b200_attn_bwd(C.addressof(a), _stream_ptr(q)), "pope_b200_attn_bwd")
+    del ws
+    if need_dfreqs and dfreqs is None:
+        dfreqs = torch.zeros_like(freqs)
+    if need_dbias and dbias is None:
+        dbias = torch.zeros_like(bias)
+    return dq, dk, dv, dfreqs, dbias
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, freqs, bias, mask, causal, scale):
+        out, lse = attn_forward(q, k, v, freqs, bias, mask, causal, scale)
+        ctx.save_for_backward(q, k, v, freqs, bias, out, lse)
+        ctx.mask, ctx.causal, ctx.scale = mask, causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, freqs, bias, out, lse = ctx.saved_tensors
+        dq, dk, dv, dfreqs, dbias = attn_backward(dout.to(q.dtype), q, k, v, out, lse, freqs, bias, ctx.mask,
+                                                  ctx.causal, ctx.scale,
+                                                  ctx.needs_input_grad[3], ctx.needs_input_grad[4])
+        if dfreqs is not None:
+            dfreqs = dfreqs.to(freqs.dtype)
+        if dbias is not None:
+            dbias = dbias.to(bias.dtype)
+        return dq, dk, dv, dfreqs, dbias, None, None, None
+
+
+def flash_attn(q, k, v, freqs, bias, mask=None, causal=False, softmax_scale=None):
+    """Differentiable fused PoPE attention on head-first (b,h,n,d) views."""
+    scale = q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
+    return _FlashAttn.apply(q, k, v, freqs, bias, mask, causal, scale)

@@ -1,0 +1,129 @@
+// extern "C" boundary of libpope_b200.so: argument validation and dispatch.
+// Declarations and the contract of each entry point live in include/pope_b200.h.
+#include <mutex>
+
+#include "kernels.h"
+
+namespace {
+
+thread_local const char* g_last_path = "none";
+
+int check_device() {
+  // one lookup per host thread and device: the kernels are sm_100a only
+  static thread_local int cached_dev = -1, cached_ok = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return POPE_ERR_CUDA;
+  if (dev != cached_dev) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return POPE_ERR_CUDA;
+    cached_dev = dev, cached_ok = (major == 10);
+  }
+  return cached_ok ? POPE_OK : POPE_ERR_ARCH;
+}
+
+int check_shape(const PopeShape& s) {
+  if (s.B <= 0 || s.H <= 0 || s.Hk <= 0 || s.Nq <= 0 || s.Nk <= 0 || s.d <= 0 || s.r < 0) return POPE_ERR_BAD_ARG;
+  if (s.H % s.Hk != 0 || s.Nq > s.Nk || s.r > s.d) return POPE_ERR_BAD_ARG;
+  if (s.dtype != POPE_F32 && s.dtype != POPE_BF16 && s.dtype != POPE_F16) return POPE_ERR_BAD_ARG;
+  if ((int64_t)s.B * s.H > 65535) return POPE_ERR_UNSUPPORTED;
+  return POPE_OK;
+}
+
+int check_embed(const PopeShape& s, const PopeEmbed& e) {
+  if (s.r > 0 && (!e.freqs || !e.bias)) return POPE_ERR_BAD_ARG;
+  return POPE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pope_b200_abi_version(void) { return POPE_B200_ABI_VERSION; }
+
+const char* pope_b200_status_str(int status) {
+  switch (status) {
+    case POPE_OK: return "ok";
+    case POPE_ERR_BAD_ARG: return "bad argument (null pointer, size, Nq > Nk, r > d, H % Hk != 0, struct size)";
+    case POPE_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case POPE_ERR_MISALIGNED: return "misaligned pointer or stride";
+    case POPE_ERR_WORKSPACE: return "workspace missing or too small";
+    case POPE_ERR_CUDA: return "CUDA runtime error";
+    case POPE_ERR_ARCH: return "device is not compute capability 10.x (B200)";
+    default: return "unknown status";
+  }
+}
+
+const char* pope_b200_last_path(void) { return g_last_path; }
+
+size_t pope_b200_workspace_bytes(int op, const void* args) {
+  if (!args) return 0;
+  switch (op) {
+    case POPE_OP_ATTN_FWD: {
+      const PopeAttnArgs& a = *static_cast<const PopeAttnArgs*>(args);
+      if (a.struct_bytes != sizeof(PopeAttnArgs) || check_shape(a.shape) != POPE_OK) return 0;
+      return pope::attn_fwd_simt_workspace(a);
+    }
+    case POPE_OP_ATTN_BWD: {
+      const PopeAttnBwdArgs& a = *static_cast<const PopeAttnBwdArgs*>(args);
+      if (a.struct_bytes != sizeof(PopeAttnBwdArgs) || check_shape(a.shape) != POPE_OK) return 0;
+      return pope::attn_bwd_simt_workspace(a);
+    }
+    default: return 0;
+  }
+}
+
+int pope_b200_sim_fwd(const PopeSimArgs* a, void* stream) {
+  if (!a || a->struct_bytes != sizeof(PopeSimArgs)) return POPE_ERR_BAD_ARG;
+  int rc = check_shape(a->shape);
+  if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
+  if (rc != POPE_OK) return rc;
+  if (!a->q || !a->k || !a->sim) return POPE_ERR_BAD_ARG;
+  if ((rc = check_device()) != POPE_OK) return rc;
+  if (pope::sim_fwd_simt(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = "simt";
+  return POPE_OK;
+}
+
+int pope_b200_sim_bwd(const PopeSimBwdArgs* a, void* stream) {
+  if (!a || a->struct_bytes != sizeof(PopeSimBwdArgs)) return POPE_ERR_BAD_ARG;
+  int rc = check_shape(a->shape);
+  if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
+  if (rc != POPE_OK) return rc;
+  if (!a->q || !a->k || !a->dsim || !a->dq || !a->dk) return POPE_ERR_BAD_ARG;
+  if ((rc = check_device()) != POPE_OK) return rc;
+  if (pope::sim_bwd_simt(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = "simt";
+  return POPE_OK;
+}
+
+int pope_b200_attn_fwd(const PopeAttnArgs* a, void* stream) {
+  if (!a || a->struct_bytes != sizeof(PopeAttnArgs)) return POPE_ERR_BAD_ARG;
+  int rc = check_shape(a->shape);
+  if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
+  if (rc != POPE_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->out || !a->lse) return POPE_ERR_BAD_ARG;
+  if (a->shape.d > 256) return POPE_ERR_UNSUPPORTED;
+  const size_t need = pope::attn_fwd_simt_workspace(*a);
+  if (need > 0 && (!a->workspace || a->workspace_bytes < need)) return POPE_ERR_WORKSPACE;
+  if ((rc = check_device()) != POPE_OK) return rc;
+  if (pope::attn_fwd_simt(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = "simt";
+  return POPE_OK;
+}
+
+int pope_b200_attn_bwd(const PopeAttnBwdArgs* a, void* stream) {
+  if (!a || a->struct_bytes != sizeof(PopeAttnBwdArgs)) return POPE_ERR_BAD_ARG;
+  int rc = check_shape(a->shape);
+  if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
+  if (rc != POPE_OK) return rc;
+  if (!a->q || !a->k || !a->v || !a->out || !a->dout || !a->lse || !a->dq || !a->dk || !a->dv) return POPE_ERR_BAD_ARG;
+  if (a->shape.d > 256) return POPE_ERR_UNSUPPORTED;
+  const size_t need = pope::attn_bwd_simt_workspace(*a);
+  if (!a->workspace || a->workspace_bytes < need) return POPE_ERR_WORKSPACE;
+  if ((rc = check_device()) != POPE_OK) return rc;
+  if (pope::attn_bwd_simt(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = "simt";
+  return POPE_OK;
+}
+
+}  // extern "C"

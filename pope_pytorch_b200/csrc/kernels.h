@@ -1,0 +1,24 @@
+// Internal launch entry points shared by the C-ABI dispatcher.  Not part of the public ABI.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "../../include/pope_b200.h"
+
+namespace pope {
+
+// exact-arithmetic (fp32 FMA) family: any shape / stride / dtype
+cudaError_t sim_fwd_simt(const PopeSimArgs& a, cudaStream_t st);
+cudaError_t sim_bwd_simt(const PopeSimBwdArgs& a, cudaStream_t st);
+size_t attn_fwd_simt_workspace(const PopeAttnArgs& a);
+cudaError_t attn_fwd_simt(const PopeAttnArgs& a, cudaStream_t st);
+size_t attn_bwd_simt_workspace(const PopeAttnBwdArgs& a);
+cudaError_t attn_bwd_simt(const PopeAttnBwdArgs& a, cudaStream_t st);
+
+// delta[b,h,i] = sum_c out[i,c] * dout[i,c]  (fp32, (B,H,Nq) contiguous); used by every backward
+cudaError_t attn_bwd_delta(const PopeAttnBwdArgs& a, float* delta, cudaStream_t st);
+
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+// 32-wide feature chunks the fp32 attention kernels are instantiated for (d <= 256)
+inline int simt_dch(int d) { int c = (d + 31) / 32; return c <= 4 ? c : 8; }
+
+}  // namespace pope

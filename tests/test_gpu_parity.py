@@ -1,0 +1,294 @@
+"""GPU parity: the CUDA kernels (through the C ABI) against the CPU oracle and the reference's
+golden vectors, on identical seeded inputs.
+
+Tolerances (written where used): fp32 similarity 1e-4 relative to max|sim|; fp32 attention and
+fp32 gradients rtol 1e-3 / atol 1e-4 (the reference's own bound, tests/test_triton.py:50-54);
+bf16 / fp16 attention outputs and gradients 2e-2 absolute.
+"""
+import math
+
+import pytest
+import torch
+
+from oracle import pope_oracle as O
+from pope_pytorch_b200 import AxialPoPE, PoPE, compute_attn_similarity, flash_attn_with_pope, _native
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def maxerr(a, b):
+    return float((a.detach().float().cpu() - b.detach().float().cpu()).abs().max()) if b.numel() else 0.0
+
+
+def assert_close32(a, b, what, rtol=1e-3, atol=1e-4):
+    a, b = a.detach().float().cpu(), b.detach().float().cpu()
+    assert a.shape == b.shape, what
+    bad = (a - b).abs() > atol + rtol * b.abs()
+    assert not bool(bad.any()), f"{what}: max err {maxerr(a, b)}"
+
+
+def gen(shape, g, dtype=torch.float32):
+    return torch.randn(*shape, generator=g).to(dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# similarity
+# ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("tag", ["square", "decode", "gqa", "table", "r0"])
+def test_similarity_golden_fwd_bwd(golden, tag):
+    g = golden.case(f"sim/{tag}")
+    q, k = g["q"].to(DEV).requires_grad_(True), g["k"].to(DEV).requires_grad_(True)
+    freqs, bias = g["freqs"].to(DEV).requires_grad_(True), g["bias"].to(DEV).requires_grad_(True)
+    sim = compute_attn_similarity(q, k, (freqs, bias), allow_tf32=False)
+    assert maxerr(sim, g["sim"]) <= 1e-4 * max(1.0, float(g["sim"].abs().max())) if g["sim"].numel() else True
+    sim.backward(g["dsim"].to(DEV))
+    assert_close32(q.grad, g["dq"], "dq"), assert_close32(k.grad, g["dk"], "dk")
+    if "dbias" in g and g["dbias"].numel():
+        assert_close32(bias.grad, g["dbias"], "dbias"), assert_close32(freqs.grad, g["dfreqs"], "dfreqs")
+
+
+def test_similarity_config1_fp32():
+    """PoPE(64, heads=8), q,k (1,8,1024,64) fp32, positions 0..1023: 1e-4 relative."""
+    g = torch.Generator().manual_seed(1001)
+    q, k = gen((1, 8, 1024, 64), g), gen((1, 8, 1024, 64), g)
+    emb = PoPE(64, heads=8)(1024)
+    ref = O.similarity(q, k, emb.freqs, emb.bias.detach())
+    sim = compute_attn_similarity(q.to(DEV), k.to(DEV), (emb.freqs.to(DEV), emb.bias.detach().to(DEV)))
+    assert sim.dtype == torch.float32 and sim.shape == (1, 8, 1024, 1024)
+    assert maxerr(sim, ref) <= 1e-4 * float(ref.abs().max())
+    attn_err = maxerr(sim.softmax(dim=-1), ref.softmax(dim=-1))
+    assert attn_err <= 1e-4
+
+
+@pytest.mark.parametrize("nq,nk,d,r", [(1, 31, 32, 0), (31, 33, 32, 16), (33, 129, 64, 64), (127, 127, 48, 32),
+                                       (129, 129, 128, 64), (5, 200, 256, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_similarity_edge_shapes(nq, nk, d, r, dtype):
+    g = torch.Generator().manual_seed(nq * 1000 + nk)
+    q, k = gen((2, 2, nq, d), g, dtype), gen((2, 2, nk, d), g, dtype)
+    freqs, bias = torch.rand(nk, r, generator=g) * 100.0, -torch.rand(2, r, generator=g) * 6.0
+    ref = O.similarity(q.float(), k.float(), freqs, bias)
+    sim = compute_attn_similarity(q.to(DEV), k.to(DEV), (freqs.to(DEV), bias.to(DEV)))
+    assert sim.dtype == dtype
+    tol = 1e-4 if dtype == torch.float32 else 1e-2       # bf16 output rounding: 2^-8 relative
+    assert maxerr(sim, ref) <= tol * float(ref.abs().max())
+
+
+def test_similarity_seq_first_and_non_contiguous_views():
+    g = torch.Generator().manual_seed(5)
+    qf, kf = gen((1, 256, 8, 64), g), gen((1, 256, 8, 64), g)          # (b, n, h, d)
+    emb = PoPE(32, heads=8)(256)
+    q_nc, k_nc = qf[:, :128].to(DEV), kf[:, :128].to(DEV)
+    freqs = emb.freqs[:128]
+    ref = O.similarity(qf[:, :128].transpose(1, 2), kf[:, :128].transpose(1, 2), freqs, emb.bias.detach())
+    sim = compute_attn_similarity(q_nc, k_nc, (freqs.to(DEV), emb.bias.detach().to(DEV)), head_dimension_at_first=False)
+    assert maxerr(sim, ref) <= 1e-4 * float(ref.abs().max())
+
+
+# ------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("tag", ["plain", "causal", "masked", "decode", "short_q", "gqa", "seq_first"])
+def test_attention_golden_fp32(golden, tag):
+    g = golden.case(f"attn/{tag}")
+    seq_first = tag == "seq_first"
+    q, k, v = (g[n].to(DEV) for n in ("q", "k", "v"))
+    if seq_first:   # feed genuinely (b, n, h, d)-contiguous tensors
+        q, k, v = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+    freqs, bias = g["freqs"].to(DEV).requires_grad_(True), g["bias"].to(DEV).requires_grad_(True)
+    mask = g["mask"].to(DEV) if "mask" in g else None
+    out = flash_attn_with_pope(q, k, v, pos_emb=(freqs, bias), mask=mask, causal=bool(int(g["causal"])),
+                               head_dimension_at_first=not seq_first)
+    dout = g["dout"].to(DEV)
+    out.backward(dout.transpose(1, 2) if seq_first else dout)
+    fix = (lambda t: t.transpose(1, 2)) if seq_first else (lambda t: t)
+    assert_close32(fix(out), g["out"], "out")
+    assert_close32(fix(q.grad), g["dq"], "dq"), assert_close32(fix(k.grad), g["dk"], "dk")
+    assert_close32(fix(v.grad), g["dv"], "dv")
+    assert_close32(bias.grad, g["dbias"], "dbias"), assert_close32(freqs.grad, g["dfreqs"], "dfreqs")
+
+
+def run_case(b, h, hk, nq, nk, d, r, dtype, causal, masked, seed, freqs=None, bias_scale=6.0, seq_first=False,
+             want_dfreqs=False, tol=2e-2):
+    g = torch.Generator().manual_seed(seed)
+    q, k, v = gen((b, h, nq, d), g, dtype), gen((b, hk, nk, d), g, dtype), gen((b, hk, nk, d), g, dtype)
+    dout = gen((b, h, nq, d), g, dtype)
+    if freqs is None:
+        freqs = PoPE(r, heads=hk)(nk).freqs if r > 0 else torch.empty(nk, 0)
+    bias = -torch.rand(hk, r, generator=g) * bias_scale
+    mask = None
+    if masked:
+        lens = torch.randint(nk // 2, nk + 1, (b,), generator=g)
+        mask = torch.arange(nk)[None, :] < lens[:, None]
+    ref = O.attention_with_grads(q.float(), k.float(), v.float(), freqs, bias, dout.float(), mask=mask, causal=causal,
+                                 want_dfreqs=want_dfreqs)
+    qg, kg, vg = (t.to(DEV) for t in (q, k, v))
+    if seq_first:
+        qg, kg, vg = (t.transpose(1, 2).contiguous() for t in (qg, kg, vg))
+    qg, kg, vg = (t.requires_grad_(True) for t in (qg, kg, vg))
+    fg, bg = freqs.to(DEV).requires_grad_(want_dfreqs), bias.to(DEV).requires_grad_(True)
+    out = flash_attn_with_pope(qg, kg, vg, pos_emb=(fg, bg), mask=None if mask is None else mask.to(DEV),
+                               causal=causal, head_dimension_at_first=not seq_first)
+    dg = dout.to(DEV)
+    out.backward(dg.transpose(1, 2) if seq_first else dg)
+    fix = (lambda t: t.transpose(1, 2)) if seq_first else (lambda t: t)
+    errs = dict(out=maxerr(fix(out), ref["out"]), dq=maxerr(fix(qg.grad), ref["dq"]), dk=maxerr(fix(kg.grad), ref["dk"]),
+                dv=maxerr(fix(vg.grad), ref["dv"]))
+    if r > 0:
+        errs["dbias_rel"] = maxerr(bg.grad, ref["dbias"]) / max(1.0, float(ref["dbias"].abs().max()))
+        if want_dfreqs:
+            errs["dfreqs_rel"] = maxerr(fg.grad, ref["dfreqs"]) / max(1.0, float(ref["dfreqs"].abs().max()))
+    assert out.dtype == dtype and not torch.isnan(out.float()).any()
+    for name, e in errs.items():
+        assert e <= tol, f"{name}: {e} (all: {errs})"
+    return errs
+
+
+# shapes of the reference's own fused-vs-manual test (tests/test_flash_attn.py:10-20)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("nq", [1, 256])
+@pytest.mark.parametrize("masked", [True, False])
+def test_attention_reference_grid(dtype, causal, nq, masked):
+    tol = 2e-2 if dtype != torch.float32 else 2e-4
+    run_case(2, 4, 4, nq, 256, 64, 32, dtype, causal, masked, seed=42, seq_first=True, want_dfreqs=True, tol=tol)
+
+
+@pytest.mark.parametrize("nq,nk,d,r", [(1, 33, 32, 0), (31, 31, 32, 16), (33, 129, 64, 64), (127, 127, 48, 32),
+                                       (129, 129, 128, 128), (65, 200, 96, 96), (40, 72, 256, 128)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_edge_shapes_bf16(nq, nk, d, r, causal):
+    run_case(2, 2, 2, nq, nk, d, r, torch.bfloat16, causal, masked=True, seed=nq + nk)
+
+
+def test_attention_gqa_bf16():
+    run_case(2, 8, 2, 96, 96, 64, 32, torch.bfloat16, causal=True, masked=False, seed=9)
+
+
+def test_attention_config2_causal_with_padding():
+    """(2,8,1024,64) bf16, PoPE dim 32, causal + key-padding prefix lengths in [512,1024]."""
+    run_case(2, 8, 8, 1024, 1024, 64, 32, torch.bfloat16, causal=True, masked=True, seed=1002)
+
+
+def test_attention_config4_axial_video():
+    """AxialPoPE(96, axial (32,32,32)) on an (8,16,16) grid, (2,8,2048,96) bf16, non-causal."""
+    freqs = AxialPoPE(96, heads=8, axial_dims=(32, 32, 32))((8, 16, 16)).freqs
+    run_case(2, 8, 8, 2048, 2048, 96, 96, torch.bfloat16, causal=False, masked=False, seed=1004, freqs=freqs)
+
+
+def test_attention_config3_training_shape_slices():
+    """(4,16,4096,128) bf16, PoPE dim 128, causal: full-size GPU run; out/dq/dk/dv checked on
+    sampled (b,h) units and the phase-bias gradient on sampled heads over the whole batch."""
+    B, H, N, D = 4, 16, 4096, 128
+    g = torch.Generator().manual_seed(1003)
+    q, k, v, do = (gen((B, H, N, D), g, torch.bfloat16) for _ in range(4))
+    pope = PoPE(D, heads=H)
+    with torch.no_grad():
+        pope.bias.uniform_(-2 * math.pi, 0.0, generator=g)
+    emb = pope(N)
+    qg, kg, vg = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    bias_g = emb.bias.detach().to(DEV).requires_grad_(True)
+    out = flash_attn_with_pope(qg, kg, vg, pos_emb=(emb.freqs.to(DEV), bias_g), causal=True)
+    out.backward(do.to(DEV))
+    heads = [0, 11]
+    dbias_ref = torch.zeros(len(heads), D)
+    for hi, hh in enumerate(heads):
+        for bb in range(B):
+            sl = (slice(bb, bb + 1), slice(hh, hh + 1))
+            ref = O.attention_with_grads(q[sl].float(), k[sl].float(), v[sl].float(), emb.freqs,
+                                         emb.bias.detach()[hh:hh + 1], do[sl].float(), causal=True)
+            dbias_ref[hi] += ref["dbias"][0]
+            if bb in (0, 3):
+                for name, got in (("out", out), ("dq", qg.grad), ("dk", kg.grad), ("dv", vg.grad)):
+                    e = maxerr(got[sl], ref[name])
+                    assert e <= 2e-2, f"{name} unit ({bb},{hh}): {e}"
+    got = bias_g.grad[heads].float().cpu()
+    rel = float((got - dbias_ref).abs().max() / dbias_ref.abs().max())
+    # a 16384 x 4096-term reduction of bf16-rounded products: bounded relative to its magnitude
+    assert rel <= 2e-2, f"dbias relative error {rel}, abs {float((got - dbias_ref).abs().max())}"
+
+
+def test_attention_config5_decode_and_prefill_rows():
+    """Long context, head dim 128, PoPE dim 64, N = 32768 (2 units of the 256): decode of the last
+    position (causal=False) and sampled causal prefill rows against the oracle."""
+    N, D, R = 32768, 128, 64
+    g = torch.Generator().manual_seed(1005)
+    q, k, v = (gen((1, 2, N, D), g, torch.bfloat16) for _ in range(3))
+    emb = PoPE(R, heads=2)(N)
+    freqs, bias = emb.freqs, emb.bias.detach()
+    kg, vg, fg, bg = k.to(DEV), v.to(DEV), freqs.to(DEV), bias.to(DEV)
+    # decode
+    out = flash_attn_with_pope(q[:, :, -1:].to(DEV), kg, vg, pos_emb=(fg, bg), causal=False)
+    ref = O.attention(q[:, :, -1:].float(), k.float(), v.float(), freqs, bias)
+    assert maxerr(out, ref) <= 2e-2
+    # prefill: full causal forward on the GPU, 64 sampled rows checked
+    full = flash_attn_with_pope(q.to(DEV), kg, vg, pos_emb=(fg, bg), causal=True)
+    rows = torch.randint(0, N, (64,), generator=g).tolist() + [0, N - 1]
+    qe, ke = O.apply_pope(freqs, bias, q.float(), k.float())
+    for i in rows:
+        s = torch.einsum("bhd,bhjd->bhj", qe[:, :, i], ke[:, :, : i + 1]) * D ** -0.5
+        ref_row = torch.einsum("bhj,bhjd->bhd", s.softmax(-1), v[:, :, : i + 1].float())
+        assert maxerr(full[:, :, i], ref_row) <= 2e-2, i
+
+
+# ------------------------------------------------------------------------------------------
+# size-independent properties and conventions
+# ------------------------------------------------------------------------------------------
+
+def test_rows_are_stochastic_and_linear_in_v():
+    g = torch.Generator().manual_seed(3)
+    q, k = gen((2, 4, 512, 64), g, torch.bfloat16).to(DEV), gen((2, 4, 512, 64), g, torch.bfloat16).to(DEV)
+    v1, v2 = gen((2, 4, 512, 64), g, torch.bfloat16).to(DEV), gen((2, 4, 512, 64), g, torch.bfloat16).to(DEV)
+    emb = PoPE(32, heads=4).to(DEV)(512)
+    emb = (emb.freqs, emb.bias.detach())
+    ones = flash_attn_with_pope(q, k, torch.ones_like(v1), pos_emb=emb, causal=True)
+    assert maxerr(ones, torch.ones_like(ones)) <= 1e-2
+    o1, o2 = flash_attn_with_pope(q, k, v1, pos_emb=emb, causal=True), flash_attn_with_pope(q, k, v2, pos_emb=emb, causal=True)
+    o12 = flash_attn_with_pope(q, k, (v1.float() + v2.float()).bfloat16(), pos_emb=emb, causal=True)
+    assert maxerr(o12, o1.float() + o2.float()) <= 5e-2
+
+
+def test_fully_masked_rows_give_zero_and_forward_is_deterministic():
+    g = torch.Generator().manual_seed(4)
+    q, k, v = (gen((1, 2, 64, 32), g, torch.bfloat16).to(DEV) for _ in range(3))
+    emb = PoPE(16, heads=2).to(DEV)(64)
+    emb = (emb.freqs, emb.bias.detach())
+    mask = torch.zeros(1, 64, dtype=torch.bool, device=DEV)
+    out, lse = _native.attn_forward(q, k, v, emb[0], emb[1], mask, False, 32 ** -0.5)
+    assert torch.all(out == 0) and torch.all(torch.isinf(lse) & (lse < 0))
+    mask[:, :40] = True
+    a = flash_attn_with_pope(q, k, v, pos_emb=emb, mask=mask, causal=True)
+    b = flash_attn_with_pope(q, k, v, pos_emb=emb, mask=mask, causal=True)
+    assert torch.equal(a, b)
+
+
+def test_decode_causal_is_top_left_aligned():
+    g = torch.Generator().manual_seed(6)
+    q, k, v = gen((1, 2, 1, 32), g).to(DEV), gen((1, 2, 48, 32), g).to(DEV), gen((1, 2, 48, 32), g).to(DEV)
+    emb = PoPE(16, heads=2).to(DEV)(48)
+    out = flash_attn_with_pope(q, k, v, pos_emb=(emb.freqs, emb.bias.detach()), causal=True)
+    assert maxerr(out[:, :, 0], v[:, :, 0]) <= 1e-6
+
+
+def test_similarity_then_softmax_matches_flash_fp32():
+    """Cross-check of the two kernels as in the reference (tests/test_flash_attn.py:78-110): < 5e-4."""
+    for nq in (1, 1024):
+        g = torch.Generator().manual_seed(8 + nq)
+        q, k, v = gen((1, nq, 8, 64), g).to(DEV), gen((1, 1024, 8, 64), g).to(DEV), gen((1, 1024, 8, 64), g).to(DEV)
+        emb = PoPE(32, heads=8).to(DEV)(1024)
+        emb = (emb.freqs, emb.bias.detach())
+        sim = compute_attn_similarity(q, k, emb, head_dimension_at_first=False)
+        attn = (sim * 64 ** -0.5).softmax(dim=-1)
+        want = torch.einsum("bhij,bjhd->bihd", attn, v)
+        got = flash_attn_with_pope(q, k, v, pos_emb=emb, head_dimension_at_first=False)
+        assert maxerr(got, want) < 5e-4
+
+
+def test_library_rejects_unsupported_and_reports_status():
+    q = torch.randn(1, 1, 4, 512, device=DEV)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        _native.attn_forward(q, q, q, torch.rand(4, 16, device=DEV), torch.zeros(1, 16, device=DEV), None, False, 1.0)
