@@ -271,8 +271,7 @@ def attn_forward(q, k, v, freqs, bias, mask, causal, scale):
     q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
     freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
     # the output takes the memory layout of q, so a (b,n,h,d) caller gets a (b,n,h,d)-contiguous result
-    out = torch.empty_strided(q.shape, q.stride(), dtype=q.dtype, device=q.device) \
-        if q.is_non_overlapping_and_dense() else torch.empty_like(q)
+    out = torch.empty_like(q)
     lse = torch.empty(q.shape[0], q.shape[1], q.shape[2], dtype=torch.float32, device=q.device)
     m8 = _mask_u8(mask)
     a = AttnArgs(C.sizeof(AttnArgs), int(causal), float(scale), 0, _shape(q, k, r), _embed_struct(freqs, bias, r),
