@@ -168,6 +168,11 @@ POPE_API const char* pope_b200_status_str(int status);
  * ("simt", "tcgen05", ...).  Diagnostic only. */
 POPE_API const char* pope_b200_last_path(void);
 
+/* Sticky device-side status of the tensor-core kernels on the current device: 0 = healthy,
+ * bit 0 = a bounded wait inside a kernel gave up (its results are then invalid).  Diagnostic:
+ * this call synchronises the device. */
+POPE_API int pope_b200_device_status(void);
+
 /* Bytes of workspace the operator needs for these arguments (`args` points at the matching
  * Pope*Args struct; pointers inside it are not dereferenced).  0 = none. */
 POPE_API size_t pope_b200_workspace_bytes(int op, const void* args);

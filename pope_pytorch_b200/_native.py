@@ -71,7 +71,8 @@ class AttnBwdArgs(C.Structure):
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
-EXPORTS = ("pope_b200_abi_version", "pope_b200_status_str", "pope_b200_last_path", "pope_b200_workspace_bytes",
+EXPORTS = ("pope_b200_abi_version", "pope_b200_status_str", "pope_b200_last_path", "pope_b200_device_status",
+           "pope_b200_workspace_bytes",
            "pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd")
 
 _lib = None
@@ -113,6 +114,13 @@ def is_available() -> bool:
 
 def last_path() -> str:
     return load_library().pope_b200_last_path().decode()
+
+
+def device_status() -> int:
+    """Sticky health word of the tensor-core kernels on the current device (synchronises)."""
+    lib = load_library()
+    lib.pope_b200_device_status.restype = C.c_int
+    return lib.pope_b200_device_status()
 
 
 def _check(rc: int, what: str) -> None:

@@ -1,6 +1,6 @@
 // extern "C" boundary of libpope_b200.so: argument validation and dispatch.
 // Declarations and the contract of each entry point live in include/pope_b200.h.
-#include <mutex>
+#include <cstdlib>
 
 #include "kernels.h"
 
@@ -29,6 +29,12 @@ int check_shape(const PopeShape& s) {
   return POPE_OK;
 }
 
+// POPE_B200_FORCE_SIMT=1 routes every call to the exact-arithmetic family (for A/B comparisons)
+bool force_simt() {
+  const char* e = std::getenv("POPE_B200_FORCE_SIMT");
+  return e && e[0] == '1';
+}
+
 int check_embed(const PopeShape& s, const PopeEmbed& e) {
   if (s.r > 0 && (!e.freqs || !e.bias)) return POPE_ERR_BAD_ARG;
   return POPE_OK;
@@ -55,12 +61,15 @@ const char* pope_b200_status_str(int status) {
 
 const char* pope_b200_last_path(void) { return g_last_path; }
 
+int pope_b200_device_status(void) { return static_cast<int>(pope::tc_read_status()); }
+
 size_t pope_b200_workspace_bytes(int op, const void* args) {
   if (!args) return 0;
   switch (op) {
     case POPE_OP_ATTN_FWD: {
       const PopeAttnArgs& a = *static_cast<const PopeAttnArgs*>(args);
       if (a.struct_bytes != sizeof(PopeAttnArgs) || check_shape(a.shape) != POPE_OK) return 0;
+      if (!force_simt() && pope::attn_fwd_tc_supported(a)) return pope::attn_fwd_tc_workspace(a);
       return pope::attn_fwd_simt_workspace(a);
     }
     case POPE_OP_ATTN_BWD: {
@@ -103,11 +112,14 @@ int pope_b200_attn_fwd(const PopeAttnArgs* a, void* stream) {
   if (rc != POPE_OK) return rc;
   if (!a->q || !a->k || !a->v || !a->out || !a->lse) return POPE_ERR_BAD_ARG;
   if (a->shape.d > 256) return POPE_ERR_UNSUPPORTED;
-  const size_t need = pope::attn_fwd_simt_workspace(*a);
+  const bool tc = !force_simt() && pope::attn_fwd_tc_supported(*a);
+  const size_t need = tc ? pope::attn_fwd_tc_workspace(*a) : pope::attn_fwd_simt_workspace(*a);
   if (need > 0 && (!a->workspace || a->workspace_bytes < need)) return POPE_ERR_WORKSPACE;
+  if (need > 0 && (reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return POPE_ERR_MISALIGNED;
   if ((rc = check_device()) != POPE_OK) return rc;
-  if (pope::attn_fwd_simt(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
-  g_last_path = "simt";
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((tc ? pope::attn_fwd_tc(*a, st) : pope::attn_fwd_simt(*a, st)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = tc ? "tcgen05" : "simt";
   return POPE_OK;
 }
 

@@ -14,6 +14,12 @@ cudaError_t attn_fwd_simt(const PopeAttnArgs& a, cudaStream_t st);
 size_t attn_bwd_simt_workspace(const PopeAttnBwdArgs& a);
 cudaError_t attn_bwd_simt(const PopeAttnBwdArgs& a, cudaStream_t st);
 
+// tensor-core (tcgen05 + TMEM) family: bf16 / fp16, d in {64, 96, 128}, r % 16 == 0, 2-D freqs
+bool attn_fwd_tc_supported(const PopeAttnArgs& a);
+size_t attn_fwd_tc_workspace(const PopeAttnArgs& a);
+cudaError_t attn_fwd_tc(const PopeAttnArgs& a, cudaStream_t st);
+unsigned int tc_read_status();  // sticky device-side status of the tensor-core kernels (synchronises)
+
 // delta[b,h,i] = sum_c out[i,c] * dout[i,c]  (fp32, (B,H,Nq) contiguous); used by every backward
 cudaError_t attn_bwd_delta(const PopeAttnBwdArgs& a, float* delta, cudaStream_t st);
 

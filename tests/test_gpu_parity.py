@@ -3,7 +3,8 @@ golden vectors, on identical seeded inputs.
 
 Tolerances (written where used): fp32 similarity 1e-4 relative to max|sim|; fp32 attention and
 fp32 gradients rtol 1e-3 / atol 1e-4 (the reference's own bound, tests/test_triton.py:50-54);
-bf16 / fp16 attention outputs and gradients 2e-2 absolute.
+bf16 / fp16 attention outputs and gradients 2e-2 absolute (widened to 2^-8 of the tensor's
+magnitude where that is larger, i.e. one bf16 rounding of the stored result).
 """
 import math
 
@@ -144,7 +145,11 @@ def run_case(b, h, hk, nq, nk, d, r, dtype, causal, masked, seed, freqs=None, bi
             errs["dfreqs_rel"] = maxerr(fg.grad, ref["dfreqs"]) / max(1.0, float(ref["dfreqs"].abs().max()))
     assert out.dtype == dtype and not torch.isnan(out.float()).any()
     for name, e in errs.items():
-        assert e <= tol, f"{name}: {e} (all: {errs})"
+        # storing a result in bf16 alone costs 2^-9 of its magnitude: where a gradient exceeds ~5 in
+        # magnitude (grouped heads sum several query heads into dk/dv) the bound scales with it
+        mag = float(ref[name].abs().max()) if (name in ref and dtype != torch.float32) else 0.0
+        bound = max(tol, 2.0 ** -8 * mag)
+        assert e <= bound, f"{name}: {e} > {bound} (all: {errs})"
     return errs
 
 

@@ -1,0 +1,61 @@
+"""The tcgen05 / TMEM kernels: they are the path taken for the benchmark shapes, they agree
+with the exact-arithmetic CUDA family on full-size inputs, and their bounded waits never fired."""
+import os
+
+import pytest
+import torch
+
+from pope_pytorch_b200 import PoPE, _native
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _fwd(q, k, v, emb, mask, causal, force_simt):
+    os.environ["POPE_B200_FORCE_SIMT"] = "1" if force_simt else "0"
+    try:
+        out, lse = _native.attn_forward(q, k, v, emb[0], emb[1], mask, causal, q.shape[-1] ** -0.5)
+        return out, lse, _native.last_path()
+    finally:
+        os.environ["POPE_B200_FORCE_SIMT"] = "0"
+
+
+@pytest.mark.parametrize("b,h,n,d,r,causal,masked,dtype", [
+    (2, 8, 1024, 64, 32, True, True, torch.bfloat16),      # forward config: causal + key padding
+    (1, 4, 4096, 128, 128, True, False, torch.bfloat16),   # training shape (4 of its 64 units)
+    (2, 8, 2048, 96, 96, False, False, torch.bfloat16),    # axial video shape
+    (1, 2, 8192, 128, 64, True, False, torch.bfloat16),    # long-context shape, shortened
+    (2, 2, 300, 64, 64, True, True, torch.float16),        # ragged tails, fp16
+    (1, 2, 257, 128, 0, False, True, torch.bfloat16),      # no rotated dims
+])
+def test_forward_tc_matches_exact_family(b, h, n, d, r, causal, masked, dtype):
+    g = torch.Generator().manual_seed(n + d)
+    q, k, v = (torch.randn(b, h, n, d, generator=g).to(dtype).to(DEV) for _ in range(3))
+    pope = PoPE(r, heads=h) if r > 0 else None
+    if pope is not None:
+        with torch.no_grad():
+            pope.bias.uniform_(-6.0, 0.0, generator=g)
+        e = pope(n)
+        emb = (e.freqs.to(DEV), e.bias.detach().to(DEV))
+    else:
+        emb = (torch.empty(n, 0, device=DEV), torch.empty(h, 0, device=DEV))
+    mask = None
+    if masked:
+        lens = torch.randint(n // 2, n + 1, (b,), generator=g)
+        mask = (torch.arange(n)[None, :] < lens[:, None]).to(DEV)
+    o_tc, lse_tc, path_tc = _fwd(q, k, v, emb, mask, causal, force_simt=False)
+    o_ex, lse_ex, path_ex = _fwd(q, k, v, emb, mask, causal, force_simt=True)
+    assert path_tc == "tcgen05" and path_ex == "simt"
+    assert _native.device_status() == 0
+    assert float((o_tc.float() - o_ex.float()).abs().max()) <= 2e-2
+    finite = torch.isfinite(lse_ex)
+    assert torch.equal(finite, torch.isfinite(lse_tc))
+    assert float((lse_tc[finite] - lse_ex[finite]).abs().max()) <= 2e-2
+
+
+def test_short_query_blocks_take_the_exact_family():
+    q = torch.randn(1, 2, 1, 64, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(1, 2, 512, 64, device=DEV, dtype=torch.bfloat16)
+    e = PoPE(32, heads=2)(512)
+    _native.attn_forward(q, k, k, e.freqs.to(DEV), e.bias.detach().to(DEV), None, False, 0.125)
+    assert _native.last_path() == "simt"
