@@ -75,6 +75,7 @@ size_t pope_b200_workspace_bytes(int op, const void* args) {
     case POPE_OP_ATTN_BWD: {
       const PopeAttnBwdArgs& a = *static_cast<const PopeAttnBwdArgs*>(args);
       if (a.struct_bytes != sizeof(PopeAttnBwdArgs) || check_shape(a.shape) != POPE_OK) return 0;
+      if (!force_simt() && pope::attn_bwd_tc_supported(a)) return pope::attn_bwd_tc_workspace(a);
       return pope::attn_bwd_simt_workspace(a);
     }
     default: return 0;
@@ -130,11 +131,14 @@ int pope_b200_attn_bwd(const PopeAttnBwdArgs* a, void* stream) {
   if (rc != POPE_OK) return rc;
   if (!a->q || !a->k || !a->v || !a->out || !a->dout || !a->lse || !a->dq || !a->dk || !a->dv) return POPE_ERR_BAD_ARG;
   if (a->shape.d > 256) return POPE_ERR_UNSUPPORTED;
-  const size_t need = pope::attn_bwd_simt_workspace(*a);
+  const bool tc = !force_simt() && pope::attn_bwd_tc_supported(*a);
+  const size_t need = tc ? pope::attn_bwd_tc_workspace(*a) : pope::attn_bwd_simt_workspace(*a);
   if (!a->workspace || a->workspace_bytes < need) return POPE_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return POPE_ERR_MISALIGNED;
   if ((rc = check_device()) != POPE_OK) return rc;
-  if (pope::attn_bwd_simt(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
-  g_last_path = "simt";
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((tc ? pope::attn_bwd_tc(*a, st) : pope::attn_bwd_simt(*a, st)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = tc ? "tcgen05" : "simt";
   return POPE_OK;
 }
 

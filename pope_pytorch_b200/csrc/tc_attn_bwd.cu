@@ -1,0 +1,233 @@
+// PoPE flash-attention backward on the Blackwell tensor cores (tcgen05 + TMEM), sm_100a only.
+//
+// Two kernels, no atomics on dq / dk / dv (deterministic):
+//   dq kernel   : a CTA keeps 128 query rows resident (Q' expanded exactly once, dO) and
+//                 streams 64-key tiles:   S = Q' K'^T, dP = dO V^T  ->  dS  ->  dQ' += dS K'
+//   dkdv kernel : a CTA keeps 128 key rows resident (K' expanded exactly once, V) and streams
+//                 64-query tiles: S^T = K' Q'^T, dP^T = V dO^T -> P^T, dS^T ->
+//                 dV += P^T dO,  dK' += dS^T Q'
+// with P = exp(S*scale - lse), dS = P (dP - delta) scale
+// (PoPE_pytorch/triton_pope_flash_attn.py:190-199) and the chain rule through the transform in
+// the epilogue (:202-210).  Accumulators live in TMEM (dq: 64+64+32+KD columns; dkdv:
+// 64+64+D+KD = 512 columns at d = r = 128); the streamed operand is expanded in registers from
+// the raw rows and a (cos, sin) phase table, the per-head phase bias being folded into whichever
+// operand is resident.  A streamed tile in shared memory serves two MMAs: as the K-major B
+// operand of the score product and, re-described as MN-major, as the B operand of the gradient
+// product -- the 8x16-byte core-matrix layout is symmetric under that exchange.
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace pope {
+
+struct TcBwdP {
+  int H, Hk, Nq, Nk, r, causal;
+  float scale, scale_log2;
+  const void *q, *k, *v, *dout;
+  void *dq, *dk, *dv;
+  Strides sq, sk, sv, sdo, sdq, sdk, sdv, sdf;
+  const float *freqs, *bias, *lse, *delta;
+  int64_t sfn, bias_sh, dbias_sh;
+  const __half2* table;
+  const uint8_t* mask;
+  int64_t msb, msn;
+  float *dfreqs, *dbias;
+  unsigned int* status;
+};
+
+constexpr int BQ = 128;  // resident rows per CTA
+constexpr int BT = 64;   // streamed rows per step
+
+// ================================================================================================
+// dq
+// ================================================================================================
+template <int D, typename T>
+__global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int DC = D / 8;
+  const int KD = D + p.r, KSTEPS = KD >> 4;
+  uint8_t* Qs = smem;                          // [KD/8][128][16 B]  resident Q'
+  uint8_t* Gs = Qs + BQ * KD * 2;              // [D/8][128][16 B]   resident dO
+  uint8_t* Ks = Gs + BQ * D * 2;               // 2 x [KD/8][64][16 B]
+  uint8_t* Vs = Ks + 2 * BT * KD * 2;          // 2 x [D/8][64][16 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * BT * D * 2);  // [0] scores ready, [1] dQ' step done
+  uint32_t* kbits = reinterpret_cast<uint32_t*>(bars + 2);           // [2 bufs][2 words]
+  uint32_t* tmem_slot = kbits + 4;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
+  const int i0 = (gridDim.x - 1 - blockIdx.x) * BQ;
+  const int qoff = p.Nk - p.Nq;
+  const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
+  const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
+  const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
+  const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
+  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
+  const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
+
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&bars[0], 1), mbar_init(&bars[1], 1);
+    mbar_init_fence();
+  }
+  // resident operands: Q' with phase (fq - bias), dO
+  stage_xform_exact128<D, T>(qbase, p.sq.n, i0, p.Nq, p.freqs, p.sfn, qoff, biasr, -1.f, p.r, Qs, tid);
+  for (int c = tid >> 7; c < DC; c += 2) {
+    const int row = tid & 127, gi = i0 + row;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (gi < p.Nq) raw = *reinterpret_cast<const uint4*>(gbase + (int64_t)gi * p.sdo.n + c * 8);
+    *reinterpret_cast<uint4*>(Gs + c * (BQ * 16) + row * 16) = raw;
+  }
+
+  int n_end = p.Nk;
+  if (p.causal) n_end = min(n_end, min(i0 + BQ, p.Nq));
+  const int T_tiles = (n_end + BT - 1) / BT;
+
+  auto stage = [&](int jt) {
+    const int buf = jt & 1, n0 = jt * BT;
+    stage_xform_table<D, BT, T>(kbase, p.sk.n, n0, p.Nk, p.table, 0, p.r, Ks + buf * (BT * KD * 2), tid);
+    stage_plain<D, BT, T>(vbase, p.sv.n, n0, p.Nk, Vs + buf * (BT * D * 2), tid);
+    if (tid < BT) {
+      const int j = n0 + tid;
+      const bool ok = j < p.Nk && (!maskb || maskb[(int64_t)j * p.msn] != 0);
+      const uint32_t bits = __ballot_sync(0xffffffffu, ok);
+      if ((tid & 31) == 0) kbits[buf * 2 + (tid >> 5)] = bits;
+    }
+  };
+
+  stage(0);
+  fence_async_smem();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  // TMEM columns: S [0,64), dP [64,128), dS (bf16 pairs) [128,160), dQ' [256, 256+KD)
+  const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
+  const uint32_t idesc_q = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
+  const uint32_t qs_addr = smem_u32(Qs), gs_addr = smem_u32(Gs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+
+  auto issue_scores = [&](int jt) {
+    const int buf = jt & 1;
+    for (int ks = 0; ks < KSTEPS; ++ks)
+      mma_ss(tmem, smem_desc(qs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
+             smem_desc(ks_addr + buf * (BT * KD * 2) + ks * 2 * (BT * 16), BT * 16, 128), idesc_s, ks > 0);
+    for (int ks = 0; ks < D / 16; ++ks)
+      mma_ss(tmem + 64, smem_desc(gs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
+             smem_desc(vs_addr + buf * (BT * D * 2) + ks * 2 * (BT * 16), BT * 16, 128), idesc_s, ks > 0);
+    mma_commit(&bars[0]);
+  };
+  if (tid == 0) issue_scores(0);
+
+  bool failed = false;
+  const int row = tid & 127, half = tid >> 7;           // thread = (query row, 32-key half)
+  const int gi = i0 + row;
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const float lse2 = gi < p.Nq ? p.lse[(int64_t)u * p.Nq + gi] * LOG2E : -CUDART_INF_F;
+  const float dlt = gi < p.Nq ? p.delta[(int64_t)u * p.Nq + gi] : 0.f;
+
+  for (int j = 0; j < T_tiles; ++j) {
+    const int buf = j & 1, n0 = j * BT;
+    if (!failed) failed = !mbar_wait(&bars[0], j & 1, WAIT_LIMIT);
+    fence_after_sync();
+    uint32_t sv[32], dv[32];
+    tmem_ld32(tmem + lane_base + half * 32, sv);
+    tmem_ld32(tmem + lane_base + 64 + half * 32, dv);
+    tmem_ld_wait();
+    uint32_t vis = kbits[buf * 2 + half];
+    if (p.causal) {
+      const int lim = gi - (n0 + half * 32);  // columns <= lim visible
+      vis &= lim >= 31 ? 0xffffffffu : (lim < 0 ? 0u : ((2u << lim) - 1u));
+    }
+    if (lse2 == -CUDART_INF_F) vis = 0u;
+    const float lse_use = lse2 == -CUDART_INF_F ? 0.f : lse2;
+    uint32_t pk[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      float p0 = ex2_approx(__uint_as_float(sv[2 * e]) * p.scale_log2 - lse_use);
+      float p1 = ex2_approx(__uint_as_float(sv[2 * e + 1]) * p.scale_log2 - lse_use);
+      p0 = ((vis >> (2 * e)) & 1u) ? p0 : 0.f;
+      p1 = ((vis >> (2 * e + 1)) & 1u) ? p1 : 0.f;
+      const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
+      const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
+      pk[e] = pack2<T>(d0, d1);
+    }
+    // the dS columns were read by the dQ' step of tile j-1
+    if (j >= 1 && !failed) failed = !mbar_wait(&bars[1], (j - 1) & 1, WAIT_LIMIT);
+    tmem_st16(tmem + lane_base + 128 + half * 16, pk);
+    tmem_st_wait();
+    fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      fence_after_sync();
+      for (int ks = 0; ks < BT / 16; ++ks)
+        mma_ts(tmem + 256, tmem + 128 + ks * 8, smem_desc(ks_addr + buf * (BT * KD * 2) + ks * 2 * 128, 128, BT * 16),
+               idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
+      mma_commit(&bars[1]);
+    }
+    if (j + 1 < T_tiles) {
+      stage(j + 1);  // buffer 1-buf was last read by the dQ' step of tile j-1 (waited for above)
+      fence_async_smem();
+      fence_before_sync();
+      __syncthreads();
+      if (tid == 0) {
+        fence_after_sync();
+        issue_scores(j + 1);
+      }
+    }
+  }
+
+  // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
+  if (!failed) failed = !mbar_wait(&bars[1], (T_tiles - 1) & 1, WAIT_LIMIT);
+  fence_after_sync();
+  {
+    constexpr int HW = D / 2;  // features handled by this thread: [half*HW, half*HW + HW)
+    const uint32_t acc = tmem + lane_base + 256;
+    const T* qrow = qbase + (int64_t)gi * p.sq.n;
+    T* dqrow = (T*)p.dq + b * p.sdq.b + h * p.sdq.h + (int64_t)gi * p.sdq.n;
+    const float* frow = p.r > 0 ? p.freqs + (int64_t)(qoff + gi) * p.sfn : nullptr;
+    float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + h * p.sdf.h + (int64_t)(qoff + gi) * p.sdf.n : nullptr;
+#pragma unroll
+    for (int c0 = 0; c0 < HW; c0 += 16) {
+      const int cbase = half * HW + c0;
+      uint32_t gc[16], gs[16];
+      tmem_ld16(acc + cbase, gc);
+      const bool rot = cbase < p.r;  // r is a multiple of 16: the 16-wide group is rotated as a whole
+      if (rot) tmem_ld16(acc + D + cbase, gs);
+      tmem_ld_wait();
+      if (gi < p.Nq) {
+        uint32_t outw[8];
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
+          if (rot) {
+            const uint32_t qw = *reinterpret_cast<const uint32_t*>(qrow + cbase + e);
+            const float2 x = unpack2<T>(qw);
+            float s0, c0f, s1, c1f;
+            sincosf(frow[cbase + e] - biasr[cbase + e], &s0, &c0f);
+            sincosf(frow[cbase + e + 1] - biasr[cbase + e + 1], &s1, &c1f);
+            const float h0 = __uint_as_float(gs[e]), h1 = __uint_as_float(gs[e + 1]);
+            if (dfrow) {
+              atomicAdd(dfrow + cbase + e, softplus_f(x.x) * (h0 * c0f - g0 * s0));
+              atomicAdd(dfrow + cbase + e + 1, softplus_f(x.y) * (h1 * c1f - g1 * s1));
+            }
+            g0 = (g0 * c0f + h0 * s0) * sigmoid_f(x.x);
+            g1 = (g1 * c1f + h1 * s1) * sigmoid_f(x.y);
+          }
+          outw[e >> 1] = pack2<T>(g0, g1);
+        }
+        *reinterpret_cast<uint4*>(dqrow + cbase) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+        *reinterpret_cast<uint4*>(dqrow + cbase + 8) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+      }
+    }
+  }
+  if (failed) atomicOr(p.status, 1u);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace pope
+
+#include "tc_attn_bwd_dkdv.inl"

@@ -1,0 +1,305 @@
+// dk / dv kernel and the host-side launch of the tensor-core backward (included by tc_attn_bwd.cu).
+namespace pope {
+
+template <int D, typename T>
+__global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int DC = D / 8;
+  const int KD = D + p.r, KSTEPS = KD >> 4;
+  uint8_t* Ks = smem;                          // [KD/8][128][16 B]  resident K' (phase fk + bias)
+  uint8_t* Vs = Ks + BQ * KD * 2;              // [D/8][128][16 B]   resident V
+  uint8_t* Qb = Vs + BQ * D * 2;               // 2 x [KD/8][64][16 B] streamed Q'
+  uint8_t* Gb = Qb + 2 * BT * KD * 2;          // 2 x [D/8][64][16 B]  streamed dO
+  uint8_t* Ps = Gb + 2 * BT * D * 2;           // [8 chunks][128][16 B] P^T  (A operand, K = 64 queries)
+  uint8_t* Ds = Ps + BQ * BT * 2;              // [8 chunks][128][16 B] dS^T
+  float* rowstat = reinterpret_cast<float*>(Ds + BQ * BT * 2);  // 2 bufs x (64 lse*log2e, 64 delta)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rowstat + 2 * 128);   // [0] scores ready, [1] accumulation done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int u = blockIdx.y, b = u / p.Hk, hk = u % p.Hk;
+  const int j0 = blockIdx.x * BQ;
+  const int qoff = p.Nk - p.Nq;
+  const int groups = p.H / p.Hk;
+  const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
+  const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
+  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
+  const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
+
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&bars[0], 1), mbar_init(&bars[1], 1);
+    mbar_init_fence();
+  }
+  stage_xform_exact128<D, T>(kbase, p.sk.n, j0, p.Nk, p.freqs, p.sfn, 0, biasr, 1.f, p.r, Ks, tid);
+  for (int c = tid >> 7; c < DC; c += 2) {
+    const int row = tid & 127, gj = j0 + row;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (gj < p.Nk) raw = *reinterpret_cast<const uint4*>(vbase + (int64_t)gj * p.sv.n + c * 8);
+    *reinterpret_cast<uint4*>(Vs + c * (BQ * 16) + row * 16) = raw;
+  }
+
+  // query tiles: under the causal mask rows i < j0 see none of this CTA's keys
+  const int m_begin = p.causal ? (j0 / BT) * BT : 0;
+  const int tiles_per_group = m_begin < p.Nq ? (p.Nq - m_begin + BT - 1) / BT : 0;
+  const int T_tiles = tiles_per_group * groups;
+
+  auto stage = [&](int jt) {
+    const int buf = jt & 1, g = jt / tiles_per_group, m0 = m_begin + (jt % tiles_per_group) * BT;
+    const int h = g * p.Hk + hk;
+    const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
+    const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
+    stage_xform_table<D, BT, T>(qbase, p.sq.n, m0, p.Nq, p.table, qoff, p.r, Qb + buf * (BT * KD * 2), tid);
+    stage_plain<D, BT, T>(gbase, p.sdo.n, m0, p.Nq, Gb + buf * (BT * D * 2), tid);
+    if (tid < BT) {
+      const int gi = m0 + tid;
+      const int64_t uq = (int64_t)(b * p.H + h) * p.Nq + gi;
+      rowstat[buf * 128 + tid] = gi < p.Nq ? p.lse[uq] * LOG2E : -CUDART_INF_F;
+      rowstat[buf * 128 + 64 + tid] = gi < p.Nq ? p.delta[uq] : 0.f;
+    }
+  };
+
+  const int row = tid & 127, half = tid >> 7;          // thread = (key row, 32-query half)
+  const int gj = j0 + row;
+  const bool key_ok = gj < p.Nk && (!maskb || maskb[(int64_t)gj * p.msn] != 0);
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  bool failed = false;
+
+  if (T_tiles > 0) stage(0);
+  fence_async_smem();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  // TMEM columns: S^T [0,64), dP^T [64,128), dV [128, 128+D), dK' [256, 256+KD)
+  const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
+  const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
+  const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
+  const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
+  const uint32_t ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
+
+  auto issue_scores = [&](int jt) {
+    const int buf = jt & 1;
+    for (int ks = 0; ks < KSTEPS; ++ks)
+      mma_ss(tmem, smem_desc(ks_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
+             smem_desc(qb_addr + buf * (BT * KD * 2) + ks * 2 * (BT * 16), BT * 16, 128), idesc_s, ks > 0);
+    for (int ks = 0; ks < D / 16; ++ks)
+      mma_ss(tmem + 64, smem_desc(vs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
+             smem_desc(gb_addr + buf * (BT * D * 2) + ks * 2 * (BT * 16), BT * 16, 128), idesc_s, ks > 0);
+    mma_commit(&bars[0]);
+  };
+  if (tid == 0 && T_tiles > 0) issue_scores(0);
+
+  for (int j = 0; j < T_tiles; ++j) {
+    const int buf = j & 1;
+    const int m0 = m_begin + (j % tiles_per_group) * BT;
+    if (!failed) failed = !mbar_wait(&bars[0], j & 1, WAIT_LIMIT);
+    fence_after_sync();
+    uint32_t sv[32], dv[32];
+    tmem_ld32(tmem + lane_base + half * 32, sv);
+    tmem_ld32(tmem + lane_base + 64 + half * 32, dv);
+    tmem_ld_wait();
+    // P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
+    if (j >= 1 && !failed) failed = !mbar_wait(&bars[1], (j - 1) & 1, WAIT_LIMIT);
+    const float* st = rowstat + buf * 128 + half * 32;
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      uint32_t pw[4], dw[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float pv[2], dsv[2];
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int col = cc * 8 + e * 2 + t;            // query column within this thread's half
+          const int gi = m0 + half * 32 + col;
+          const float l2 = st[col];
+          const bool ok = key_ok && gi < p.Nq && (!p.causal || gj <= gi) && l2 != -CUDART_INF_F;
+          const float pr = ok ? ex2_approx(__uint_as_float(sv[col]) * p.scale_log2 - l2) : 0.f;
+          pv[t] = pr;
+          dsv[t] = pr * (__uint_as_float(dv[col]) - st[64 + col]) * p.scale;
+        }
+        pw[e] = pack2<T>(pv[0], pv[1]);
+        dw[e] = pack2<T>(dsv[0], dsv[1]);
+      }
+      const int chunk = half * 4 + cc;
+      *reinterpret_cast<uint4*>(Ps + chunk * (BQ * 16) + row * 16) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+      *reinterpret_cast<uint4*>(Ds + chunk * (BQ * 16) + row * 16) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+    }
+    fence_async_smem();
+    fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      fence_after_sync();
+      for (int ks = 0; ks < BT / 16; ++ks) {
+        const uint64_t pa = smem_desc(ps_addr + ks * 2 * (BQ * 16), BQ * 16, 128);
+        const uint64_t da = smem_desc(ds_addr + ks * 2 * (BQ * 16), BQ * 16, 128);
+        mma_ss(tmem + 128, pa, smem_desc(gb_addr + buf * (BT * D * 2) + ks * 2 * 128, 128, BT * 16), idesc_v,
+               (j > 0 || ks > 0) ? 1u : 0u);
+        mma_ss(tmem + 256, da, smem_desc(qb_addr + buf * (BT * KD * 2) + ks * 2 * 128, 128, BT * 16), idesc_k,
+               (j > 0 || ks > 0) ? 1u : 0u);
+      }
+      mma_commit(&bars[1]);
+    }
+    if (j + 1 < T_tiles) {
+      stage(j + 1);  // buffers 1-buf were last read by the accumulation step of tile j-1 (waited for above)
+      fence_async_smem();
+      fence_before_sync();
+      __syncthreads();
+      if (tid == 0) {
+        fence_after_sync();
+        issue_scores(j + 1);
+      }
+    }
+  }
+
+  // ---- epilogue ---------------------------------------------------------------------------------
+  if (T_tiles > 0 && !failed) failed = !mbar_wait(&bars[1], (T_tiles - 1) & 1, WAIT_LIMIT);
+  fence_after_sync();
+  __syncthreads();                       // all MMAs done: the streamed buffers can be reused
+  float* red = reinterpret_cast<float*>(Qb);   // [r] per-CTA sum of the key-phase gradient
+  for (int c = tid; c < p.r; c += 256) red[c] = 0.f;
+  __syncthreads();
+  {
+    constexpr int HW = D / 2;
+    const uint32_t accv = tmem + lane_base + 128, acck = tmem + lane_base + 256;
+    const T* krow = kbase + (int64_t)gj * p.sk.n;
+    T* dkrow = (T*)p.dk + b * p.sdk.b + hk * p.sdk.h + (int64_t)gj * p.sdk.n;
+    T* dvrow = (T*)p.dv + b * p.sdv.b + hk * p.sdv.h + (int64_t)gj * p.sdv.n;
+    const float* frow = p.r > 0 ? p.freqs + (int64_t)gj * p.sfn : nullptr;
+    float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + hk * p.sdf.h + (int64_t)gj * p.sdf.n : nullptr;
+    const bool live = gj < p.Nk;
+#pragma unroll
+    for (int c0 = 0; c0 < HW; c0 += 16) {
+      const int cbase = half * HW + c0;
+      uint32_t gv[16], gc[16], gs[16];
+      const bool rot = cbase < p.r;
+      if (T_tiles > 0) {
+        tmem_ld16(accv + cbase, gv);
+        tmem_ld16(acck + cbase, gc);
+        if (rot) tmem_ld16(acck + D + cbase, gs);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) gv[e] = gc[e] = gs[e] = 0u;
+      }
+      uint32_t wv[8], wk[8];
+#pragma unroll
+      for (int e = 0; e < 16; e += 2) {
+        wv[e >> 1] = pack2<T>(__uint_as_float(gv[e]), __uint_as_float(gv[e + 1]));
+        float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
+        if (rot) {
+          float d0 = 0.f, d1 = 0.f;
+          if (live) {
+            const float2 x = unpack2<T>(*reinterpret_cast<const uint32_t*>(krow + cbase + e));
+            float s0, c0f, s1, c1f;
+            sincosf(frow[cbase + e] + biasr[cbase + e], &s0, &c0f);
+            sincosf(frow[cbase + e + 1] + biasr[cbase + e + 1], &s1, &c1f);
+            const float h0 = __uint_as_float(gs[e]), h1 = __uint_as_float(gs[e + 1]);
+            d0 = softplus_f(x.x) * (h0 * c0f - g0 * s0);
+            d1 = softplus_f(x.y) * (h1 * c1f - g1 * s1);
+            if (dfrow) atomicAdd(dfrow + cbase + e, d0), atomicAdd(dfrow + cbase + e + 1, d1);
+            g0 = (g0 * c0f + h0 * s0) * sigmoid_f(x.x);
+            g1 = (g1 * c1f + h1 * s1) * sigmoid_f(x.y);
+          }
+          if (p.dbias) {   // warp-uniform branch: sum over the 32 key rows of this warp
+            d0 = warp_sum(d0), d1 = warp_sum(d1);
+            if ((tid & 31) == 0) atomicAdd(&red[cbase + e], d0), atomicAdd(&red[cbase + e + 1], d1);
+          }
+        }
+        wk[e >> 1] = pack2<T>(g0, g1);
+      }
+      if (live) {
+        *reinterpret_cast<uint4*>(dvrow + cbase) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        *reinterpret_cast<uint4*>(dvrow + cbase + 8) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+        *reinterpret_cast<uint4*>(dkrow + cbase) = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+        *reinterpret_cast<uint4*>(dkrow + cbase + 8) = make_uint4(wk[4], wk[5], wk[6], wk[7]);
+      }
+    }
+  }
+  if (p.dbias && p.r > 0) {
+    __syncthreads();
+    for (int c = tid; c < p.r; c += 256) atomicAdd(p.dbias + hk * p.dbias_sh + c, red[c]);
+  }
+  if (failed) atomicOr(p.status, 1u);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+static bool bwd_aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+static bool bwd_stride_ok(const PopeStride3& s) { return s.b % 8 == 0 && s.h % 8 == 0 && s.n % 8 == 0; }
+
+bool attn_bwd_tc_supported(const PopeAttnBwdArgs& a) {
+  const PopeShape& s = a.shape;
+  if (s.dtype != POPE_BF16 && s.dtype != POPE_F16) return false;
+  if (s.d != 64 && s.d != 96 && s.d != 128) return false;
+  if (s.r % 16 != 0) return false;
+  if (s.Nq < 64) return false;
+  if (s.r > 0 && (a.embed.sf.b != 0 || a.embed.sf.h != 0)) return false;
+  if (a.dfreqs && (a.sdf.b != 0 || a.sdf.h != 0)) return false;
+  const void* ptrs[] = {a.q, a.k, a.v, a.dout, a.dq, a.dk, a.dv};
+  for (const void* ptr : ptrs)
+    if (!bwd_aligned16(ptr)) return false;
+  const PopeStride3 strides[] = {a.sq, a.sk, a.sv, a.sdo, a.sdq, a.sdk, a.sdv};
+  for (const PopeStride3& st : strides)
+    if (!bwd_stride_ok(st)) return false;
+  return true;
+}
+
+static size_t delta_bytes(const PopeShape& s) { return ((size_t)s.B * s.H * s.Nq * sizeof(float) + 255) / 256 * 256; }
+
+size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
+  return delta_bytes(a.shape) + (size_t)a.shape.Nk * a.shape.r * sizeof(__half2) + 16;
+}
+
+template <int D, typename T>
+static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
+  const PopeShape& s = a.shape;
+  float* delta = reinterpret_cast<float*>(a.workspace);
+  __half2* table = reinterpret_cast<__half2*>(reinterpret_cast<uint8_t*>(a.workspace) + delta_bytes(s));
+  cudaError_t e = attn_bwd_delta(a, delta, st);
+  if (e != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, table, st)) != cudaSuccess) return e;
+  TcBwdP p = {};
+  p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
+  p.scale = a.softmax_scale, p.scale_log2 = a.softmax_scale * LOG2E;
+  p.q = a.q, p.k = a.k, p.v = a.v, p.dout = a.dout, p.dq = a.dq, p.dk = a.dk, p.dv = a.dv;
+  p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.sdo = a.sdo, p.sdq = a.sdq, p.sdk = a.sdk, p.sdv = a.sdv, p.sdf = a.sdf;
+  p.freqs = a.embed.freqs, p.bias = a.embed.bias, p.lse = a.lse, p.delta = delta;
+  p.sfn = a.embed.sf.n, p.bias_sh = a.embed.bias_stride_h, p.dbias_sh = a.dbias_stride_h;
+  p.table = table, p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
+  p.dfreqs = s.r > 0 ? a.dfreqs : nullptr, p.dbias = s.r > 0 ? a.dbias : nullptr;
+  p.status = tc_status_ptr();
+  if (!p.status) return cudaErrorInvalidSymbol;
+  const int KD = s.d + s.r;
+  size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + 2 * BT * KD * 2 + 2 * BT * D * 2 + 2 * 8 + 4 * 4 + 16;
+  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + 2 * BT * KD * 2 + 2 * BT * D * 2 + 2 * BQ * BT * 2 + 256 * 4 + 2 * 8 + 16;
+  // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
+  if (smem_q < 120 * 1024) smem_q = 120 * 1024;
+  if (smem_k < 120 * 1024) smem_k = 120 * 1024;
+  if ((e = cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(attn_bwd_dkdv_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k)) != cudaSuccess) return e;
+  attn_bwd_dq_tc_kernel<D, T><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), 256, smem_q, st>>>(p);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), 256, smem_k, st>>>(p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t bwd_tc_d(const PopeAttnBwdArgs& a, cudaStream_t st) {
+  switch (a.shape.d) {
+    case 64: return launch_bwd_tc<64, T>(a, st);
+    case 96: return launch_bwd_tc<96, T>(a, st);
+    default: return launch_bwd_tc<128, T>(a, st);
+  }
+}
+
+cudaError_t attn_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
+  return a.shape.dtype == POPE_BF16 ? bwd_tc_d<__nv_bfloat16>(a, st) : bwd_tc_d<__half>(a, st);
+}
+
+}  // namespace pope

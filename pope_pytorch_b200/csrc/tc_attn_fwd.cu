@@ -19,60 +19,22 @@
 //
 // Semantics follow PoPE_pytorch/triton_pope_flash_attn.py:23-117 (top-left causal mask,
 // bottom-right positions, mask True = keep, zero output and -inf LSE for empty rows).
-#include <math_constants.h>
-
-#include "common.cuh"
 #include "kernels.h"
-#include "tc05.cuh"
+#include "tc_common.cuh"
 
 namespace pope {
 
-using namespace tc;
-
 __device__ unsigned int g_tc_status = 0;  // sticky: bit 0 = a bounded wait gave up
+
+unsigned int* tc_status_ptr() {
+  void* p = nullptr;
+  return cudaGetSymbolAddress(&p, g_tc_status) == cudaSuccess ? static_cast<unsigned int*>(p) : nullptr;
+}
 
 unsigned int tc_read_status() {
   unsigned int v = 0;
   cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(v));
   return v;
-}
-
-template <typename T> struct TcFmt;
-template <> struct TcFmt<__nv_bfloat16> { static constexpr uint32_t fmt = FMT_BF16; };
-template <> struct TcFmt<__half> { static constexpr uint32_t fmt = FMT_F16; };
-
-template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 v = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t u);
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
-  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
-}
-template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
-  return __half22float2(*reinterpret_cast<__half2*>(&u));
-}
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float lg2_approx(float x) {
-  float y;
-  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// softplus(x) = max(x,0) + log1p(exp(-|x|)); beyond x = 20 the second term is below 2.1e-9,
-// i.e. the reference's cut-over to the identity is reproduced to fp32 rounding.
-__device__ __forceinline__ float softplus_fast(float x) {
-  const float t = ex2_approx(-fabsf(x) * 1.4426950408889634f);
-  return fmaxf(x, 0.f) + lg2_approx(1.f + t) * 0.6931471805599453f;
 }
 
 // ---- pre-pass: table[pos][c] = (cos, sin) of freqs[pos][c] as half2 ---------------------------
@@ -83,6 +45,12 @@ __global__ void pope_trig_table_kernel(const float* freqs, int64_t sfn, int n, i
   float sn, cs;
   sincosf(freqs[pos * sfn + c], &sn, &cs);
   table[idx] = __floats2half2_rn(cs, sn);
+}
+
+cudaError_t launch_trig_table(const float* freqs, int64_t sfn, int n, int r, __half2* table, cudaStream_t st) {
+  const int64_t total = (int64_t)n * r;
+  pope_trig_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(freqs, sfn, n, r, table);
+  return cudaGetLastError();
 }
 
 struct TcFwdP {
@@ -103,7 +71,6 @@ struct TcFwdP {
 
 constexpr int TQ = 128;   // rows per MMA tile
 constexpr int TK = 64;    // keys per step
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 // Expand 64 key rows starting at n0 into Kbuf (K-major, chunk-major storage: chunk*1024 + row*16),
 // stage the matching V rows MN-major (chunk*1024 + key*16) and publish the key-validity bits.
@@ -444,9 +411,8 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   if (s.r > 0) {
     const int64_t n = (int64_t)s.Nk * s.r;
-    pope_trig_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.embed.freqs, a.embed.sf.n, s.Nk, s.r,
-                                                                       reinterpret_cast<__half2*>(a.workspace));
-    cudaError_t e = cudaGetLastError();
+    (void)n;
+    cudaError_t e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, reinterpret_cast<__half2*>(a.workspace), st);
     if (e != cudaSuccess) return e;
   }
   const int KD = s.d + s.r;

@@ -59,3 +59,53 @@ def test_short_query_blocks_take_the_exact_family():
     e = PoPE(32, heads=2)(512)
     _native.attn_forward(q, k, k, e.freqs.to(DEV), e.bias.detach().to(DEV), None, False, 0.125)
     assert _native.last_path() == "simt"
+
+
+def _bwd(do, q, k, v, out, lse, emb, mask, causal, force_simt, want_dfreqs=True):
+    os.environ["POPE_B200_FORCE_SIMT"] = "1" if force_simt else "0"
+    try:
+        res = _native.attn_backward(do, q, k, v, out, lse, emb[0], emb[1], mask, causal, q.shape[-1] ** -0.5,
+                                    want_dfreqs, True)
+        return res, _native.last_path()
+    finally:
+        os.environ["POPE_B200_FORCE_SIMT"] = "0"
+
+
+@pytest.mark.parametrize("b,h,hk,n,d,r,causal,masked,dtype", [
+    (2, 8, 8, 1024, 64, 32, True, True, torch.bfloat16),
+    (1, 4, 4, 4096, 128, 128, True, False, torch.bfloat16),
+    (2, 4, 4, 2048, 96, 96, False, False, torch.bfloat16),
+    (1, 2, 2, 2048, 128, 64, True, False, torch.bfloat16),
+    (2, 2, 2, 300, 64, 64, True, True, torch.float16),
+    (1, 2, 2, 257, 128, 0, False, True, torch.bfloat16),
+    (1, 4, 2, 320, 64, 32, True, False, torch.bfloat16),     # grouped heads
+])
+def test_backward_tc_matches_exact_family(b, h, hk, n, d, r, causal, masked, dtype):
+    g = torch.Generator().manual_seed(n + d + 1)
+    q = torch.randn(b, h, n, d, generator=g).to(dtype).to(DEV)
+    k, v = (torch.randn(b, hk, n, d, generator=g).to(dtype).to(DEV) for _ in range(2))
+    do = torch.randn(b, h, n, d, generator=g).to(dtype).to(DEV)
+    if r > 0:
+        pope = PoPE(r, heads=hk)
+        with torch.no_grad():
+            pope.bias.uniform_(-6.0, 0.0, generator=g)
+        e = pope(n)
+        emb = (e.freqs.to(DEV), e.bias.detach().to(DEV))
+    else:
+        emb = (torch.empty(n, 0, device=DEV), torch.empty(hk, 0, device=DEV))
+    mask = None
+    if masked:
+        lens = torch.randint(n // 2, n + 1, (b,), generator=g)
+        mask = (torch.arange(n)[None, :] < lens[:, None]).to(DEV)
+    out, lse, _ = _fwd(q, k, v, emb, mask, causal, force_simt=True)
+    (dq1, dk1, dv1, df1, db1), path1 = _bwd(do, q, k, v, out, lse, emb, mask, causal, force_simt=False)
+    (dq0, dk0, dv0, df0, db0), path0 = _bwd(do, q, k, v, out, lse, emb, mask, causal, force_simt=True)
+    assert path1 == "tcgen05" and path0 == "simt"
+    assert _native.device_status() == 0
+    for name, a1, a0 in (("dq", dq1, dq0), ("dk", dk1, dk0), ("dv", dv1, dv0)):
+        err = float((a1.float() - a0.float()).abs().max())
+        assert err <= max(2e-2, 2.0 ** -8 * float(a0.float().abs().max())), f"{name}: {err}"
+    if r > 0:
+        for name, a1, a0 in (("dbias", db1, db0), ("dfreqs", df1, df0)):
+            rel = float((a1 - a0).abs().max() / a0.abs().max().clamp_min(1.0))
+            assert rel <= 2e-2, f"{name}: {rel}"
