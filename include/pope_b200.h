@@ -50,7 +50,8 @@ typedef enum PopeStatus {
   POPE_ERR_MISALIGNED = -3,   /* a pointer or stride breaks the documented alignment          */
   POPE_ERR_WORKSPACE = -4,    /* workspace missing or smaller than pope_b200_workspace_bytes   */
   POPE_ERR_CUDA = -5,         /* a CUDA runtime call failed (launch, attribute, symbol lookup) */
-  POPE_ERR_ARCH = -6          /* the current device is not compute capability 10.x            */
+  POPE_ERR_ARCH = -6,         /* the current device is not compute capability 10.x            */
+  POPE_ERR_TOO_LARGE = -7     /* the problem exceeds a fixed built-in capacity                */
 } PopeStatus;
 
 typedef enum PopeDtype { POPE_F32 = 0, POPE_BF16 = 1, POPE_F16 = 2 } PopeDtype;
@@ -181,6 +182,30 @@ POPE_API int pope_b200_sim_fwd(const PopeSimArgs* args, void* stream);
 POPE_API int pope_b200_sim_bwd(const PopeSimBwdArgs* args, void* stream);
 POPE_API int pope_b200_attn_fwd(const PopeAttnArgs* args, void* stream);
 POPE_API int pope_b200_attn_bwd(const PopeAttnBwdArgs* args, void* stream);
+
+/* ---- attention forward for callers that cannot allocate -----------------------------------------
+ * (No counterpart in the reference: its wrappers always allocate through torch.)
+ *
+ * Same arguments and results as pope_b200_attn_fwd, but `workspace` / `workspace_bytes` are
+ * ignored: the kernel's scratch (its position phase table) lives in a fixed array inside the
+ * library instead.  Meant for hosts that may not touch a device allocator where they call us --
+ * an inference loop whose memory plan is frozen, a plugin that is only ever handed input and
+ * output buffers, a latency-critical thread that must not take the allocator's lock.  The call
+ * itself performs no device allocation or free of any kind.
+ *
+ * Limits and rules
+ *   - Only the tensor-core shapes are served (bf16/fp16, d in {64,96,128}, r % 16 == 0, Nq >= 64,
+ *     2-D freqs, 16-byte aligned rows); anything else returns POPE_ERR_UNSUPPORTED.
+ *   - The table needs Nk * r * 4 + 16 bytes; more than POPE_B200_NOALLOC_MAX_SCRATCH returns
+ *     POPE_ERR_TOO_LARGE and launches nothing.  Every GPU that loads the library holds that many
+ *     bytes until the process exits.
+ *   - The first call on each device looks up the array's device address (a one-time runtime
+ *     query made with that device current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array and each call rewrites the part it uses, so
+ *     nothing is carried over between calls -- but two calls whose kernels overlap on the GPU
+ *     (different streams, no ordering) race on it.  Serialise them. */
+#define POPE_B200_NOALLOC_MAX_SCRATCH (4u << 20)
+POPE_API int pope_b200_attn_fwd_noalloc(const PopeAttnArgs* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -72,7 +72,7 @@ class AttnBwdArgs(C.Structure):
 
 
 EXPORTS = ("pope_b200_abi_version", "pope_b200_status_str", "pope_b200_last_path", "pope_b200_device_status",
-           "pope_b200_workspace_bytes",
+           "pope_b200_workspace_bytes", "pope_b200_attn_fwd_noalloc",
            "pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd")
 
 _lib = None
@@ -322,6 +322,31 @@ def attn_backward(dout, q, k, v, out, lse, freqs, bias, mask, causal, scale, nee
     if need_dbias and dbias is None:
         dbias = torch.zeros_like(bias)
     return dq, dk, dv, dfreqs, dbias
+
+
+NOALLOC_MAX_SCRATCH = 4 << 20
+
+
+def attn_forward_noalloc(q, k, v, freqs, bias, mask, causal, scale, out, lse):
+    """Forward attention through ``pope_b200_attn_fwd_noalloc``: for hosts that must not allocate
+    device memory at call time.  Every tensor, including ``out`` (like q) and ``lse``
+    (b, h, nq) fp32, is supplied by the caller; the library keeps its scratch in a fixed internal
+    array, so this wrapper creates no tensor either.  Inputs must already be in the form the
+    kernel reads (CUDA, fp32 contiguous freqs/bias, feature-contiguous q/k/v, uint8/bool mask).
+    Raises RuntimeError when the shape is not served or needs more than NOALLOC_MAX_SCRATCH.
+    Calls that overlap on the GPU share the scratch and race; keep them on one stream."""
+    lib = load_library()
+    lib.pope_b200_attn_fwd_noalloc.restype = C.c_int
+    lib.pope_b200_attn_fwd_noalloc.argtypes = [C.c_void_p, C.c_void_p]
+    r = freqs.shape[-1]
+    m8 = _mask_u8(mask)
+    a = AttnArgs(C.sizeof(AttnArgs), int(causal), float(scale), 0, _shape(q, k, r), _embed_struct(freqs, bias, r),
+                 q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), v.data_ptr(), _s3(v), out.data_ptr(), _s3(out),
+                 lse.data_ptr(), m8.data_ptr() if m8 is not None else None,
+                 m8.stride(0) if m8 is not None else 0, m8.stride(1) if m8 is not None else 0, None, 0)
+    with torch.cuda.device(q.device):
+        _check(lib.pope_b200_attn_fwd_noalloc(C.addressof(a), _stream_ptr(q)), "pope_b200_attn_fwd_noalloc")
+    return out, lse
 
 
 class _FlashAttn(torch.autograd.Function):

@@ -55,6 +55,7 @@ const char* pope_b200_status_str(int status) {
     case POPE_ERR_WORKSPACE: return "workspace missing or too small";
     case POPE_ERR_CUDA: return "CUDA runtime error";
     case POPE_ERR_ARCH: return "device is not compute capability 10.x (B200)";
+    case POPE_ERR_TOO_LARGE: return "problem exceeds the library's fixed built-in scratch capacity";
     default: return "unknown status";
   }
 }

@@ -19,6 +19,8 @@
 //
 // Semantics follow PoPE_pytorch/triton_pope_flash_attn.py:23-117 (top-left causal mask,
 // bottom-right positions, mask True = keep, zero output and -inf LSE for empty rows).
+#include <mutex>
+
 #include "kernels.h"
 #include "tc_common.cuh"
 
@@ -440,4 +442,58 @@ cudaError_t attn_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   return a.shape.dtype == POPE_BF16 ? fwd_tc_d<__nv_bfloat16>(a, st) : fwd_tc_d<__half>(a, st);
 }
 
+// ---- forward with library-owned scratch ------------------------------------------------------------
+// The phase table of the forward kernel normally sits in a workspace the caller allocates.  Some
+// callers cannot allocate device memory at the point where they need attention: code running
+// under a framework that forbids allocator calls inside a region (a serving loop with a frozen
+// memory plan, a real-time thread, a plugin whose host hands it fixed input/output buffers
+// only).  For them the table lives in this fixed array, which every GPU that loads the library
+// carries until the process exits.
+constexpr size_t kStaticScratchBytes = POPE_B200_NOALLOC_MAX_SCRATCH;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Host code cannot use g_static_scratch as a pointer: the name is only a handle for the runtime.
+// The device address is looked up once per device, with that device current.
+static cudaError_t static_scratch_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* addr[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    addr[dev] = ptr;
+  }
+  *out = addr[dev];
+  return cudaSuccess;
+}
+
 }  // namespace pope
+
+extern "C" int pope_b200_attn_fwd_noalloc(const PopeAttnArgs* args, void* stream) {
+  using namespace pope;
+  if (!args || args->struct_bytes != sizeof(PopeAttnArgs)) return POPE_ERR_BAD_ARG;
+  const PopeShape& s = args->shape;
+  if (s.B <= 0 || s.H <= 0 || s.Hk <= 0 || s.Nq <= 0 || s.Nk <= 0 || s.d <= 0 || s.r < 0) return POPE_ERR_BAD_ARG;
+  if (s.H % s.Hk != 0 || s.Nq > s.Nk || s.r > s.d || (int64_t)s.B * s.H > 65535) return POPE_ERR_BAD_ARG;
+  if (!args->q || !args->k || !args->v || !args->out || !args->lse) return POPE_ERR_BAD_ARG;
+  if (s.r > 0 && (!args->embed.freqs || !args->embed.bias)) return POPE_ERR_BAD_ARG;
+  if (!attn_fwd_tc_supported(*args)) return POPE_ERR_UNSUPPORTED;
+  if (attn_fwd_tc_workspace(*args) > kStaticScratchBytes) return POPE_ERR_TOO_LARGE;
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+    return POPE_ERR_CUDA;
+  if (major != 10) return POPE_ERR_ARCH;
+  void* scratch = nullptr;
+  if (static_scratch_address(&scratch) != cudaSuccess) return POPE_ERR_CUDA;
+  PopeAttnArgs local = *args;
+  local.workspace = scratch;              // the kernel must get the looked-up address, never the symbol
+  local.workspace_bytes = kStaticScratchBytes;
+  return attn_fwd_tc(local, static_cast<cudaStream_t>(stream)) == cudaSuccess ? POPE_OK : POPE_ERR_CUDA;
+}
