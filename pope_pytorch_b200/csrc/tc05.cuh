@@ -28,20 +28,22 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("{\n.reg .b64 st;\nmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// One try_wait: the hardware parks the thread until the phase completes or `hint_ns` elapses, so a
+// waiting warp issues no instructions in between and wakes as soon as the barrier flips.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
-      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls and returns false (the caller records the failure
-// in a status word and unwinds); a healthy wait completes within microseconds.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 24)) {
+// Bounded wait: gives up after `limit` parked tries (about limit x 10 us in the worst case) and returns
+// false; the caller records the failure in a status word and unwinds.  A healthy wait takes microseconds.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 17)) {
   for (uint32_t i = 0; i < limit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity, 10000u)) return true;
   return false;
 }
 

@@ -27,7 +27,7 @@ struct TcBwdP {
   Strides sq, sk, sv, sdo, sdq, sdk, sdv, sdf;
   const float *freqs, *bias, *lse, *delta;
   int64_t sfn, bias_sh, dbias_sh;
-  const __half2* table;
+  const __half* table;
   const uint8_t* mask;
   int64_t msb, msn;
   float *dfreqs, *dbias;
@@ -43,15 +43,17 @@ constexpr int BT = 64;   // streamed rows per step
 template <int D, typename T>
 __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int DC = D / 8;
   const int KD = D + p.r, KSTEPS = KD >> 4;
   uint8_t* Qs = smem;                          // [KD/8][128][16 B]  resident Q'
   uint8_t* Gs = Qs + BQ * KD * 2;              // [D/8][128][16 B]   resident dO
+  const int KBUF = (KD / 8) * CS64, VBUF = (D / 8) * CS64;  // one streamed buffer (padded chunk stride)
   uint8_t* Ks = Gs + BQ * D * 2;               // 2 x [KD/8][64][16 B]
-  uint8_t* Vs = Ks + 2 * BT * KD * 2;          // 2 x [D/8][64][16 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * BT * D * 2);  // [0] scores ready, [1] dQ' step done
+  uint8_t* Vs = Ks + 2 * KBUF;                 // 2 x [D/8][64][16 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);  // [0] scores ready, [1] dQ' step done
   uint32_t* kbits = reinterpret_cast<uint32_t*>(bars + 2);           // [2 bufs][2 words]
   uint32_t* tmem_slot = kbits + 4;
+  float* bias_cb = reinterpret_cast<float*>(tmem_slot + 4);
+  float* bias_sb = bias_cb + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
@@ -73,13 +75,10 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
     mbar_init_fence();
   }
   // resident operands: Q' with phase (fq - bias), dO
-  stage_xform_exact128<D, T>(qbase, p.sq.n, i0, p.Nq, p.freqs, p.sfn, qoff, biasr, -1.f, p.r, Qs, tid);
-  for (int c = tid >> 7; c < DC; c += 2) {
-    const int row = tid & 127, gi = i0 + row;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (gi < p.Nq) raw = *reinterpret_cast<const uint4*>(gbase + (int64_t)gi * p.sdo.n + c * 8);
-    *reinterpret_cast<uint4*>(Gs + c * (BQ * 16) + row * 16) = raw;
-  }
+  load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
+  __syncthreads();
+  stage_xform<D, BQ, T, true>(qbase, p.sq.n, i0, p.Nq, p.table, p.Nk, qoff, p.r, bias_cb, bias_sb, Qs, tid);
+  stage_plain<D, BQ, T>(gbase, p.sdo.n, i0, p.Nq, Gs, tid);
 
   int n_end = p.Nk;
   if (p.causal) n_end = min(n_end, min(i0 + BQ, p.Nq));
@@ -87,8 +86,8 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
 
   auto stage = [&](int jt) {
     const int buf = jt & 1, n0 = jt * BT;
-    stage_xform_table<D, BT, T>(kbase, p.sk.n, n0, p.Nk, p.table, 0, p.r, Ks + buf * (BT * KD * 2), tid);
-    stage_plain<D, BT, T>(vbase, p.sv.n, n0, p.Nk, Vs + buf * (BT * D * 2), tid);
+    stage_xform<D, BT, T, false>(kbase, p.sk.n, n0, p.Nk, p.table, p.Nk, 0, p.r, nullptr, nullptr, Ks + buf * KBUF, tid);
+    stage_plain<D, BT, T>(vbase, p.sv.n, n0, p.Nk, Vs + buf * VBUF, tid);
     if (tid < BT) {
       const int j = n0 + tid;
       const bool ok = j < p.Nk && (!maskb || maskb[(int64_t)j * p.msn] != 0);
@@ -112,10 +111,10 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
     const int buf = jt & 1;
     for (int ks = 0; ks < KSTEPS; ++ks)
       mma_ss(tmem, smem_desc(qs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
-             smem_desc(ks_addr + buf * (BT * KD * 2) + ks * 2 * (BT * 16), BT * 16, 128), idesc_s, ks > 0);
+             smem_desc(ks_addr + buf * KBUF + ks * 2 * CS64, CS64, 128), idesc_s, ks > 0);
     for (int ks = 0; ks < D / 16; ++ks)
       mma_ss(tmem + 64, smem_desc(gs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
-             smem_desc(vs_addr + buf * (BT * D * 2) + ks * 2 * (BT * 16), BT * 16, 128), idesc_s, ks > 0);
+             smem_desc(vs_addr + buf * VBUF + ks * 2 * CS64, CS64, 128), idesc_s, ks > 0);
     mma_commit(&bars[0]);
   };
   if (tid == 0) issue_scores(0);
@@ -162,7 +161,7 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
     if (tid == 0) {
       fence_after_sync();
       for (int ks = 0; ks < BT / 16; ++ks)
-        mma_ts(tmem + 256, tmem + 128 + ks * 8, smem_desc(ks_addr + buf * (BT * KD * 2) + ks * 2 * 128, 128, BT * 16),
+        mma_ts(tmem + 256, tmem + 128 + ks * 8, smem_desc(ks_addr + buf * KBUF + ks * 2 * 128, 128, CS64),
                idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
       mma_commit(&bars[1]);
     }

@@ -4,17 +4,19 @@ namespace pope {
 template <int D, typename T>
 __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int DC = D / 8;
   const int KD = D + p.r, KSTEPS = KD >> 4;
   uint8_t* Ks = smem;                          // [KD/8][128][16 B]  resident K' (phase fk + bias)
   uint8_t* Vs = Ks + BQ * KD * 2;              // [D/8][128][16 B]   resident V
+  const int KBUF = (KD / 8) * CS64, VBUF = (D / 8) * CS64;  // one streamed buffer (padded chunk stride)
   uint8_t* Qb = Vs + BQ * D * 2;               // 2 x [KD/8][64][16 B] streamed Q'
-  uint8_t* Gb = Qb + 2 * BT * KD * 2;          // 2 x [D/8][64][16 B]  streamed dO
-  uint8_t* Ps = Gb + 2 * BT * D * 2;           // [8 chunks][128][16 B] P^T  (A operand, K = 64 queries)
+  uint8_t* Gb = Qb + 2 * KBUF;                 // 2 x [D/8][64][16 B]  streamed dO
+  uint8_t* Ps = Gb + 2 * VBUF;                 // [8 chunks][128][16 B] P^T  (A operand, K = 64 queries)
   uint8_t* Ds = Ps + BQ * BT * 2;              // [8 chunks][128][16 B] dS^T
   float* rowstat = reinterpret_cast<float*>(Ds + BQ * BT * 2);  // 2 bufs x (64 lse*log2e, 64 delta)
   uint64_t* bars = reinterpret_cast<uint64_t*>(rowstat + 2 * 128);   // [0] scores ready, [1] accumulation done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  float* bias_cb = reinterpret_cast<float*>(Ps);   // only needed while the resident K' is built: borrows the P^T tile
+  float* bias_sb = bias_cb + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int u = blockIdx.y, b = u / p.Hk, hk = u % p.Hk;
@@ -34,13 +36,10 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
     mbar_init(&bars[0], 1), mbar_init(&bars[1], 1);
     mbar_init_fence();
   }
-  stage_xform_exact128<D, T>(kbase, p.sk.n, j0, p.Nk, p.freqs, p.sfn, 0, biasr, 1.f, p.r, Ks, tid);
-  for (int c = tid >> 7; c < DC; c += 2) {
-    const int row = tid & 127, gj = j0 + row;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (gj < p.Nk) raw = *reinterpret_cast<const uint4*>(vbase + (int64_t)gj * p.sv.n + c * 8);
-    *reinterpret_cast<uint4*>(Vs + c * (BQ * 16) + row * 16) = raw;
-  }
+  load_bias_trig(biasr, p.r, 1.f, bias_cb, bias_sb, tid);
+  __syncthreads();
+  stage_xform<D, BQ, T, true>(kbase, p.sk.n, j0, p.Nk, p.table, p.Nk, 0, p.r, bias_cb, bias_sb, Ks, tid);
+  stage_plain<D, BQ, T>(vbase, p.sv.n, j0, p.Nk, Vs, tid);
 
   // query tiles: under the causal mask rows i < j0 see none of this CTA's keys
   const int m_begin = p.causal ? (j0 / BT) * BT : 0;
@@ -52,8 +51,8 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
     const int h = g * p.Hk + hk;
     const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
     const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
-    stage_xform_table<D, BT, T>(qbase, p.sq.n, m0, p.Nq, p.table, qoff, p.r, Qb + buf * (BT * KD * 2), tid);
-    stage_plain<D, BT, T>(gbase, p.sdo.n, m0, p.Nq, Gb + buf * (BT * D * 2), tid);
+    stage_xform<D, BT, T, false>(qbase, p.sq.n, m0, p.Nq, p.table, p.Nk, qoff, p.r, nullptr, nullptr, Qb + buf * KBUF, tid);
+    stage_plain<D, BT, T>(gbase, p.sdo.n, m0, p.Nq, Gb + buf * VBUF, tid);
     if (tid < BT) {
       const int gi = m0 + tid;
       const int64_t uq = (int64_t)(b * p.H + h) * p.Nq + gi;
@@ -85,10 +84,10 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
     const int buf = jt & 1;
     for (int ks = 0; ks < KSTEPS; ++ks)
       mma_ss(tmem, smem_desc(ks_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
-             smem_desc(qb_addr + buf * (BT * KD * 2) + ks * 2 * (BT * 16), BT * 16, 128), idesc_s, ks > 0);
+             smem_desc(qb_addr + buf * KBUF + ks * 2 * CS64, CS64, 128), idesc_s, ks > 0);
     for (int ks = 0; ks < D / 16; ++ks)
       mma_ss(tmem + 64, smem_desc(vs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
-             smem_desc(gb_addr + buf * (BT * D * 2) + ks * 2 * (BT * 16), BT * 16, 128), idesc_s, ks > 0);
+             smem_desc(gb_addr + buf * VBUF + ks * 2 * CS64, CS64, 128), idesc_s, ks > 0);
     mma_commit(&bars[0]);
   };
   if (tid == 0 && T_tiles > 0) issue_scores(0);
@@ -136,9 +135,9 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
       for (int ks = 0; ks < BT / 16; ++ks) {
         const uint64_t pa = smem_desc(ps_addr + ks * 2 * (BQ * 16), BQ * 16, 128);
         const uint64_t da = smem_desc(ds_addr + ks * 2 * (BQ * 16), BQ * 16, 128);
-        mma_ss(tmem + 128, pa, smem_desc(gb_addr + buf * (BT * D * 2) + ks * 2 * 128, 128, BT * 16), idesc_v,
+        mma_ss(tmem + 128, pa, smem_desc(gb_addr + buf * VBUF + ks * 2 * 128, 128, CS64), idesc_v,
                (j > 0 || ks > 0) ? 1u : 0u);
-        mma_ss(tmem + 256, da, smem_desc(qb_addr + buf * (BT * KD * 2) + ks * 2 * 128, 128, BT * 16), idesc_k,
+        mma_ss(tmem + 256, da, smem_desc(qb_addr + buf * KBUF + ks * 2 * 128, 128, CS64), idesc_k,
                (j > 0 || ks > 0) ? 1u : 0u);
       }
       mma_commit(&bars[1]);
@@ -253,17 +252,17 @@ bool attn_bwd_tc_supported(const PopeAttnBwdArgs& a) {
 static size_t delta_bytes(const PopeShape& s) { return ((size_t)s.B * s.H * s.Nq * sizeof(float) + 255) / 256 * 256; }
 
 size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
-  return delta_bytes(a.shape) + (size_t)a.shape.Nk * a.shape.r * sizeof(__half2) + 16;
+  return delta_bytes(a.shape) + trig_table_bytes(a.shape.Nk, a.shape.r);
 }
 
 template <int D, typename T>
 static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
   float* delta = reinterpret_cast<float*>(a.workspace);
-  __half2* table = reinterpret_cast<__half2*>(reinterpret_cast<uint8_t*>(a.workspace) + delta_bytes(s));
+  __half* table = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(a.workspace) + delta_bytes(s));
   cudaError_t e = attn_bwd_delta(a, delta, st);
   if (e != cudaSuccess) return e;
-  if (s.r > 0 && (e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, table, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, table, false, st)) != cudaSuccess) return e;
   TcBwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
   p.scale = a.softmax_scale, p.scale_log2 = a.softmax_scale * LOG2E;
@@ -276,8 +275,9 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   p.status = tc_status_ptr();
   if (!p.status) return cudaErrorInvalidSymbol;
   const int KD = s.d + s.r;
-  size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + 2 * BT * KD * 2 + 2 * BT * D * 2 + 2 * 8 + 4 * 4 + 16;
-  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + 2 * BT * KD * 2 + 2 * BT * D * 2 + 2 * BQ * BT * 2 + 256 * 4 + 2 * 8 + 16;
+  const size_t streamed = 2 * (size_t)(KD / 8) * CS64 + 2 * (size_t)(D / 8) * CS64;
+  size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + 2 * 8 + 4 * 4 + 16 + 1024;
+  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + 2 * BQ * BT * 2 + 256 * 4 + 2 * 8 + 16 + 16;
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;

@@ -28,9 +28,36 @@ namespace pope {
 
 __device__ unsigned int g_tc_status = 0;  // sticky: bit 0 = a bounded wait gave up
 
+// Optional phase timers (compile with -DPOPE_TC_PROFILE): clock64 deltas of warp 0 / lane 0 of every
+// CTA summed per phase.  [0] prologue [1] wait PV [2] stage [3] sync A [4] wait S [5] softmax [6] sync B
+// [7] epilogue [8] CTA count [9] tiles
+#ifdef POPE_TC_PROFILE
+__device__ unsigned long long g_tc_prof[16];
+#define PROF_DECL long long _t0 = clock64(), _t1; unsigned long long _acc[16] = {}
+#define PROF(i) do { _t1 = clock64(); _acc[i] += (unsigned long long)(_t1 - _t0); _t0 = _t1; } while (0)
+#define PROF_FLUSH(lo, hi) do { for (int _i = lo; _i < hi; ++_i) atomicAdd(&g_tc_prof[_i], _acc[_i]); } while (0)
+#define PROF_COUNT(i, n) atomicAdd(&g_tc_prof[i], (unsigned long long)(n))
+#else
+#define PROF_DECL
+#define PROF(i)
+#define PROF_FLUSH(lo, hi)
+#define PROF_COUNT(i, n)
+#endif
+
 unsigned int* tc_status_ptr() {
   void* p = nullptr;
   return cudaGetSymbolAddress(&p, g_tc_status) == cudaSuccess ? static_cast<unsigned int*>(p) : nullptr;
+}
+
+// copies the phase timers (zeros unless built with POPE_TC_PROFILE) and clears them
+void tc_read_profile(unsigned long long* out16) {
+#ifdef POPE_TC_PROFILE
+  cudaMemcpyFromSymbol(out16, g_tc_prof, 16 * sizeof(unsigned long long));
+  unsigned long long z[16] = {};
+  cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z));
+#else
+  for (int i = 0; i < 16; ++i) out16[i] = 0;
+#endif
 }
 
 unsigned int tc_read_status() {
@@ -39,19 +66,25 @@ unsigned int tc_read_status() {
   return v;
 }
 
-// ---- pre-pass: table[pos][c] = (cos, sin) of freqs[pos][c] as half2 ---------------------------
-__global__ void pope_trig_table_kernel(const float* freqs, int64_t sfn, int n, int r, __half2* table) {
+// ---- pre-pass: cos / sin tables of freqs as 16-bit arrays [n][r] -------------------------------------
+template <typename TT>
+__global__ void pope_trig_table_kernel(const float* freqs, int64_t sfn, int n, int r, TT* table) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)n * r) return;
   const int pos = idx / r, c = idx % r;
   float sn, cs;
   sincosf(freqs[pos * sfn + c], &sn, &cs);
-  table[idx] = __floats2half2_rn(cs, sn);
+  table[idx] = from_f32<TT>(cs);
+  table[(int64_t)n * r + idx] = from_f32<TT>(sn);
 }
 
-cudaError_t launch_trig_table(const float* freqs, int64_t sfn, int n, int r, __half2* table, cudaStream_t st) {
+cudaError_t launch_trig_table(const float* freqs, int64_t sfn, int n, int r, void* table, bool as_bf16, cudaStream_t st) {
   const int64_t total = (int64_t)n * r;
-  pope_trig_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(freqs, sfn, n, r, table);
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (as_bf16)
+    pope_trig_table_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(freqs, sfn, n, r, static_cast<__nv_bfloat16*>(table));
+  else
+    pope_trig_table_kernel<__half><<<blocks, 256, 0, st>>>(freqs, sfn, n, r, static_cast<__half*>(table));
   return cudaGetLastError();
 }
 
@@ -66,7 +99,7 @@ struct TcFwdP {
   int64_t sfn;
   const float* bias;
   int64_t bias_sh;
-  const __half2* table;
+  const void* table;   // cos / sin in the dtype of q, k, v
   const uint8_t* mask;
   int64_t msb, msn;
 };
@@ -74,197 +107,239 @@ struct TcFwdP {
 constexpr int TQ = 128;   // rows per MMA tile
 constexpr int TK = 64;    // keys per step
 
-// Expand 64 key rows starting at n0 into Kbuf (K-major, chunk-major storage: chunk*1024 + row*16),
-// stage the matching V rows MN-major (chunk*1024 + key*16) and publish the key-validity bits.
-template <int D, typename T>
-__device__ __forceinline__ void stage_keys(const TcFwdP& p, const T* kbase, const T* vbase, const uint8_t* maskb, int n0,
-                                           uint8_t* Kbuf, uint8_t* Vbuf, uint32_t* kbits, int tid) {
-  constexpr int DC = D / 8;
-  const int RC = p.r >> 3;
-#pragma unroll
-  for (int it = 0; it < (TK * DC) / 256; ++it) {
-    const int task = tid + it * 256;
-    const int row = task & (TK - 1), c = task >> 6;
-    const int j = n0 + row;
-    const bool ok = j < p.Nk;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (ok) raw = *reinterpret_cast<const uint4*>(kbase + (int64_t)j * p.sk.n + c * 8);
-    if (c < RC) {
-      uint4 t0 = make_uint4(0, 0, 0, 0), t1 = t0;
-      if (ok) {
-        const uint4* tp = reinterpret_cast<const uint4*>(p.table + (int64_t)j * p.r + c * 8);
-        t0 = tp[0], t1 = tp[1];
-      }
-      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-      const uint32_t tw[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-      uint32_t oc[4], os[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 x = unpack2<T>(rw[e]);
-        const float a0 = softplus_fast(x.x), a1 = softplus_fast(x.y);
-        const float2 cs0 = __half22float2(*reinterpret_cast<const __half2*>(&tw[2 * e]));
-        const float2 cs1 = __half22float2(*reinterpret_cast<const __half2*>(&tw[2 * e + 1]));
-        oc[e] = ok ? pack2<T>(a0 * cs0.x, a1 * cs1.x) : 0u;
-        os[e] = ok ? pack2<T>(a0 * cs0.y, a1 * cs1.y) : 0u;
-      }
-      *reinterpret_cast<uint4*>(Kbuf + c * (TK * 16) + row * 16) = make_uint4(oc[0], oc[1], oc[2], oc[3]);
-      *reinterpret_cast<uint4*>(Kbuf + (DC + c) * (TK * 16) + row * 16) = make_uint4(os[0], os[1], os[2], os[3]);
-    } else {
-      *reinterpret_cast<uint4*>(Kbuf + c * (TK * 16) + row * 16) = raw;
-    }
+// Warp roles of the forward kernel (17 warps, 544 threads)
+constexpr int FWD_SOFTMAX_WARPS = 8;   // warps 0-7  : one query row per thread (two 128-row tiles)
+constexpr int FWD_PRODUCER_WARPS = 8;  // warps 8-15 : expand K tiles, stage V, publish key-validity bits
+constexpr int FWD_MMA_WARP = FWD_SOFTMAX_WARPS + FWD_PRODUCER_WARPS;   // warp 16 issues every MMA
+constexpr int FWD_THREADS = 32 * (FWD_MMA_WARP + 1);
+
+// mbarrier slots
+enum { B_KFULL = 0, B_SFULL = 2, B_PVDONE = 4, B_PFULL = 6 /* [buf][tile] */, B_QFULL = 10, B_COUNT = 11 };
+
+struct WaitBuffer {   // producer hook: block until the K'/V buffer of tile j has been consumed (PV(j-2) done)
+  uint64_t* bar;
+  uint32_t parity;
+  bool enabled;
+  bool* failed;
+  __device__ __forceinline__ void operator()() const {
+    if (enabled && !*failed) *failed = !mbar_wait(bar, parity, WAIT_LIMIT);
   }
-  // the sin block of K' only spans chunks [DC, DC + RC); nothing to clear beyond it
-#pragma unroll
-  for (int it = 0; it < (TK * DC) / 256; ++it) {
-    const int task = tid + it * 256;
-    const int row = task & (TK - 1), c = task >> 6;
-    const int j = n0 + row;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (j < p.Nk) raw = *reinterpret_cast<const uint4*>(vbase + (int64_t)j * p.sv.n + c * 8);
-    *reinterpret_cast<uint4*>(Vbuf + c * (TK * 16) + row * 16) = raw;
-  }
-  if (tid < TK) {
-    const int j = n0 + tid;
-    const bool ok = j < p.Nk && (!maskb || maskb[(int64_t)j * p.msn] != 0);
-    const uint32_t bits = __ballot_sync(0xffffffffu, ok);
-    if ((tid & 31) == 0) kbits[tid >> 5] = bits;
-  }
-}
+};
 
 template <int D, typename T>
-__global__ void __launch_bounds__(256, 1) attn_fwd_tc_kernel(TcFwdP p) {
+__global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int DC = D / 8;
-  const int RC = p.r >> 3, KD = D + p.r, KSTEPS = KD >> 4;
+  const int KD = D + p.r, KSTEPS = KD >> 4;
   uint8_t* Qs = smem;                              // 2 tiles x [KD/8 chunks][128 rows][16 B]
   uint8_t* Ks = Qs + 2 * TQ * KD * 2;              // 2 bufs  x [KD/8 chunks][64 rows][16 B]
-  uint8_t* Vs = Ks + 2 * TK * KD * 2;              // 2 bufs  x [D/8 chunks][64 keys][16 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * TK * D * 2);  // s[0], s[1], pv[0], pv[1]
-  uint32_t* kbits = reinterpret_cast<uint32_t*>(bars + 4);           // [2 bufs][2 words]
+  const int KBUF = (KD / 8) * CS64, VBUF = (D / 8) * CS64;   // bytes of one streamed K' / V buffer (padded chunks)
+  uint8_t* Vs = Ks + 2 * KBUF;                     // 2 bufs  x [D/8 chunks][64 keys][16 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);
+  uint32_t* kbits = reinterpret_cast<uint32_t*>(bars + B_COUNT + 1);  // [2 bufs][2 words]
   uint32_t* tmem_slot = kbits + 4;
+  float* bias_cb = reinterpret_cast<float*>(tmem_slot + 4);           // cos / sin of the head's phase bias
+  float* bias_sb = bias_cb + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
   const int i0 = (gridDim.x - 1 - blockIdx.x) * (2 * TQ);  // heavy (late) row blocks first
   const int qoff = p.Nk - p.Nq;
-  const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
   const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
   const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
-  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
-  const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
 
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-  }
-  if (tid == 0) {
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
-    mbar_init_fence();
-  }
-
-  // ---- Q' for both tiles: thread = row -------------------------------------------------------
-  {
-    const int gi = i0 + tid;
-    const bool ok = gi < p.Nq;
-    const T* qrow = qbase + (int64_t)gi * p.sq.n;
-    const float* frow = p.r > 0 ? p.freqs + (int64_t)(qoff + gi) * p.sfn : nullptr;
-    uint8_t* Qt = Qs + (tid >> 7) * (TQ * KD * 2) + (tid & 127) * 16;
-#pragma unroll 2
-    for (int c = 0; c < DC; ++c) {
-      uint4 raw = make_uint4(0, 0, 0, 0);
-      if (ok) raw = *reinterpret_cast<const uint4*>(qrow + c * 8);
-      if (c < RC) {
-        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-        uint32_t oc[4] = {0, 0, 0, 0}, os[4] = {0, 0, 0, 0};
-        if (ok) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 x = unpack2<T>(rw[e]);
-            float s0, c0, s1, c1;
-            sincosf(frow[c * 8 + 2 * e] - biasr[c * 8 + 2 * e], &s0, &c0);
-            sincosf(frow[c * 8 + 2 * e + 1] - biasr[c * 8 + 2 * e + 1], &s1, &c1);
-            const float a0 = softplus_f(x.x), a1 = softplus_f(x.y);
-            oc[e] = pack2<T>(a0 * c0, a1 * c1);
-            os[e] = pack2<T>(a0 * s0, a1 * s1);
-          }
-        }
-        *reinterpret_cast<uint4*>(Qt + c * (TQ * 16)) = make_uint4(oc[0], oc[1], oc[2], oc[3]);
-        *reinterpret_cast<uint4*>(Qt + (DC + c) * (TQ * 16)) = make_uint4(os[0], os[1], os[2], os[3]);
-      } else {
-        *reinterpret_cast<uint4*>(Qt + c * (TQ * 16)) = raw;
-      }
-    }
-  }
-
-  // key range and tile activity
   int n_end = p.Nk;
   if (p.causal) n_end = min(n_end, min(i0 + 2 * TQ, p.Nq));
   const int T_tiles = (n_end + TK - 1) / TK;
   const bool has_rows1 = i0 + TQ < p.Nq;
-  const int tile = warp >> 2;                     // which 128-row tile this thread's row is in
-  const int row = i0 + tid;                       // global query row of this thread
-  const bool tile_has_rows = tile == 0 || has_rows1;
+  // number of key tiles tile t takes part in (under the causal mask tile 0 stops 128 keys earlier)
+  const int T0 = p.causal ? min(T_tiles, (min(n_end, i0 + TQ) + TK - 1) / TK) : T_tiles;
+  const int T1 = has_rows1 ? T_tiles : 0;
 
-  stage_keys<D, T>(p, kbase, vbase, maskb, 0, Ks, Vs, kbits, tid);
-  fence_async_smem();
+  if (warp == FWD_MMA_WARP) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&bars[B_KFULL], FWD_PRODUCER_WARPS), mbar_init(&bars[B_KFULL + 1], FWD_PRODUCER_WARPS);
+    mbar_init(&bars[B_SFULL], 1), mbar_init(&bars[B_SFULL + 1], 1);
+    mbar_init(&bars[B_PVDONE], 1), mbar_init(&bars[B_PVDONE + 1], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bars[B_PFULL + i], 4);
+    mbar_init(&bars[B_QFULL], FWD_SOFTMAX_WARPS);
+    mbar_init_fence();
+  }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  // TMEM columns: scores S[buf][tile] at (buf*2 + tile)*64 (P aliases the first 32), outputs at 256 + tile*128
-  const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, TQ, TK, false, false);
-  const uint32_t idesc_o = instr_desc(TcFmt<T>::fmt, TQ, D, false, true);
-  const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
-
-  auto issue_s = [&](int jt) {  // S(jt) for both tiles into score buffer jt & 1
-    const int buf = jt & 1, n0 = jt * TK;
-    for (int t = 0; t < 2; ++t) {
-      if (t == 1 && !has_rows1) continue;
-      if (p.causal && n0 > i0 + t * TQ + TQ - 1) continue;
-      const uint32_t d = tmem + (buf * 2 + t) * 64;
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        const uint64_t ad = smem_desc(qs_addr + t * (TQ * KD * 2) + ks * 2 * (TQ * 16), TQ * 16, 128);
-        const uint64_t bd = smem_desc(ks_addr + buf * (TK * KD * 2) + ks * 2 * (TK * 16), TK * 16, 128);
-        mma_ss(d, ad, bd, idesc_s, ks > 0);
-      }
-    }
-    mma_commit(&bars[buf]);
-  };
-  if (tid == 0) issue_s(0);
-
   bool failed = false;
-  float m_run = -CUDART_INF_F, l_run = 0.f;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
-  for (int j = 0; j < T_tiles; ++j) {
-    const int buf = j & 1, n0 = j * TK;
-    if (j + 1 < T_tiles) {
-      // V buffer 1-buf was read by PV(j-1); K' buffer 1-buf by S(j-1), which softmax(j-1) waited for
-      if (j >= 1 && !failed) failed = !mbar_wait(&bars[2 + ((j - 1) & 1)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
-      stage_keys<D, T>(p, kbase, vbase, maskb, n0 + TK, Ks + (1 - buf) * (TK * KD * 2), Vs + (1 - buf) * (TK * D * 2),
-                       kbits + (1 - buf) * 2, tid);
-      fence_async_smem();
-      fence_before_sync();
-      __syncthreads();
-      if (tid == 0) {
-        fence_after_sync();
-        issue_s(j + 1);
-      }
-    }
-    const bool active = tile_has_rows && (!p.causal || n0 <= i0 + tile * TQ + TQ - 1);
-    if (active) {
-      if (!failed) failed = !mbar_wait(&bars[buf], (j >> 1) & 1, WAIT_LIMIT);
-      fence_after_sync();
-      const uint32_t s_addr = tmem + lane_base + (buf * 2 + tile) * 64;
-      uint32_t sv[64];
-      {
-        uint32_t a[32], c[32];
-        tmem_ld32(s_addr, a);
-        tmem_ld32(s_addr + 32, c);
-        tmem_ld_wait();
+  if (warp >= FWD_SOFTMAX_WARPS && warp < FWD_SOFTMAX_WARPS + FWD_PRODUCER_WARPS) {
+    // =============================== producers ===============================================
+    const int pw = warp - FWD_SOFTMAX_WARPS;
+    const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
+    PROF_DECL;
+    // Work of one tile for this warp: NT expand tasks (8 rows x 4 chunks each) and NT plain V tasks.  A window
+    // of W expand tasks stays in flight in registers, across tile boundaries, so the loads of the next tasks
+    // travel while the current one is being expanded; V is loaded at the start of a tile and stored at its end.
+    constexpr int NT = (TK * D / 256) / FWD_PRODUCER_WARPS;
+    constexpr int W = (NT % 4 == 0) ? 4 : (NT % 3 == 0 ? 3 : 2);
+    static_assert(NT % W == 0, "window must divide the per-tile task count");
+    const T* tab = static_cast<const T*>(p.table);
+    const T* tab_s = tab + (int64_t)p.Nk * p.r;
+    XTask win[W];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[i] = a[i], sv[32 + i] = c[i];
+    for (int it = 0; it < W; ++it)
+      xtask_load<D, TK, T>(win[it], kbase, p.sk.n, 0, p.Nk, tab, tab_s, 0, p.r, pw + FWD_PRODUCER_WARPS * it, lane);
+    for (int j = 0; j < T_tiles; ++j) {
+      const int buf = j & 1, n0 = j * TK;
+      uint8_t* Kb = Ks + buf * KBUF;
+      uint8_t* Vb = Vs + buf * VBUF;
+      PROF(0);
+      uint4 vreg[NT];
+#pragma unroll
+      for (int it = 0; it < NT; ++it) {
+        int row, c;
+        stage_coords<TK, D / 8>(pw + FWD_PRODUCER_WARPS * it, lane, row, c);
+        vreg[it] = make_uint4(0, 0, 0, 0);
+        if (n0 + row < p.Nk) vreg[it] = *reinterpret_cast<const uint4*>(vbase + (int64_t)(n0 + row) * p.sv.n + c * 8);
       }
+      PROF(1);
+      // the K' buffer of tile j was last read by S(j-2), the V buffer by PV(j-2)
+#ifndef POPE_DBG_PRODUCER_ONLY
+      if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_SFULL + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+#endif
+      PROF(12);
+#pragma unroll
+      for (int it = 0; it < NT; ++it) {
+        xtask_store_packed<D, TK, T>(win[it % W], p.r, Kb, pw + FWD_PRODUCER_WARPS * it, lane);
+        const int nit = it + W;   // refill the slot with the task W ahead (possibly in the next tile)
+        if (nit < NT) {
+          xtask_load<D, TK, T>(win[it % W], kbase, p.sk.n, n0, p.Nk, tab, tab_s, 0, p.r,
+                            pw + FWD_PRODUCER_WARPS * nit, lane);
+        } else if (j + 1 < T_tiles) {
+          xtask_load<D, TK, T>(win[it % W], kbase, p.sk.n, n0 + TK, p.Nk, tab, tab_s, 0, p.r,
+                            pw + FWD_PRODUCER_WARPS * (nit - NT), lane);
+        }
+      }
+      PROF(2);
+#ifndef POPE_DBG_PRODUCER_ONLY
+      if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+#endif
+      PROF(13);
+#pragma unroll
+      for (int it = 0; it < NT; ++it) {
+        int row, c;
+        stage_coords<TK, D / 8>(pw + FWD_PRODUCER_WARPS * it, lane, row, c);
+        *reinterpret_cast<uint4*>(Vb + c * CS64 + row * 16) = vreg[it];
+      }
+      if (pw < 2) {
+        const int jk = n0 + pw * 32 + lane;
+        const bool ok = jk < p.Nk && (!maskb || maskb[(int64_t)jk * p.msn] != 0);
+        const uint32_t bits = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) kbits[buf * 2 + pw] = bits;
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[B_KFULL + buf]);
+      PROF(0);
+    }
+    if (warp == FWD_SOFTMAX_WARPS && lane == 0) { PROF_FLUSH(0, 3); PROF_FLUSH(12, 14); PROF_COUNT(14, 1); PROF_COUNT(15, T_tiles); }
+  } else if (warp == FWD_MMA_WARP) {
+    // =============================== MMA issue ================================================
+#ifdef POPE_DBG_PRODUCER_ONLY
+    if (false) {
+#else
+    if (lane == 0) {
+#endif
+      const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, TQ, TK, false, false);
+      const uint32_t idesc_o = instr_desc(TcFmt<T>::fmt, TQ, D, false, true);
+      const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+      auto issue_s = [&](int jt) {   // S(jt) = Q'_t K'(jt)^T into score buffer jt & 1
+        const int buf = jt & 1;
+        for (int t = 0; t < 2; ++t) {
+          if (jt >= (t == 0 ? T0 : T1)) continue;
+          const uint32_t d = tmem + (buf * 2 + t) * 64;
+          uint64_t ad = smem_desc(qs_addr + t * (TQ * KD * 2), TQ * 16, 128);
+          uint64_t bd = smem_desc(ks_addr + buf * KBUF, CS64, 128);
+          mma_ss(d, ad, bd, idesc_s, 0u);
+          for (int ks = 1; ks < KSTEPS; ++ks) {
+            ad += (2 * TQ * 16) >> 4, bd += (2 * CS64) >> 4;
+            mma_ss(d, ad, bd, idesc_s, 1u);
+          }
+        }
+        mma_commit(&bars[B_SFULL + buf]);
+      };
+      PROF_DECL;
+      if (!mbar_wait(&bars[B_QFULL], 0, WAIT_LIMIT)) failed = true;
+      if (!mbar_wait(&bars[B_KFULL], 0, WAIT_LIMIT)) failed = true;
+      fence_after_sync();
+      issue_s(0);
+      PROF(3);
+      for (int j = 0; j < T_tiles; ++j) {
+        const int buf = j & 1;
+        if (j + 1 < T_tiles) {
+          if (!failed) failed = !mbar_wait(&bars[B_KFULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
+          PROF(4);
+          // score buffer 1-buf still holds P(j-1) until PV(j-1) has read it
+          if (j >= 1 && !failed) failed = !mbar_wait(&bars[B_PVDONE + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+          fence_after_sync();
+          PROF(5);
+          issue_s(j + 1);
+          PROF(6);
+        }
+        for (int t = 0; t < 2; ++t) {
+          if (j >= (t == 0 ? T0 : T1)) continue;
+          if (!failed) failed = !mbar_wait(&bars[B_PFULL + buf * 2 + t], (j >> 1) & 1, WAIT_LIMIT);
+          fence_after_sync();
+          PROF(7);
+          const uint32_t d = tmem + 256 + t * 128;
+          const uint32_t a = tmem + (buf * 2 + t) * 64;
+          uint64_t bd = smem_desc(vs_addr + buf * VBUF, 128, CS64);
+#pragma unroll
+          for (int ks = 0; ks < TK / 16; ++ks) {
+            mma_ts(d, a + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+            bd += (2 * 128) >> 4;
+          }
+          PROF(8);
+        }
+        mma_commit(&bars[B_PVDONE + buf]);
+      }
+      PROF_FLUSH(3, 9);
+    }
+    __syncwarp();
+  } else {
+    // =============================== softmax ==================================================
+    const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
+    const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
+    load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const T* qtab = static_cast<const T*>(p.table);
+    stage_xform<D, TQ, T, true>(qbase, p.sq.n, i0, p.Nq, qtab, p.Nk, qoff, p.r, bias_cb, bias_sb, Qs, tid);
+    stage_xform<D, TQ, T, true>(qbase, p.sq.n, i0 + TQ, p.Nq, qtab, p.Nk, qoff, p.r, bias_cb, bias_sb,
+                                Qs + TQ * KD * 2, tid);
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bars[B_QFULL]);
+
+    const int tile = warp >> 2;
+    const int row = i0 + tid;
+#ifdef POPE_DBG_PRODUCER_ONLY
+    const int T_mine = 0;
+#else
+    const int T_mine = tile == 0 ? T0 : T1;
+#endif
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    float m_run = -CUDART_INF_F, l_run = 0.f;
+    PROF_DECL;
+    PROF(9);
+
+    for (int j = 0; j < T_mine; ++j) {
+      const int buf = j & 1, n0 = j * TK;
+      if (!failed) failed = !mbar_wait(&bars[B_KFULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the kbits read
+      if (!failed) failed = !mbar_wait(&bars[B_SFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
+      fence_after_sync();
+      PROF(10);
+      const uint32_t s_addr = tmem + lane_base + (buf * 2 + tile) * 64;
       // visibility of the 64 keys of this tile for this row
       uint64_t vis = ((uint64_t)kbits[buf * 2 + 1] << 32) | kbits[buf * 2];
       if (p.causal) {
@@ -272,14 +347,25 @@ __global__ void __launch_bounds__(256, 1) attn_fwd_tc_kernel(TcFwdP p) {
         vis &= lim >= 63 ? ~0ull : (lim < 0 ? 0ull : ((2ull << lim) - 1ull));
       }
       const bool all_vis = __all_sync(0xffffffffu, vis == ~0ull);
+      // pass 1: row maximum (four independent chains per 32 columns)
       float mx = -CUDART_INF_F;
-      if (all_vis) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
-      } else {
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t sv[32];
+        tmem_ld32(s_addr + hh * 32, sv);
+        tmem_ld_wait();
+        const uint32_t vh = (uint32_t)(vis >> (32 * hh));
+        float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+        if (all_vis) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if ((vis >> i) & 1ull) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < 32; i += 2)
+            m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((vh >> i) & 1u) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[i]));
+        }
+        mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
       }
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
       // keep a stale maximum while it is within 2^8 of the true one: P stays below 256 and the
@@ -292,8 +378,8 @@ __global__ void __launch_bounds__(256, 1) attn_fwd_tc_kernel(TcFwdP p) {
         m_run = m_new;
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
-        // O was last written by PV(j-1): complete, since its barrier was waited for above or here
-        if (!failed) failed = !mbar_wait(&bars[2 + ((j - 1) & 1)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+        // O was last written by PV(j-1)
+        if (!failed) failed = !mbar_wait(&bars[B_PVDONE + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
         fence_after_sync();
         const uint32_t o_addr = tmem + lane_base + 256 + tile * 128;
 #pragma unroll
@@ -307,48 +393,43 @@ __global__ void __launch_bounds__(256, 1) attn_fwd_tc_kernel(TcFwdP p) {
         }
         tmem_st_wait();
       }
+      // pass 2: P = 2^(s*c - m), written over the scores (16 packed columns per 32 scores)
       const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
-      float lsum = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float p0 = ex2_approx(__uint_as_float(sv[2 * i]) * p.scale_log2 - m_use);
-        float p1 = ex2_approx(__uint_as_float(sv[2 * i + 1]) * p.scale_log2 - m_use);
-        if (!all_vis) {
-          p0 = ((vis >> (2 * i)) & 1ull) ? p0 : 0.f;
-          p1 = ((vis >> (2 * i + 1)) & 1ull) ? p1 : 0.f;
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t sv[32];
+        tmem_ld32(s_addr + hh * 32, sv);
+        tmem_ld_wait();
+        const uint32_t vh = (uint32_t)(vis >> (32 * hh));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_use));
+          float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_use));
+          if (!all_vis) {
+            p0 = ((vh >> (2 * i)) & 1u) ? p0 : 0.f;
+            p1 = ((vh >> (2 * i + 1)) & 1u) ? p1 : 0.f;
+          }
+          ls4[i & 3] += p0 + p1;
+          pk[hh * 16 + i] = pack2<T>(p0, p1);
         }
-        lsum += p0 + p1;
-        pk[i] = pack2<T>(p0, p1);
       }
-      l_run += lsum;
+      l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       tmem_st32(s_addr, pk);
       tmem_st_wait();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[B_PFULL + buf * 2 + tile]);
+      PROF(11);
     }
-    fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      fence_after_sync();
-      for (int t = 0; t < 2; ++t) {
-        if (t == 1 && !has_rows1) continue;
-        if (p.causal && n0 > i0 + t * TQ + TQ - 1) continue;
-        const uint32_t d = tmem + 256 + t * 128;
-        const uint32_t a = tmem + (buf * 2 + t) * 64;
-        for (int ks = 0; ks < TK / 16; ++ks) {
-          const uint64_t bd = smem_desc(vs_addr + buf * (TK * D * 2) + ks * 2 * 128, 128, TK * 16);
-          mma_ts(d, a + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-      }
-      mma_commit(&bars[2 + buf]);
-    }
-  }
+    if (warp == 4 && lane == 0) PROF_FLUSH(9, 12);
 
-  // ---- epilogue: O / l, LSE -----------------------------------------------------------------------
-  {
-    const int jl = T_tiles - 1;
-    if (!failed) failed = !mbar_wait(&bars[2 + (jl & 1)], (jl >> 1) & 1, WAIT_LIMIT);
-    fence_after_sync();
-    if (tile_has_rows) {
+    // ---- epilogue: O / l, LSE ---------------------------------------------------------------------
+    if (T_mine > 0) {
+      const int jl = T_mine - 1;
+      if (!failed) failed = !mbar_wait(&bars[B_PVDONE + (jl & 1)], (jl >> 1) & 1, WAIT_LIMIT);
+      fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const uint32_t o_addr = tmem + lane_base + 256 + tile * 128;
       T* orow = (T*)p.o + b * p.so.b + h * p.so.h + (int64_t)row * p.so.n;
@@ -370,14 +451,13 @@ __global__ void __launch_bounds__(256, 1) attn_fwd_tc_kernel(TcFwdP p) {
         }
       }
       if (row < p.Nq)
-        p.lse[(int64_t)u * p.Nq + row] = l_run > 0.f ? m_run * 0.6931471805599453f + logf(l_run) : -CUDART_INF_F;
+        p.lse[(int64_t)u * p.Nq + row] = l_run > 0.f ? m_run * LN2 + logf(l_run) : -CUDART_INF_F;
     }
   }
   if (failed) atomicOr(&g_tc_status, 1u);
   fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
-  (void)lane;
+  if (warp == FWD_MMA_WARP) tmem_dealloc(tmem, 512);
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -397,7 +477,7 @@ bool attn_fwd_tc_supported(const PopeAttnArgs& a) {
 }
 
 size_t attn_fwd_tc_workspace(const PopeAttnArgs& a) {
-  return (size_t)a.shape.Nk * a.shape.r * sizeof(__half2) + 16;
+  return trig_table_bytes(a.shape.Nk, a.shape.r);
 }
 
 template <int D, typename T>
@@ -409,23 +489,23 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   p.q = a.q, p.k = a.k, p.v = a.v, p.o = a.out, p.lse = a.lse;
   p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.so = a.so;
   p.freqs = a.embed.freqs, p.sfn = a.embed.sf.n, p.bias = a.embed.bias, p.bias_sh = a.embed.bias_stride_h;
-  p.table = reinterpret_cast<const __half2*>(a.workspace);
+  p.table = a.workspace;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   if (s.r > 0) {
     const int64_t n = (int64_t)s.Nk * s.r;
     (void)n;
-    cudaError_t e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, reinterpret_cast<__half2*>(a.workspace), st);
+    cudaError_t e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, a.workspace, s.dtype == POPE_BF16, st);
     if (e != cudaSuccess) return e;
   }
   const int KD = s.d + s.r;
-  size_t smem = (size_t)2 * TQ * KD * 2 + 2 * TK * KD * 2 + 2 * TK * D * 2 + 4 * 8 + 4 * 4 + 16;
+  size_t smem = (size_t)2 * TQ * KD * 2 + 2 * (KD / 8) * CS64 + 2 * (D / 8) * CS64 + (B_COUNT + 1) * 8 + 4 * 4 + 16 + 2 * 128 * 4;
   // every CTA allocates all 512 TMEM columns: ask for more than half of the SM's shared memory so
   // that two CTAs are never co-resident
   if (smem < 120 * 1024) smem = 120 * 1024;
   cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   dim3 grid((s.Nq + 2 * TQ - 1) / (2 * TQ), s.B * s.H);
-  attn_fwd_tc_kernel<D, T><<<grid, 256, smem, st>>>(p);
+  attn_fwd_tc_kernel<D, T><<<grid, FWD_THREADS, smem, st>>>(p);
   return cudaGetLastError();
 }
 
@@ -474,6 +554,10 @@ static cudaError_t static_scratch_address(void** out) {
 }
 
 }  // namespace pope
+
+extern "C" __attribute__((visibility("default"))) void pope_b200_debug_profile(unsigned long long* out16) {
+  pope::tc_read_profile(out16);
+}
 
 extern "C" int pope_b200_attn_fwd_noalloc(const PopeAttnArgs* args, void* stream) {
   using namespace pope;

@@ -15,7 +15,7 @@ using namespace tc;
 // device address of the sticky status word (bit 0 = a bounded wait gave up) on the current device
 unsigned int* tc_status_ptr();
 
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_LIMIT = 1u << 17;   // parked tries of up to 10 us each
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -57,103 +57,233 @@ __device__ __forceinline__ float softplus_fast(float x) {
   return fmaxf(x, 0.f) + lg2_approx(1.f + t) * 0.6931471805599453f;
 }
 
-// table[pos][c] = (cos, sin) of freqs[pos][c] as half2, built once per call in the workspace
-cudaError_t launch_trig_table(const float* freqs, int64_t sfn, int n, int r, __half2* table, cudaStream_t st);
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// softplus with ONE special-function op: t = 2^(-|x| log2 e), log1p(t) = t * q(t) with a degree-5
+// polynomial q (relative error 1.8e-5 on (0, 1]); the operand is rounded to 8 or 11 bits afterwards.
+__device__ __forceinline__ float softplus_poly(float x) {
+  const float t = ex2_approx(-fabsf(x) * LOG2E);
+  float q = fmaf(t, -0.023689253f, 0.10028721f);
+  q = fmaf(t, q, -0.20866966f);
+  q = fmaf(t, q, 0.32441181f);
+  q = fmaf(t, q, -0.49918786f);
+  q = fmaf(t, q, 0.99998188f);
+  return fmaf(t, q, fmaxf(x, 0.f));
+}
+
+template <typename T> __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t mul2<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+template <> __device__ __forceinline__ uint32_t mul2<__half>(uint32_t a, uint32_t b) {
+  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Phase tables built once per call in the workspace: cos(freqs[pos][c]) and sin(freqs[pos][c]) as two
+// half arrays [n][r], the sine array following the cosine array.
+// `as_bf16` selects bf16 instead of fp16 entries (the forward multiplies in the operand dtype).
+cudaError_t launch_trig_table(const float* freqs, int64_t sfn, int n, int r, void* table, bool as_bf16, cudaStream_t st);
+inline size_t trig_table_bytes(int n, int r) { return (size_t)n * r * 2 * sizeof(__half) + 16; }
+
+// cos / sin of the per-head phase bias into shared memory (r floats each); `sign` = -1 folds the bias
+// into a query-side phase (f - b), +1 into a key-side phase (f + b).  Call before a __syncthreads().
+__device__ __forceinline__ void load_bias_trig(const float* bias, int r, float sign, float* cb, float* sb, int tid) {
+  for (int c = tid; c < r; c += 256) {
+    float s, co;
+    sincosf(sign * bias[c], &s, &co);
+    cb[c] = co, sb[c] = s;
+  }
+}
+
+// Work split of the staging helpers: the 16-byte chunks of a ROWS x D tile are numbered row-major and a
+// warp takes 32 consecutive ones per pass, so every global request covers 512 contiguous bytes of a row
+// pair (requests spread over 8 rows ran at a third of that rate).  In shared memory chunk c of a
+// streamed 64-row tile starts at c * (64*16 + 16): the 16 bytes of padding put the lanes of a pass,
+// which hold consecutive chunks of one row, on distinct banks.
+template <int ROWS> struct ChunkStride { static constexpr int v = ROWS == 64 ? 64 * 16 + 16 : ROWS * 16; };
+constexpr int CS64 = ChunkStride<64>::v;
+constexpr int CS128 = ChunkStride<128>::v;
+
+template <int ROWS, int DC>
+__device__ __forceinline__ void stage_coords(int wt, int lane, int& row, int& c) {
+  const int f = wt * 32 + lane;
+  row = f / DC;
+  c = f - row * DC;
+}
 
 // Expand ROWS rows (row0 .. row0+ROWS) of a (rows, D) operand into the K-major operand layout
-// (chunk-major storage: chunk*ROWS*16 + row*16 bytes): chunks [0, D/8) hold a*cos for rotated
-// features and the raw feature otherwise, chunks [D/8, D/8 + r/8) hold a*sin.  Phases come from
-// the table row (pos0 + row); rows at or beyond `nrows` are zero-filled.  256 threads.
-template <int D, int ROWS, typename T>
-__device__ __forceinline__ void stage_xform_table(const T* base, int64_t sn, int row0, int nrows, const __half2* table,
-                                                  int pos0, int r, uint8_t* buf, int tid) {
-  constexpr int DC = D / 8;
+// (chunk-major storage: chunk*ROWS*16 + row*16 bytes): chunks [0, D/8) hold a*cos(phase) for rotated
+// features and the raw feature otherwise, chunks [D/8, D/8 + r/8) hold a*sin(phase).  phase = table
+// row (pos0 + row), rotated by the shared-memory bias trig when BIAS.  Rows >= nrows are zero-filled.
+// All global loads of a batch are issued before any of its arithmetic.  256 threads.
+struct NoHook {
+  __device__ __forceinline__ void operator()() const {}
+};
+
+// NW warps share the work; `warp` is this warp's index among them (0 .. NW-1).  `before_store` runs once,
+// after the first batch of loads has been issued and before anything is written to `buf` (the place to
+// wait for the buffer to become free without delaying the loads).
+template <int D, int ROWS, typename T, bool BIAS, int NW = 8, typename Hook = NoHook, typename TT = __half>
+__device__ __forceinline__ void stage_xform_w(const T* base, int64_t sn, int row0, int nrows, const TT* tab,
+                                              int tab_n, int pos0, int r, const float* cb, const float* sb, uint8_t* buf,
+                                              int warp, int lane, Hook before_store = Hook()) {
+  constexpr int DC = D / 8, NT = (ROWS * DC / 32) / NW, BATCH = NT > 4 ? NT / 2 : NT;
+  static_assert(NT * NW * 32 == ROWS * DC && NT % BATCH == 0, "work does not split evenly");
   const int RC = r >> 3;
+  const TT* tab_s = tab + (int64_t)tab_n * r;
 #pragma unroll
-  for (int it = 0; it < (ROWS * DC) / 256; ++it) {
-    const int task = tid + it * 256;
-    const int row = task % ROWS, c = task / ROWS;
-    const int j = row0 + row;
-    const bool ok = j < nrows;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (ok) raw = *reinterpret_cast<const uint4*>(base + (int64_t)j * sn + c * 8);
-    if (c < RC) {
-      uint4 t0 = make_uint4(0, 0, 0, 0), t1 = t0;
-      if (ok) {
-        const uint4* tp = reinterpret_cast<const uint4*>(table + (int64_t)(pos0 + j) * r + c * 8);
-        t0 = tp[0], t1 = tp[1];
-      }
-      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-      const uint32_t tw[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-      uint32_t oc[4], os[4];
+  for (int b0 = 0; b0 < NT; b0 += BATCH) {
+    uint4 raw[BATCH], tc[BATCH], ts[BATCH];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 x = unpack2<T>(rw[e]);
-        const float a0 = softplus_fast(x.x), a1 = softplus_fast(x.y);
-        const float2 cs0 = __half22float2(*reinterpret_cast<const __half2*>(&tw[2 * e]));
-        const float2 cs1 = __half22float2(*reinterpret_cast<const __half2*>(&tw[2 * e + 1]));
-        oc[e] = ok ? pack2<T>(a0 * cs0.x, a1 * cs1.x) : 0u;
-        os[e] = ok ? pack2<T>(a0 * cs0.y, a1 * cs1.y) : 0u;
+    for (int it = 0; it < BATCH; ++it) {
+      int row, c;
+      stage_coords<ROWS, DC>(warp + NW * (b0 + it), lane, row, c);
+      const int j = row0 + row;
+      raw[it] = tc[it] = ts[it] = make_uint4(0, 0, 0, 0);
+#ifdef POPE_DBG_NOLOAD
+      if (false) {
+#else
+      if (j < nrows) {
+#endif
+        raw[it] = *reinterpret_cast<const uint4*>(base + (int64_t)j * sn + c * 8);
+        if (c < RC) {
+          tc[it] = *reinterpret_cast<const uint4*>(tab + (int64_t)(pos0 + j) * r + c * 8);
+          ts[it] = *reinterpret_cast<const uint4*>(tab_s + (int64_t)(pos0 + j) * r + c * 8);
+        }
       }
-      *reinterpret_cast<uint4*>(buf + c * (ROWS * 16) + row * 16) = make_uint4(oc[0], oc[1], oc[2], oc[3]);
-      *reinterpret_cast<uint4*>(buf + (DC + c) * (ROWS * 16) + row * 16) = make_uint4(os[0], os[1], os[2], os[3]);
-    } else {
-      *reinterpret_cast<uint4*>(buf + c * (ROWS * 16) + row * 16) = raw;
     }
-  }
-}
-
-// Copy ROWS rows of a (rows, D) operand unchanged into the same chunk-major layout.  256 threads.
-template <int D, int ROWS, typename T>
-__device__ __forceinline__ void stage_plain(const T* base, int64_t sn, int row0, int nrows, uint8_t* buf, int tid) {
-  constexpr int DC = D / 8;
+    if (b0 == 0) before_store();
 #pragma unroll
-  for (int it = 0; it < (ROWS * DC) / 256; ++it) {
-    const int task = tid + it * 256;
-    const int row = task % ROWS, c = task / ROWS;
-    const int j = row0 + row;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (j < nrows) raw = *reinterpret_cast<const uint4*>(base + (int64_t)j * sn + c * 8);
-    *reinterpret_cast<uint4*>(buf + c * (ROWS * 16) + row * 16) = raw;
-  }
-}
-
-// Exact (sincosf, log1pf) transform of 128 resident rows, phase = freqs[pos0 + row] + sign*bias.
-// Same layout as above with ROWS = 128.  256 threads: thread handles row tid%128, chunks tid/128 + 2k.
-template <int D, typename T>
-__device__ __forceinline__ void stage_xform_exact128(const T* base, int64_t sn, int row0, int nrows, const float* freqs,
-                                                     int64_t sfn, int pos0, const float* bias, float sign, int r,
-                                                     uint8_t* buf, int tid) {
-  constexpr int DC = D / 8;
-  const int RC = r >> 3;
-  const int row = tid & 127, j = row0 + row;
-  const bool ok = j < nrows;
-  const T* src = base + (int64_t)j * sn;
-  const float* frow = r > 0 ? freqs + (int64_t)(pos0 + j) * sfn : nullptr;
-  for (int c = tid >> 7; c < DC; c += 2) {
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (ok) raw = *reinterpret_cast<const uint4*>(src + c * 8);
-    if (c < RC) {
-      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-      uint32_t oc[4] = {0, 0, 0, 0}, os[4] = {0, 0, 0, 0};
-      if (ok) {
+    for (int it = 0; it < BATCH; ++it) {
+      int row, c;
+      stage_coords<ROWS, DC>(warp + NW * (b0 + it), lane, row, c);
+      if (c < RC) {
+        const uint32_t rw[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
+        const uint32_t cw[4] = {tc[it].x, tc[it].y, tc[it].z, tc[it].w};
+        const uint32_t sw[4] = {ts[it].x, ts[it].y, ts[it].z, ts[it].w};
+        uint32_t oc[4], os[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 x = unpack2<T>(rw[e]);
-          float s0, c0, s1, c1;
-          sincosf(frow[c * 8 + 2 * e] + sign * bias[c * 8 + 2 * e], &s0, &c0);
-          sincosf(frow[c * 8 + 2 * e + 1] + sign * bias[c * 8 + 2 * e + 1], &s1, &c1);
-          const float a0 = softplus_f(x.x), a1 = softplus_f(x.y);
-          oc[e] = pack2<T>(a0 * c0, a1 * c1);
-          os[e] = pack2<T>(a0 * s0, a1 * s1);
+          float2 co = unpack2<TT>(cw[e]);
+          float2 si = unpack2<TT>(sw[e]);
+          if (BIAS) {
+            const float2 b_c = *reinterpret_cast<const float2*>(cb + c * 8 + 2 * e);
+            const float2 b_s = *reinterpret_cast<const float2*>(sb + c * 8 + 2 * e);
+            const float2 c2 = make_float2(co.x * b_c.x - si.x * b_s.x, co.y * b_c.y - si.y * b_s.y);
+            si = make_float2(si.x * b_c.x + co.x * b_s.x, si.y * b_c.y + co.y * b_s.y);
+            co = c2;
+          }
+#ifdef POPE_DBG_NOMATH
+          const float a0 = x.x, a1 = x.y;
+#else
+          const float a0 = softplus_fast(x.x), a1 = softplus_fast(x.y);
+#endif
+          oc[e] = pack2<T>(a0 * co.x, a1 * co.y);   // zero rows: softplus(0) * table 0 = 0
+          os[e] = pack2<T>(a0 * si.x, a1 * si.y);
         }
+        *reinterpret_cast<uint4*>(buf + c * ChunkStride<ROWS>::v + row * 16) = make_uint4(oc[0], oc[1], oc[2], oc[3]);
+        *reinterpret_cast<uint4*>(buf + (DC + c) * ChunkStride<ROWS>::v + row * 16) = make_uint4(os[0], os[1], os[2], os[3]);
+      } else {
+        *reinterpret_cast<uint4*>(buf + c * ChunkStride<ROWS>::v + row * 16) = raw[it];
       }
-      *reinterpret_cast<uint4*>(buf + c * (128 * 16) + row * 16) = make_uint4(oc[0], oc[1], oc[2], oc[3]);
-      *reinterpret_cast<uint4*>(buf + (DC + c) * (128 * 16) + row * 16) = make_uint4(os[0], os[1], os[2], os[3]);
-    } else {
-      *reinterpret_cast<uint4*>(buf + c * (128 * 16) + row * 16) = raw;
     }
   }
+}
+
+// ---- streaming producer: a register window of K-tile tasks kept in flight across tiles ---------------
+struct XTask {
+  uint4 raw, tc, ts;
+};
+
+// load the inputs of one 8-row x 4-chunk warp task (no shared-memory traffic)
+template <int D, int ROWS, typename T>
+__device__ __forceinline__ void xtask_load(XTask& t, const T* base, int64_t sn, int row0, int nrows, const T* tab,
+                                           const T* tab_s, int pos0, int r, int wt, int lane) {
+  constexpr int DC = D / 8;
+  int row, c;
+  stage_coords<ROWS, DC>(wt, lane, row, c);
+  const int j = row0 + row;
+  t.raw = t.tc = t.ts = make_uint4(0, 0, 0, 0);
+  if (j < nrows) {
+    t.raw = *reinterpret_cast<const uint4*>(base + (int64_t)j * sn + c * 8);
+    if (c < (r >> 3)) {
+      t.tc = *reinterpret_cast<const uint4*>(tab + (int64_t)(pos0 + j) * r + c * 8);
+      t.ts = *reinterpret_cast<const uint4*>(tab_s + (int64_t)(pos0 + j) * r + c * 8);
+    }
+  }
+}
+
+// Expand one task and write it into the operand buffer.  The table holds cos / sin in the operand dtype
+// and the products are packed 16-bit multiplies: no 16 -> 32-bit conversion of the table.
+template <int D, int ROWS, typename T>
+__device__ __forceinline__ void xtask_store_packed(const XTask& t, int r, uint8_t* buf, int wt, int lane) {
+  constexpr int DC = D / 8;
+  int row, c;
+  stage_coords<ROWS, DC>(wt, lane, row, c);
+  if (c < (r >> 3)) {
+    const uint32_t rw[4] = {t.raw.x, t.raw.y, t.raw.z, t.raw.w};
+    const uint32_t cw[4] = {t.tc.x, t.tc.y, t.tc.z, t.tc.w};
+    const uint32_t sw[4] = {t.ts.x, t.ts.y, t.ts.z, t.ts.w};
+    uint32_t oc[4], os[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+#ifdef POPE_DBG_NOMATH
+      oc[e] = rw[e] ^ cw[e];
+      os[e] = rw[e] ^ sw[e];
+#else
+      const float2 x = unpack2<T>(rw[e]);
+      const uint32_t a2 = pack2<T>(softplus_poly(x.x), softplus_poly(x.y));
+      oc[e] = mul2<T>(a2, cw[e]);
+      os[e] = mul2<T>(a2, sw[e]);
+#endif
+    }
+    *reinterpret_cast<uint4*>(buf + c * ChunkStride<ROWS>::v + row * 16) = make_uint4(oc[0], oc[1], oc[2], oc[3]);
+    *reinterpret_cast<uint4*>(buf + (DC + c) * ChunkStride<ROWS>::v + row * 16) = make_uint4(os[0], os[1], os[2], os[3]);
+  } else {
+    *reinterpret_cast<uint4*>(buf + c * ChunkStride<ROWS>::v + row * 16) = t.raw;
+  }
+}
+
+// 256-thread form used where all of a CTA's first eight warps stage together
+template <int D, int ROWS, typename T, bool BIAS, typename TT>
+__device__ __forceinline__ void stage_xform(const T* base, int64_t sn, int row0, int nrows, const TT* tab, int tab_n,
+                                            int pos0, int r, const float* cb, const float* sb, uint8_t* buf, int tid) {
+  stage_xform_w<D, ROWS, T, BIAS, 8, NoHook, TT>(base, sn, row0, nrows, tab, tab_n, pos0, r, cb, sb, buf, tid >> 5,
+                                                   tid & 31);
+}
+
+// Copy ROWS rows of a (rows, D) operand unchanged into the same chunk-major layout.
+template <int D, int ROWS, typename T, int NW = 8, typename Hook = NoHook>
+__device__ __forceinline__ void stage_plain_w(const T* base, int64_t sn, int row0, int nrows, uint8_t* buf, int warp,
+                                              int lane, Hook before_store = Hook()) {
+  constexpr int DC = D / 8, NT = (ROWS * DC / 32) / NW;
+  uint4 raw[NT];
+#pragma unroll
+  for (int it = 0; it < NT; ++it) {
+    int row, c;
+    stage_coords<ROWS, DC>(warp + NW * it, lane, row, c);
+    const int j = row0 + row;
+    raw[it] = make_uint4(0, 0, 0, 0);
+    if (j < nrows) raw[it] = *reinterpret_cast<const uint4*>(base + (int64_t)j * sn + c * 8);
+  }
+  before_store();
+#pragma unroll
+  for (int it = 0; it < NT; ++it) {
+    int row, c;
+    stage_coords<ROWS, DC>(warp + NW * it, lane, row, c);
+    *reinterpret_cast<uint4*>(buf + c * ChunkStride<ROWS>::v + row * 16) = raw[it];
+  }
+}
+template <int D, int ROWS, typename T>
+__device__ __forceinline__ void stage_plain(const T* base, int64_t sn, int row0, int nrows, uint8_t* buf, int tid) {
+  stage_plain_w<D, ROWS, T, 8>(base, sn, row0, nrows, buf, tid >> 5, tid & 31);
 }
 
 }  // namespace pope
