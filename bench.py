@@ -242,7 +242,9 @@ def main():
 
     flops_rank = algorithmic_flops(B, H, N, d, r, True)
     value = flops_rank * world / (ms_per_step * 1e-3) / 1e12
-    launches_per_step = 1 + 3 if path == "simt" else int(os.environ.get("POPE_LAUNCHES_PER_STEP", "4"))
+    # kernels of this library per step -- exact-arithmetic path: fwd, delta, dq, dkdv; tensor-core path:
+    # phase table + fwd, then delta + phase table + dq + dkdv
+    launches_per_step = 4 if path == "simt" else 6
 
     # ---- end to end: pinned host buffers -> public API -> results back on the host -------------
     hq, hk, hv, hdo = make_inputs(3000 + rank, w, pin=True)

@@ -27,7 +27,7 @@ struct TcBwdP {
   Strides sq, sk, sv, sdo, sdq, sdk, sdv, sdf;
   const float *freqs, *bias, *lse, *delta;
   int64_t sfn, bias_sh, dbias_sh;
-  const __half* table;
+  const void* table;   // cos / sin tables in the dtype of q, k, v
   const uint8_t* mask;
   int64_t msb, msn;
   float *dfreqs, *dbias;
@@ -40,8 +40,33 @@ constexpr int BT = 64;   // streamed rows per step
 // ================================================================================================
 // dq
 // ================================================================================================
+constexpr int BWD_THREADS = 288;   // warps 0-7 stage and do the elementwise work, warp 8 issues every MMA
+
+// mbarrier slots shared by both backward kernels
+enum { BB_SCORES = 0,    // tcgen05.commit: the two score products of the current tile are in TMEM
+       BB_ACC = 1,       // tcgen05.commit: the accumulation step of the current tile has finished
+       BB_CONSUMED = 2,  // 8 warps: scores copied to registers, the score columns may be overwritten
+       BB_STAGED = 3,    // 8 warps: the next streamed tile is in shared memory
+       BB_GRAD = 4,      // 8 warps: dS (and P) of the current tile are written
+       BB_COUNT = 5 };
+
+struct WaitAcc {   // staging hook: the streamed buffers of tile j+1 were last read by the accumulation of tile j-1
+  uint64_t* bar;
+  uint32_t parity;
+  bool enabled;
+  bool* failed;
+  __device__ __forceinline__ void operator()() const {
+    if (enabled && !*failed) *failed = !mbar_wait(bar, parity, WAIT_LIMIT);
+  }
+};
+
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
 template <int D, typename T>
-__global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int KD = D + p.r, KSTEPS = KD >> 4;
   uint8_t* Qs = smem;                          // [KD/8][128][16 B]  resident Q'
@@ -49,13 +74,14 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
   const int KBUF = (KD / 8) * CS64, VBUF = (D / 8) * CS64;  // one streamed buffer (padded chunk stride)
   uint8_t* Ks = Gs + BQ * D * 2;               // 2 x [KD/8][64][16 B]
   uint8_t* Vs = Ks + 2 * KBUF;                 // 2 x [D/8][64][16 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);  // [0] scores ready, [1] dQ' step done
-  uint32_t* kbits = reinterpret_cast<uint32_t*>(bars + 2);           // [2 bufs][2 words]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);
+  uint32_t* kbits = reinterpret_cast<uint32_t*>(bars + BB_COUNT + 1);  // [2 bufs][2 words]
   uint32_t* tmem_slot = kbits + 4;
   float* bias_cb = reinterpret_cast<float*>(tmem_slot + 4);
   float* bias_sb = bias_cb + 128;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool issuer = warp == 8;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
   const int i0 = (gridDim.x - 1 - blockIdx.x) * BQ;
   const int qoff = p.Nk - p.Nq;
@@ -66,27 +92,24 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
   const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
   const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
 
-  if (warp == 0) {
+  if (issuer) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(&bars[0], 1), mbar_init(&bars[1], 1);
+    mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1);
+    mbar_init(&bars[BB_CONSUMED], 8), mbar_init(&bars[BB_STAGED], 8), mbar_init(&bars[BB_GRAD], 8);
     mbar_init_fence();
   }
-  // resident operands: Q' with phase (fq - bias), dO
-  load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
-  __syncthreads();
-  stage_xform<D, BQ, T, true>(qbase, p.sq.n, i0, p.Nq, p.table, p.Nk, qoff, p.r, bias_cb, bias_sb, Qs, tid);
-  stage_plain<D, BQ, T>(gbase, p.sdo.n, i0, p.Nq, Gs, tid);
-
   int n_end = p.Nk;
   if (p.causal) n_end = min(n_end, min(i0 + BQ, p.Nq));
   const int T_tiles = (n_end + BT - 1) / BT;
+  bool failed = false;
 
-  auto stage = [&](int jt) {
+  auto stage = [&](int jt, WaitAcc hook) {   // workers only
     const int buf = jt & 1, n0 = jt * BT;
-    stage_xform<D, BT, T, false>(kbase, p.sk.n, n0, p.Nk, p.table, p.Nk, 0, p.r, nullptr, nullptr, Ks + buf * KBUF, tid);
+    stage_xform_w<D, BT, T, false, 8, WaitAcc, T>(kbase, p.sk.n, n0, p.Nk, static_cast<const T*>(p.table), p.Nk, 0, p.r, nullptr, nullptr,
+                                               Ks + buf * KBUF, warp, lane, hook);
     stage_plain<D, BT, T>(vbase, p.sv.n, n0, p.Nk, Vs + buf * VBUF, tid);
     if (tid < BT) {
       const int j = n0 + tid;
@@ -96,30 +119,69 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
     }
   };
 
-  stage(0);
-  fence_async_smem();
+  if (!issuer) {
+    // resident operands: Q' with phase (fq - bias), dO; then the first key tile
+    load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    stage_xform<D, BQ, T, true>(qbase, p.sq.n, i0, p.Nq, static_cast<const T*>(p.table), p.Nk, qoff, p.r, bias_cb, bias_sb, Qs, tid);
+    stage_plain<D, BQ, T>(gbase, p.sdo.n, i0, p.Nq, Gs, tid);
+    stage(0, WaitAcc{nullptr, 0, false, &failed});
+    fence_async_smem();
+  }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   // TMEM columns: S [0,64), dP [64,128), dS (bf16 pairs) [128,160), dQ' [256, 256+KD)
-  const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
-  const uint32_t idesc_q = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
-  const uint32_t qs_addr = smem_u32(Qs), gs_addr = smem_u32(Gs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
 
-  auto issue_scores = [&](int jt) {
-    const int buf = jt & 1;
-    for (int ks = 0; ks < KSTEPS; ++ks)
-      mma_ss(tmem, smem_desc(qs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
-             smem_desc(ks_addr + buf * KBUF + ks * 2 * CS64, CS64, 128), idesc_s, ks > 0);
-    for (int ks = 0; ks < D / 16; ++ks)
-      mma_ss(tmem + 64, smem_desc(gs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
-             smem_desc(vs_addr + buf * VBUF + ks * 2 * CS64, CS64, 128), idesc_s, ks > 0);
-    mma_commit(&bars[0]);
-  };
-  if (tid == 0) issue_scores(0);
+  if (issuer) {
+    if (lane == 0) {
+      const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
+      const uint32_t idesc_q = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
+      const uint32_t qs_addr = smem_u32(Qs), gs_addr = smem_u32(Gs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+      auto issue_scores = [&](int jt) {
+        const int buf = jt & 1;
+        uint64_t ad = smem_desc(qs_addr, BQ * 16, 128), bd = smem_desc(ks_addr + buf * KBUF, CS64, 128);
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          mma_ss(tmem, ad, bd, idesc_s, ks > 0);
+          ad += (2 * BQ * 16) >> 4, bd += (2 * CS64) >> 4;
+        }
+        ad = smem_desc(gs_addr, BQ * 16, 128), bd = smem_desc(vs_addr + buf * VBUF, CS64, 128);
+        for (int ks = 0; ks < D / 16; ++ks) {
+          mma_ss(tmem + 64, ad, bd, idesc_s, ks > 0);
+          ad += (2 * BQ * 16) >> 4, bd += (2 * CS64) >> 4;
+        }
+        mma_commit(&bars[BB_SCORES]);
+      };
+      issue_scores(0);
+      for (int j = 0; j < T_tiles; ++j) {
+        const int buf = j & 1;
+        if (j + 1 < T_tiles) {
+          if (!failed) failed = !mbar_wait(&bars[BB_STAGED], j & 1, WAIT_LIMIT);
+          if (!failed) failed = !mbar_wait(&bars[BB_CONSUMED], j & 1, WAIT_LIMIT);
+          fence_after_sync();
+          issue_scores(j + 1);
+        }
+        if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
+        fence_after_sync();
+        uint64_t bd = smem_desc(ks_addr + buf * KBUF, 128, CS64);
+#pragma unroll
+        for (int ks = 0; ks < BT / 16; ++ks) {
+          mma_ts(tmem + 256, tmem + 128 + ks * 8, bd, idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
+          bd += (2 * 128) >> 4;
+        }
+        mma_commit(&bars[BB_ACC]);
+      }
+      if (failed) atomicOr(p.status, 1u);
+    }
+    __syncwarp();
+    fence_before_sync();
+    __syncthreads();
+    tmem_dealloc(tmem, 512);
+    return;
+  }
 
-  bool failed = false;
+  // ------------------------------- workers ----------------------------------------------------------
   const int row = tid & 127, half = tid >> 7;           // thread = (query row, 32-key half)
   const int gi = i0 + row;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -128,12 +190,24 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
 
   for (int j = 0; j < T_tiles; ++j) {
     const int buf = j & 1, n0 = j * BT;
-    if (!failed) failed = !mbar_wait(&bars[0], j & 1, WAIT_LIMIT);
+    bool acc_prev_waited = false;
+    if (j + 1 < T_tiles) {
+      // the buffers of tile j+1 were last read by the accumulation step of tile j-1: the loads of the first
+      // batch are in flight while that wait runs
+      stage(j + 1, WaitAcc{&bars[BB_ACC], (uint32_t)((j - 1) & 1), j >= 1, &failed});
+      acc_prev_waited = true;
+      fence_async_smem();
+      warp_arrive(&bars[BB_STAGED], lane);
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // kbits of tile j+1 visible to every worker
+    }
+    if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
     fence_after_sync();
     uint32_t sv[32], dv[32];
     tmem_ld32(tmem + lane_base + half * 32, sv);
     tmem_ld32(tmem + lane_base + 64 + half * 32, dv);
     tmem_ld_wait();
+    fence_before_sync();
+    warp_arrive(&bars[BB_CONSUMED], lane);
     uint32_t vis = kbits[buf * 2 + half];
     if (p.causal) {
       const int lim = gi - (n0 + half * 32);  // columns <= lim visible
@@ -144,41 +218,24 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
     uint32_t pk[16];
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
-      float p0 = ex2_approx(__uint_as_float(sv[2 * e]) * p.scale_log2 - lse_use);
-      float p1 = ex2_approx(__uint_as_float(sv[2 * e + 1]) * p.scale_log2 - lse_use);
+      float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse_use));
+      float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse_use));
       p0 = ((vis >> (2 * e)) & 1u) ? p0 : 0.f;
       p1 = ((vis >> (2 * e + 1)) & 1u) ? p1 : 0.f;
       const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
       const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
       pk[e] = pack2<T>(d0, d1);
     }
-    // the dS columns were read by the dQ' step of tile j-1
-    if (j >= 1 && !failed) failed = !mbar_wait(&bars[1], (j - 1) & 1, WAIT_LIMIT);
+    // the dS columns were read by the accumulation step of tile j-1
+    if (j >= 1 && !acc_prev_waited && !failed) failed = !mbar_wait(&bars[BB_ACC], (j - 1) & 1, WAIT_LIMIT);
     tmem_st16(tmem + lane_base + 128 + half * 16, pk);
     tmem_st_wait();
     fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      fence_after_sync();
-      for (int ks = 0; ks < BT / 16; ++ks)
-        mma_ts(tmem + 256, tmem + 128 + ks * 8, smem_desc(ks_addr + buf * KBUF + ks * 2 * 128, 128, CS64),
-               idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
-      mma_commit(&bars[1]);
-    }
-    if (j + 1 < T_tiles) {
-      stage(j + 1);  // buffer 1-buf was last read by the dQ' step of tile j-1 (waited for above)
-      fence_async_smem();
-      fence_before_sync();
-      __syncthreads();
-      if (tid == 0) {
-        fence_after_sync();
-        issue_scores(j + 1);
-      }
-    }
+    warp_arrive(&bars[BB_GRAD], lane);
   }
 
   // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
-  if (!failed) failed = !mbar_wait(&bars[1], (T_tiles - 1) & 1, WAIT_LIMIT);
+  if (!failed) failed = !mbar_wait(&bars[BB_ACC], (T_tiles - 1) & 1, WAIT_LIMIT);
   fence_after_sync();
   {
     constexpr int HW = D / 2;  // features handled by this thread: [half*HW, half*HW + HW)
@@ -223,8 +280,7 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
   }
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  __syncthreads();   // the issuing warp frees the tensor memory after this barrier
 }
 
 }  // namespace pope

@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
   }
   load_bias_trig(biasr, p.r, 1.f, bias_cb, bias_sb, tid);
   __syncthreads();
-  stage_xform<D, BQ, T, true>(kbase, p.sk.n, j0, p.Nk, p.table, p.Nk, 0, p.r, bias_cb, bias_sb, Ks, tid);
+  stage_xform<D, BQ, T, true>(kbase, p.sk.n, j0, p.Nk, static_cast<const T*>(p.table), p.Nk, 0, p.r, bias_cb, bias_sb, Ks, tid);
   stage_plain<D, BQ, T>(vbase, p.sv.n, j0, p.Nk, Vs, tid);
 
   // query tiles: under the causal mask rows i < j0 see none of this CTA's keys
@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
     const int h = g * p.Hk + hk;
     const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
     const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
-    stage_xform<D, BT, T, false>(qbase, p.sq.n, m0, p.Nq, p.table, p.Nk, qoff, p.r, nullptr, nullptr, Qb + buf * KBUF, tid);
+    stage_xform<D, BT, T, false>(qbase, p.sq.n, m0, p.Nq, static_cast<const T*>(p.table), p.Nk, qoff, p.r, nullptr, nullptr, Qb + buf * KBUF, tid);
     stage_plain<D, BT, T>(gbase, p.sdo.n, m0, p.Nq, Gb + buf * VBUF, tid);
     if (tid < BT) {
       const int gi = m0 + tid;
@@ -259,10 +259,10 @@ template <int D, typename T>
 static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
   float* delta = reinterpret_cast<float*>(a.workspace);
-  __half* table = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(a.workspace) + delta_bytes(s));
+  void* table = reinterpret_cast<uint8_t*>(a.workspace) + delta_bytes(s);
   cudaError_t e = attn_bwd_delta(a, delta, st);
   if (e != cudaSuccess) return e;
-  if (s.r > 0 && (e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, table, false, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, table, s.dtype == POPE_BF16, st)) != cudaSuccess) return e;
   TcBwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
   p.scale = a.softmax_scale, p.scale_log2 = a.softmax_scale * LOG2E;
@@ -276,14 +276,14 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   if (!p.status) return cudaErrorInvalidSymbol;
   const int KD = s.d + s.r;
   const size_t streamed = 2 * (size_t)(KD / 8) * CS64 + 2 * (size_t)(D / 8) * CS64;
-  size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + 2 * 8 + 4 * 4 + 16 + 1024;
+  size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + (BB_COUNT + 1) * 8 + 4 * 4 + 16 + 1024;
   size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + 2 * BQ * BT * 2 + 256 * 4 + 2 * 8 + 16 + 16;
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;
   if ((e = cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(attn_bwd_dkdv_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k)) != cudaSuccess) return e;
-  attn_bwd_dq_tc_kernel<D, T><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), 256, smem_q, st>>>(p);
+  attn_bwd_dq_tc_kernel<D, T><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), BWD_THREADS, smem_q, st>>>(p);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), 256, smem_k, st>>>(p);
   return cudaGetLastError();

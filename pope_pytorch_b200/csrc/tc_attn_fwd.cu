@@ -182,19 +182,22 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
     // of W expand tasks stays in flight in registers, across tile boundaries, so the loads of the next tasks
     // travel while the current one is being expanded; V is loaded at the start of a tile and stored at its end.
     constexpr int NT = (TK * D / 256) / FWD_PRODUCER_WARPS;
-    constexpr int W = (NT % 4 == 0) ? 4 : (NT % 3 == 0 ? 3 : 2);
+    constexpr int W = (NT % 2 == 0) ? 2 : 3;
     static_assert(NT % W == 0, "window must divide the per-tile task count");
     const T* tab = static_cast<const T*>(p.table);
     const T* tab_s = tab + (int64_t)p.Nk * p.r;
     XTask win[W];
-#pragma unroll
-    for (int it = 0; it < W; ++it)
-      xtask_load<D, TK, T>(win[it], kbase, p.sk.n, 0, p.Nk, tab, tab_s, 0, p.r, pw + FWD_PRODUCER_WARPS * it, lane);
     for (int j = 0; j < T_tiles; ++j) {
       const int buf = j & 1, n0 = j * TK;
       uint8_t* Kb = Ks + buf * KBUF;
       uint8_t* Vb = Vs + buf * VBUF;
       PROF(0);
+      // every load of a tile is issued inside that tile's iteration: the proxy fence that closes an
+      // iteration waits for all of the thread's outstanding loads, so loads carried across it would
+      // only stall it
+#pragma unroll
+      for (int it = 0; it < W; ++it)
+        xtask_load<D, TK, T>(win[it], kbase, p.sk.n, n0, p.Nk, tab, tab_s, 0, p.r, pw + FWD_PRODUCER_WARPS * it, lane);
       uint4 vreg[NT];
 #pragma unroll
       for (int it = 0; it < NT; ++it) {
@@ -212,14 +215,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
 #pragma unroll
       for (int it = 0; it < NT; ++it) {
         xtask_store_packed<D, TK, T>(win[it % W], p.r, Kb, pw + FWD_PRODUCER_WARPS * it, lane);
-        const int nit = it + W;   // refill the slot with the task W ahead (possibly in the next tile)
-        if (nit < NT) {
+        const int nit = it + W;   // refill the slot with the task W ahead
+        if (nit < NT)
           xtask_load<D, TK, T>(win[it % W], kbase, p.sk.n, n0, p.Nk, tab, tab_s, 0, p.r,
                             pw + FWD_PRODUCER_WARPS * nit, lane);
-        } else if (j + 1 < T_tiles) {
-          xtask_load<D, TK, T>(win[it % W], kbase, p.sk.n, n0 + TK, p.Nk, tab, tab_s, 0, p.r,
-                            pw + FWD_PRODUCER_WARPS * (nit - NT), lane);
-        }
       }
       PROF(2);
 #ifndef POPE_DBG_PRODUCER_ONLY

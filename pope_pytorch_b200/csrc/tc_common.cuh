@@ -171,22 +171,23 @@ __device__ __forceinline__ void stage_xform_w(const T* base, int64_t sn, int row
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 x = unpack2<T>(rw[e]);
-          float2 co = unpack2<TT>(cw[e]);
-          float2 si = unpack2<TT>(sw[e]);
-          if (BIAS) {
+          if (BIAS) {   // resident operand, built once per CTA: fp32 products with the bias rotation
+            float2 co = unpack2<TT>(cw[e]);
+            float2 si = unpack2<TT>(sw[e]);
             const float2 b_c = *reinterpret_cast<const float2*>(cb + c * 8 + 2 * e);
             const float2 b_s = *reinterpret_cast<const float2*>(sb + c * 8 + 2 * e);
             const float2 c2 = make_float2(co.x * b_c.x - si.x * b_s.x, co.y * b_c.y - si.y * b_s.y);
             si = make_float2(si.x * b_c.x + co.x * b_s.x, si.y * b_c.y + co.y * b_s.y);
             co = c2;
+            const float a0 = softplus_fast(x.x), a1 = softplus_fast(x.y);
+            oc[e] = pack2<T>(a0 * co.x, a1 * co.y);   // zero rows: softplus(0) * table 0 = 0
+            os[e] = pack2<T>(a0 * si.x, a1 * si.y);
+          } else {      // streamed operand: packed 16-bit products, table already in the operand dtype
+            static_assert(BIAS || sizeof(TT) == sizeof(T), "streamed tiles multiply in the operand dtype");
+            const uint32_t a2 = pack2<T>(softplus_poly(x.x), softplus_poly(x.y));
+            oc[e] = mul2<T>(a2, cw[e]);
+            os[e] = mul2<T>(a2, sw[e]);
           }
-#ifdef POPE_DBG_NOMATH
-          const float a0 = x.x, a1 = x.y;
-#else
-          const float a0 = softplus_fast(x.x), a1 = softplus_fast(x.y);
-#endif
-          oc[e] = pack2<T>(a0 * co.x, a1 * co.y);   // zero rows: softplus(0) * table 0 = 0
-          os[e] = pack2<T>(a0 * si.x, a1 * si.y);
         }
         *reinterpret_cast<uint4*>(buf + c * ChunkStride<ROWS>::v + row * 16) = make_uint4(oc[0], oc[1], oc[2], oc[3]);
         *reinterpret_cast<uint4*>(buf + (DC + c) * ChunkStride<ROWS>::v + row * 16) = make_uint4(os[0], os[1], os[2], os[3]);
@@ -211,7 +212,12 @@ __device__ __forceinline__ void xtask_load(XTask& t, const T* base, int64_t sn, 
   stage_coords<ROWS, DC>(wt, lane, row, c);
   const int j = row0 + row;
   t.raw = t.tc = t.ts = make_uint4(0, 0, 0, 0);
+#ifdef POPE_DBG_NOLOAD
+  t.raw = make_uint4(j, c, wt, lane); t.tc = t.raw; t.ts = t.raw;
+  if (false) {
+#else
   if (j < nrows) {
+#endif
     t.raw = *reinterpret_cast<const uint4*>(base + (int64_t)j * sn + c * 8);
     if (c < (r >> 3)) {
       t.tc = *reinterpret_cast<const uint4*>(tab + (int64_t)(pos0 + j) * r + c * 8);
@@ -244,8 +250,13 @@ __device__ __forceinline__ void xtask_store_packed(const XTask& t, int r, uint8_
       os[e] = mul2<T>(a2, sw[e]);
 #endif
     }
+#ifdef POPE_DBG_NOSTORE
+    if ((oc[0] ^ oc[1] ^ oc[2] ^ oc[3] ^ os[0] ^ os[1] ^ os[2] ^ os[3]) == 0x12345u)
+#endif
+    {
     *reinterpret_cast<uint4*>(buf + c * ChunkStride<ROWS>::v + row * 16) = make_uint4(oc[0], oc[1], oc[2], oc[3]);
     *reinterpret_cast<uint4*>(buf + (DC + c) * ChunkStride<ROWS>::v + row * 16) = make_uint4(os[0], os[1], os[2], os[3]);
+    }
   } else {
     *reinterpret_cast<uint4*>(buf + c * ChunkStride<ROWS>::v + row * 16) = t.raw;
   }

@@ -210,8 +210,9 @@ def test_attention_config3_training_shape_slices():
             if bb in (0, 3):
                 for name, got in (("out", out), ("dq", qg.grad), ("dk", kg.grad), ("dv", vg.grad)):
                     e = maxerr(got[sl], ref[name])
-                    # 2e-2 absolute; where a gradient exceeds ~5 the bf16 store alone costs 2^-9 of it
-                    bound = max(2e-2, 2.0 ** -8 * float(ref[name].abs().max()))
+                    # 2e-2 absolute on the value, plus the half-ulp its bf16 storage costs at that magnitude
+                    # (|dv| reaches 4.3 here: 2^-9 of it is 0.008 before any arithmetic error)
+                    bound = 2e-2 + 2.0 ** -9 * float(ref[name].abs().max())
                     assert e <= bound, f"{name} unit ({bb},{hh}): {e} > {bound}"
     got = bias_g.grad[heads].float().cpu()
     rel = float((got - dbias_ref).abs().max() / dbias_ref.abs().max())
