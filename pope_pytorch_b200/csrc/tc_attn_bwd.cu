@@ -40,29 +40,64 @@ constexpr int BT = 64;   // streamed rows per step
 // ================================================================================================
 // dq
 // ================================================================================================
-constexpr int BWD_THREADS = 288;   // warps 0-7 stage and do the elementwise work, warp 8 issues every MMA
+// Warp roles of both backward kernels (17 warps, 544 threads)
+constexpr int BWD_E_WARPS = 8;     // warps 0-7  : elementwise work (P, dS) and the epilogue; build the resident operands
+constexpr int BWD_P_WARPS = 8;     // warps 8-15 : expand / copy the streamed tiles
+constexpr int BWD_M_WARP = 16;     // warp 16    : issues every MMA
+constexpr int BWD_THREADS = 32 * (BWD_M_WARP + 1);
 
 // mbarrier slots shared by both backward kernels
-enum { BB_SCORES = 0,    // tcgen05.commit: the two score products of the current tile are in TMEM
-       BB_ACC = 1,       // tcgen05.commit: the accumulation step of the current tile has finished
-       BB_CONSUMED = 2,  // 8 warps: scores copied to registers, the score columns may be overwritten
-       BB_STAGED = 3,    // 8 warps: the next streamed tile is in shared memory
-       BB_GRAD = 4,      // 8 warps: dS (and P) of the current tile are written
-       BB_COUNT = 5 };
-
-struct WaitAcc {   // staging hook: the streamed buffers of tile j+1 were last read by the accumulation of tile j-1
-  uint64_t* bar;
-  uint32_t parity;
-  bool enabled;
-  bool* failed;
-  __device__ __forceinline__ void operator()() const {
-    if (enabled && !*failed) *failed = !mbar_wait(bar, parity, WAIT_LIMIT);
-  }
-};
+enum { BB_FULL = 0,      // [2] 8 producer warps: streamed tile j is in buffer j & 1
+       BB_SCORES = 2,    // tcgen05.commit: the two score products of the current tile are in TMEM
+       BB_ACC = 3,       // [2] tcgen05.commit: the accumulation step of tile j has finished (slot j & 1; a waiter
+                         //     may lag two tiles behind, which a single barrier's phase parity cannot express)
+       BB_CONSUMED = 5,  // 8 warps: scores copied to registers, the score columns may be overwritten
+       BB_GRAD = 6,      // 8 warps: dS (and P) of the current tile are written
+       BB_RESIDENT = 7,  // 8 warps: the resident operands are in shared memory
+       BB_COUNT = 8 };
 
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
+}
+
+// All eight producer warps share every tile.  (Two groups of four on alternate tiles were measured slower:
+// 2.34 ms against 1.83 ms for the dq kernel at the training shape.)
+constexpr int BWD_PG_WARPS = BWD_P_WARPS;
+
+// One streamed tile by the producer warps: BT rows of X expanded with the phase table (rows pos0 + row) into Xb,
+// BT rows of Y copied into Yb, in batches whose loads are all issued before their first store; `wait_free`
+// runs after the first batch of loads and before the first shared-memory store.
+template <int D, typename T, typename Wait>
+__device__ __forceinline__ void produce_tile(const T* xbase, int64_t xsn, const T* ybase, int64_t ysn, int row0, int nrows,
+                                             const T* tab, int tab_n, int pos0, int r, uint8_t* Xb, uint8_t* Yb, int pw,
+                                             int lane, Wait wait_free) {
+  constexpr int NT = (BT * D / 256) / BWD_PG_WARPS;   // warp tasks (32 chunks of 16 B) per warp and operand
+  constexpr int NB = NT % 4 == 0 ? 4 : (NT % 3 == 0 ? 3 : 2);
+  const T* tab_s = tab + (int64_t)tab_n * r;
+#pragma unroll
+  for (int b0 = 0; b0 < NT; b0 += NB) {
+    XTask xt[NB];
+    uint4 yr[NB];
+#pragma unroll
+    for (int it = 0; it < NB; ++it) {
+      const int wt = pw + BWD_PG_WARPS * (b0 + it);
+      xtask_load<D, BT, T>(xt[it], xbase, xsn, row0, nrows, tab, tab_s, pos0, r, wt, lane);
+      int row, c;
+      stage_coords<BT, D / 8>(wt, lane, row, c);
+      yr[it] = make_uint4(0, 0, 0, 0);
+      if (row0 + row < nrows) yr[it] = *reinterpret_cast<const uint4*>(ybase + (int64_t)(row0 + row) * ysn + c * 8);
+    }
+    if (b0 == 0) wait_free();
+#pragma unroll
+    for (int it = 0; it < NB; ++it) {
+      const int wt = pw + BWD_PG_WARPS * (b0 + it);
+      xtask_store_packed<D, BT, T>(xt[it], r, Xb, wt, lane);
+      int row, c;
+      stage_coords<BT, D / 8>(wt, lane, row, c);
+      *reinterpret_cast<uint4*>(Yb + c * CS64 + row * 16) = yr[it];
+    }
+  }
 }
 
 template <int D, typename T>
@@ -81,60 +116,63 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   float* bias_sb = bias_cb + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool issuer = warp == 8;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
   const int i0 = (gridDim.x - 1 - blockIdx.x) * BQ;
   const int qoff = p.Nk - p.Nq;
   const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
-  const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
-  const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
-  const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
-  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
   const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
+  const T* tab = static_cast<const T*>(p.table);
 
-  if (issuer) {
+  if (warp == BWD_M_WARP) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1);
-    mbar_init(&bars[BB_CONSUMED], 8), mbar_init(&bars[BB_STAGED], 8), mbar_init(&bars[BB_GRAD], 8);
+    mbar_init(&bars[BB_FULL], BWD_PG_WARPS), mbar_init(&bars[BB_FULL + 1], BWD_PG_WARPS);
+    mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1), mbar_init(&bars[BB_ACC + 1], 1);
+    mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
+    mbar_init(&bars[BB_RESIDENT], BWD_E_WARPS);
     mbar_init_fence();
   }
   int n_end = p.Nk;
   if (p.causal) n_end = min(n_end, min(i0 + BQ, p.Nq));
   const int T_tiles = (n_end + BT - 1) / BT;
+  // Key tiles are visited in an order rotated per unit: the CTAs resident at one time belong to different
+  // units and would otherwise all ask L2 for the same phase-table lines at the same moment.
+  const int rot = (u * 5 + blockIdx.x * 3) % T_tiles;
+  auto tile_start = [&](int j) { int t = j + rot; if (t >= T_tiles) t -= T_tiles; return t * BT; };
   bool failed = false;
-
-  auto stage = [&](int jt, WaitAcc hook) {   // workers only
-    const int buf = jt & 1, n0 = jt * BT;
-    stage_xform_w<D, BT, T, false, 8, WaitAcc, T>(kbase, p.sk.n, n0, p.Nk, static_cast<const T*>(p.table), p.Nk, 0, p.r, nullptr, nullptr,
-                                               Ks + buf * KBUF, warp, lane, hook);
-    stage_plain<D, BT, T>(vbase, p.sv.n, n0, p.Nk, Vs + buf * VBUF, tid);
-    if (tid < BT) {
-      const int j = n0 + tid;
-      const bool ok = j < p.Nk && (!maskb || maskb[(int64_t)j * p.msn] != 0);
-      const uint32_t bits = __ballot_sync(0xffffffffu, ok);
-      if ((tid & 31) == 0) kbits[buf * 2 + (tid >> 5)] = bits;
-    }
-  };
-
-  if (!issuer) {
-    // resident operands: Q' with phase (fq - bias), dO; then the first key tile
-    load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    stage_xform<D, BQ, T, true>(qbase, p.sq.n, i0, p.Nq, static_cast<const T*>(p.table), p.Nk, qoff, p.r, bias_cb, bias_sb, Qs, tid);
-    stage_plain<D, BQ, T>(gbase, p.sdo.n, i0, p.Nq, Gs, tid);
-    stage(0, WaitAcc{nullptr, 0, false, &failed});
-    fence_async_smem();
-  }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   // TMEM columns: S [0,64), dP [64,128), dS (bf16 pairs) [128,160), dQ' [256, 256+KD)
 
-  if (issuer) {
+  if (warp >= BWD_E_WARPS && warp < BWD_M_WARP) {
+    // =============================== producers: K' and V tiles =================================
+    const int pw = warp - BWD_E_WARPS;
+    const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
+    const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
+    const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
+    for (int j = 0; j < T_tiles; ++j) {
+      const int buf = j & 1, n0 = tile_start(j);
+      // buffer j & 1 was last read by the accumulation step of tile j-2 (its score products finished earlier)
+      auto wait_free = [&]() {
+        if (j >= 2 && !failed) failed = !mbar_wait(&bars[BB_ACC + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+      };
+      produce_tile<D, T>(kbase, p.sk.n, vbase, p.sv.n, n0, p.Nk, tab, p.Nk, 0, p.r, Ks + buf * KBUF, Vs + buf * VBUF, pw,
+                         lane, wait_free);
+      if (pw < 2) {
+        const int jk = n0 + pw * 32 + lane;
+        const bool ok = jk < p.Nk && (!maskb || maskb[(int64_t)jk * p.msn] != 0);
+        const uint32_t bits = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) kbits[buf * 2 + pw] = bits;
+      }
+      fence_async_smem();
+      warp_arrive(&bars[BB_FULL + buf], lane);
+    }
+  } else if (warp == BWD_M_WARP) {
+    // =============================== MMA issue ===================================================
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
       const uint32_t idesc_q = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
@@ -153,11 +191,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         }
         mma_commit(&bars[BB_SCORES]);
       };
+      if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
+      if (!mbar_wait(&bars[BB_FULL], 0, WAIT_LIMIT)) failed = true;
+      fence_after_sync();
       issue_scores(0);
       for (int j = 0; j < T_tiles; ++j) {
         const int buf = j & 1;
         if (j + 1 < T_tiles) {
-          if (!failed) failed = !mbar_wait(&bars[BB_STAGED], j & 1, WAIT_LIMIT);
+          if (!failed) failed = !mbar_wait(&bars[BB_FULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
           if (!failed) failed = !mbar_wait(&bars[BB_CONSUMED], j & 1, WAIT_LIMIT);
           fence_after_sync();
           issue_scores(j + 1);
@@ -170,64 +211,71 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
           mma_ts(tmem + 256, tmem + 128 + ks * 8, bd, idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
           bd += (2 * 128) >> 4;
         }
-        mma_commit(&bars[BB_ACC]);
+        mma_commit(&bars[BB_ACC + buf]);
       }
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
+  }
+  if (warp >= BWD_E_WARPS) {
     fence_before_sync();
     __syncthreads();
-    tmem_dealloc(tmem, 512);
+    if (warp == BWD_M_WARP) tmem_dealloc(tmem, 512);
     return;
   }
 
-  // ------------------------------- workers ----------------------------------------------------------
+  // =============================== elementwise warps ================================================
+  {
+    const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
+    load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    stage_xform<D, BQ, T, true>(qbase, p.sq.n, i0, p.Nq, tab, p.Nk, qoff, p.r, bias_cb, bias_sb, Qs, tid);
+    stage_plain<D, BQ, T>(gbase, p.sdo.n, i0, p.Nq, Gs, tid);
+    fence_async_smem();
+    warp_arrive(&bars[BB_RESIDENT], lane);
+  }
   const int row = tid & 127, half = tid >> 7;           // thread = (query row, 32-key half)
   const int gi = i0 + row;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   const float lse2 = gi < p.Nq ? p.lse[(int64_t)u * p.Nq + gi] * LOG2E : -CUDART_INF_F;
+  const float lse_use = lse2 == -CUDART_INF_F ? 0.f : lse2;
   const float dlt = gi < p.Nq ? p.delta[(int64_t)u * p.Nq + gi] : 0.f;
 
   for (int j = 0; j < T_tiles; ++j) {
-    const int buf = j & 1, n0 = j * BT;
-    bool acc_prev_waited = false;
-    if (j + 1 < T_tiles) {
-      // the buffers of tile j+1 were last read by the accumulation step of tile j-1: the loads of the first
-      // batch are in flight while that wait runs
-      stage(j + 1, WaitAcc{&bars[BB_ACC], (uint32_t)((j - 1) & 1), j >= 1, &failed});
-      acc_prev_waited = true;
-      fence_async_smem();
-      warp_arrive(&bars[BB_STAGED], lane);
-      asm volatile("bar.sync 1, 256;" ::: "memory");   // kbits of tile j+1 visible to every worker
-    }
+    const int buf = j & 1, n0 = tile_start(j);
+    if (!failed) failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the kbits read
     if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
     fence_after_sync();
-    uint32_t sv[32], dv[32];
-    tmem_ld32(tmem + lane_base + half * 32, sv);
-    tmem_ld32(tmem + lane_base + 64 + half * 32, dv);
-    tmem_ld_wait();
-    fence_before_sync();
-    warp_arrive(&bars[BB_CONSUMED], lane);
     uint32_t vis = kbits[buf * 2 + half];
     if (p.causal) {
       const int lim = gi - (n0 + half * 32);  // columns <= lim visible
       vis &= lim >= 31 ? 0xffffffffu : (lim < 0 ? 0u : ((2u << lim) - 1u));
     }
     if (lse2 == -CUDART_INF_F) vis = 0u;
-    const float lse_use = lse2 == -CUDART_INF_F ? 0.f : lse2;
     uint32_t pk[16];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse_use));
-      float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse_use));
-      p0 = ((vis >> (2 * e)) & 1u) ? p0 : 0.f;
-      p1 = ((vis >> (2 * e + 1)) & 1u) ? p1 : 0.f;
-      const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
-      const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
-      pk[e] = pack2<T>(d0, d1);
+    for (int hh = 0; hh < 2; ++hh) {   // 16 key columns at a time keeps the register footprint small
+      uint32_t sv[16], dv[16];
+      tmem_ld16(tmem + lane_base + half * 32 + hh * 16, sv);
+      tmem_ld16(tmem + lane_base + 64 + half * 32 + hh * 16, dv);
+      tmem_ld_wait();
+      if (hh == 1) {   // every score of this tile is in registers: the next score products may overwrite them
+        fence_before_sync();
+        warp_arrive(&bars[BB_CONSUMED], lane);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse_use));
+        float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse_use));
+        p0 = ((vis >> (hh * 16 + 2 * e)) & 1u) ? p0 : 0.f;
+        p1 = ((vis >> (hh * 16 + 2 * e + 1)) & 1u) ? p1 : 0.f;
+        const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
+        const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
+        pk[hh * 8 + e] = pack2<T>(d0, d1);
+      }
     }
     // the dS columns were read by the accumulation step of tile j-1
-    if (j >= 1 && !acc_prev_waited && !failed) failed = !mbar_wait(&bars[BB_ACC], (j - 1) & 1, WAIT_LIMIT);
+    if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
     tmem_st16(tmem + lane_base + 128 + half * 16, pk);
     tmem_st_wait();
     fence_before_sync();
@@ -235,7 +283,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   }
 
   // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
-  if (!failed) failed = !mbar_wait(&bars[BB_ACC], (T_tiles - 1) & 1, WAIT_LIMIT);
+  if (!failed) failed = !mbar_wait(&bars[BB_ACC + ((T_tiles - 1) & 1)], ((T_tiles - 1) >> 1) & 1, WAIT_LIMIT);
   fence_after_sync();
   {
     constexpr int HW = D / 2;  // features handled by this thread: [half*HW, half*HW + HW)

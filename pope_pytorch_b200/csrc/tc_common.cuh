@@ -198,6 +198,23 @@ __device__ __forceinline__ void stage_xform_w(const T* base, int64_t sn, int row
   }
 }
 
+// Pull one streamed tile towards L2 ahead of use.  Every CTA of a (batch, head) unit walks the same tiles at
+// about the same time, so without this each tile's first touch is an HBM miss that all of them wait on.
+// 256 producer threads: thread t covers row t % 64 of array t / 64 (X rows, Y rows, cos rows, sin rows);
+// a row is D (or r) 2-byte elements.
+template <int D, typename T>
+__device__ __forceinline__ void prefetch_tile_l2(const T* xbase, int64_t xsn, const T* ybase, int64_t ysn, int row0,
+                                                 int nrows, const T* tab, int tab_n, int pos0, int r, int ptid) {
+  const int row = row0 + (ptid & 63), which = ptid >> 6;
+  if (row >= nrows) return;
+  const char* ptr;
+  int bytes;
+  if (which == 0) ptr = reinterpret_cast<const char*>(xbase + (int64_t)row * xsn), bytes = D * 2;
+  else if (which == 1) ptr = reinterpret_cast<const char*>(ybase + (int64_t)row * ysn), bytes = D * 2;
+  else ptr = reinterpret_cast<const char*>(tab + (int64_t)(which - 2) * tab_n * r + (int64_t)(pos0 + row) * r), bytes = r * 2;
+  for (int o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr + o));
+}
+
 // ---- streaming producer: a register window of K-tile tasks kept in flight across tiles ---------------
 struct XTask {
   uint4 raw, tc, ts;
