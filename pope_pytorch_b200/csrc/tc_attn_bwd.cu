@@ -86,7 +86,7 @@ __device__ __forceinline__ void produce_tile(const T* xbase, int64_t xsn, const 
       int row, c;
       stage_coords<BT, D / 8>(wt, lane, row, c);
       yr[it] = make_uint4(0, 0, 0, 0);
-      if (row0 + row < nrows) yr[it] = *reinterpret_cast<const uint4*>(ybase + (int64_t)(row0 + row) * ysn + c * 8);
+      if (row0 + row < nrows) yr[it] = __ldg(reinterpret_cast<const uint4*>(ybase + (int64_t)(row0 + row) * ysn + c * 8));
     }
     if (b0 == 0) wait_free();
 #pragma unroll
@@ -252,6 +252,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       vis &= lim >= 31 ? 0xffffffffu : (lim < 0 ? 0u : ((2u << lim) - 1u));
     }
     if (lse2 == -CUDART_INF_F) vis = 0u;
+    const bool all_vis = __all_sync(0xffffffffu, vis == 0xffffffffu);   // interior tile: no masking work
     uint32_t pk[16];
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {   // 16 key columns at a time keeps the register footprint small
@@ -267,8 +268,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       for (int e = 0; e < 8; ++e) {
         float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse_use));
         float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse_use));
-        p0 = ((vis >> (hh * 16 + 2 * e)) & 1u) ? p0 : 0.f;
-        p1 = ((vis >> (hh * 16 + 2 * e + 1)) & 1u) ? p1 : 0.f;
+        if (!all_vis) {
+          p0 = ((vis >> (hh * 16 + 2 * e)) & 1u) ? p0 : 0.f;
+          p1 = ((vis >> (hh * 16 + 2 * e + 1)) & 1u) ? p1 : 0.f;
+        }
         const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
         const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
         pk[hh * 8 + e] = pack2<T>(d0, d1);

@@ -56,7 +56,8 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
     if (tid < BT) {
       const int gi = m0 + tid;
       const int64_t uq = (int64_t)(b * p.H + h) * p.Nq + gi;
-      rowstat[buf * 128 + tid] = gi < p.Nq ? p.lse[uq] * LOG2E : -CUDART_INF_F;
+      const float lse_i = gi < p.Nq ? p.lse[uq] : -CUDART_INF_F;
+      rowstat[buf * 128 + tid] = lse_i == -CUDART_INF_F ? CUDART_INF_F : lse_i * LOG2E;   // +inf: P becomes exactly 0
       rowstat[buf * 128 + 64 + tid] = gi < p.Nq ? p.delta[uq] : 0.f;
     }
   };
@@ -104,8 +105,16 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
     // P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[1], (j - 1) & 1, WAIT_LIMIT);
     const float* st = rowstat + buf * 128 + half * 32;
+    // interior tile for this warp: every key row valid and (causal) every key at or before every query column;
+    // out-of-range queries and rows without any visible key carry lse = +inf, which makes P exactly 0
+    const int gj_hi = j0 + (warp & 3) * 32 + 31, gi_lo = m0 + half * 32;
+    const bool interior = __all_sync(0xffffffffu, key_ok) && (!p.causal || gj_hi <= gi_lo);
 #pragma unroll
     for (int cc = 0; cc < 4; ++cc) {
+      const float4 la = *reinterpret_cast<const float4*>(st + cc * 8), lb = *reinterpret_cast<const float4*>(st + cc * 8 + 4);
+      const float4 da = *reinterpret_cast<const float4*>(st + 64 + cc * 8), db = *reinterpret_cast<const float4*>(st + 64 + cc * 8 + 4);
+      const float l2v[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+      const float dlv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
       uint32_t pw[4], dw[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -113,12 +122,10 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           const int col = cc * 8 + e * 2 + t;            // query column within this thread's half
-          const int gi = m0 + half * 32 + col;
-          const float l2 = st[col];
-          const bool ok = key_ok && gi < p.Nq && (!p.causal || gj <= gi) && l2 != -CUDART_INF_F;
-          const float pr = ok ? ex2_approx(__uint_as_float(sv[col]) * p.scale_log2 - l2) : 0.f;
+          float pr = ex2_approx(fmaf(__uint_as_float(sv[col]), p.scale_log2, -l2v[e * 2 + t]));
+          if (!interior) pr = (key_ok && (!p.causal || gj <= gi_lo + col)) ? pr : 0.f;
           pv[t] = pr;
-          dsv[t] = pr * (__uint_as_float(dv[col]) - st[64 + col]) * p.scale;
+          dsv[t] = pr * (__uint_as_float(dv[col]) - dlv[e * 2 + t]) * p.scale;
         }
         pw[e] = pack2<T>(pv[0], pv[1]);
         dw[e] = pack2<T>(dsv[0], dsv[1]);

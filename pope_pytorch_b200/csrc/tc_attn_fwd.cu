@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
         int row, c;
         stage_coords<TK, D / 8>(pw + FWD_PRODUCER_WARPS * it, lane, row, c);
         vreg[it] = make_uint4(0, 0, 0, 0);
-        if (n0 + row < p.Nk) vreg[it] = *reinterpret_cast<const uint4*>(vbase + (int64_t)(n0 + row) * p.sv.n + c * 8);
+        if (n0 + row < p.Nk) vreg[it] = __ldg(reinterpret_cast<const uint4*>(vbase + (int64_t)(n0 + row) * p.sv.n + c * 8));
       }
       PROF(1);
       // the K' buffer of tile j was last read by S(j-2), the V buffer by PV(j-2)

@@ -184,7 +184,7 @@ __device__ __forceinline__ void stage_xform_w(const T* base, int64_t sn, int row
             os[e] = pack2<T>(a0 * si.x, a1 * si.y);
           } else {      // streamed operand: packed 16-bit products, table already in the operand dtype
             static_assert(BIAS || sizeof(TT) == sizeof(T), "streamed tiles multiply in the operand dtype");
-            const uint32_t a2 = pack2<T>(softplus_poly(x.x), softplus_poly(x.y));
+            const uint32_t a2 = pack2<T>(softplus_fast(x.x), softplus_fast(x.y));
             oc[e] = mul2<T>(a2, cw[e]);
             os[e] = mul2<T>(a2, sw[e]);
           }
@@ -235,10 +235,10 @@ __device__ __forceinline__ void xtask_load(XTask& t, const T* base, int64_t sn, 
 #else
   if (j < nrows) {
 #endif
-    t.raw = *reinterpret_cast<const uint4*>(base + (int64_t)j * sn + c * 8);
+    t.raw = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)j * sn + c * 8));
     if (c < (r >> 3)) {
-      t.tc = *reinterpret_cast<const uint4*>(tab + (int64_t)(pos0 + j) * r + c * 8);
-      t.ts = *reinterpret_cast<const uint4*>(tab_s + (int64_t)(pos0 + j) * r + c * 8);
+      t.tc = __ldg(reinterpret_cast<const uint4*>(tab + (int64_t)(pos0 + j) * r + c * 8));
+      t.ts = __ldg(reinterpret_cast<const uint4*>(tab_s + (int64_t)(pos0 + j) * r + c * 8));
     }
   }
 }
@@ -262,7 +262,7 @@ __device__ __forceinline__ void xtask_store_packed(const XTask& t, int r, uint8_
       os[e] = rw[e] ^ sw[e];
 #else
       const float2 x = unpack2<T>(rw[e]);
-      const uint32_t a2 = pack2<T>(softplus_poly(x.x), softplus_poly(x.y));
+      const uint32_t a2 = pack2<T>(softplus_fast(x.x), softplus_fast(x.y));
       oc[e] = mul2<T>(a2, cw[e]);
       os[e] = mul2<T>(a2, sw[e]);
 #endif
