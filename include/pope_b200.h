@@ -92,6 +92,7 @@ typedef struct PopeSimArgs {
   const void* q; PopeStride3 sq;
   const void* k; PopeStride3 sk;
   void* sim;     PopeStride3 ss;
+  void* workspace; size_t workspace_bytes;  /* pope_b200_workspace_bytes(POPE_OP_SIM_FWD, &args); may be NULL when 0 */
 } PopeSimArgs;
 
 /* Replaces PoPESimilarityFunction.backward, PoPE_pytorch/triton_pope.py:290-362.

@@ -38,7 +38,7 @@ class Embed(C.Structure):
 class SimArgs(C.Structure):
     _fields_ = [("struct_bytes", C.c_uint32), ("allow_tf32", C.c_int32), ("shape", Shape), ("embed", Embed),
                 ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
-                ("sim", C.c_void_p), ("ss", Stride3)]
+                ("sim", C.c_void_p), ("ss", Stride3), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
 class SimBwdArgs(C.Structure):
@@ -206,9 +206,11 @@ def sim_forward(q, k, freqs, bias, allow_tf32=True) -> torch.Tensor:
     freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
     sim = torch.empty(q.shape[0], q.shape[1], q.shape[2], k.shape[2], dtype=q.dtype, device=q.device)
     a = SimArgs(C.sizeof(SimArgs), int(allow_tf32), _shape(q, k, r), _embed_struct(freqs, bias, r),
-                q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), sim.data_ptr(), _s3(sim))
+                q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), sim.data_ptr(), _s3(sim), None, 0)
+    ws = _workspace(OP_SIM_FWD, a, q.device)
     with torch.cuda.device(q.device):
         _check(lib.pope_b200_sim_fwd(C.addressof(a), _stream_ptr(q)), "pope_b200_sim_fwd")
+    del ws
     return sim
 
 

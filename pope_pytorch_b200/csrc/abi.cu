@@ -67,6 +67,11 @@ int pope_b200_device_status(void) { return static_cast<int>(pope::tc_read_status
 size_t pope_b200_workspace_bytes(int op, const void* args) {
   if (!args) return 0;
   switch (op) {
+    case POPE_OP_SIM_FWD: {
+      const PopeSimArgs& a = *static_cast<const PopeSimArgs*>(args);
+      if (a.struct_bytes != sizeof(PopeSimArgs) || check_shape(a.shape) != POPE_OK) return 0;
+      return (!force_simt() && pope::sim_fwd_tc_supported(a)) ? pope::sim_fwd_tc_workspace(a) : 0;
+    }
     case POPE_OP_ATTN_FWD: {
       const PopeAttnArgs& a = *static_cast<const PopeAttnArgs*>(args);
       if (a.struct_bytes != sizeof(PopeAttnArgs) || check_shape(a.shape) != POPE_OK) return 0;
@@ -89,9 +94,14 @@ int pope_b200_sim_fwd(const PopeSimArgs* a, void* stream) {
   if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
   if (rc != POPE_OK) return rc;
   if (!a->q || !a->k || !a->sim) return POPE_ERR_BAD_ARG;
+  // the tensor-core kernel needs its phase tables; a caller that passes no workspace gets the exact family
+  const bool tc = !force_simt() && pope::sim_fwd_tc_supported(*a) && a->workspace &&
+                  a->workspace_bytes >= pope::sim_fwd_tc_workspace(*a) &&
+                  (reinterpret_cast<uintptr_t>(a->workspace) & 15) == 0;
   if ((rc = check_device()) != POPE_OK) return rc;
-  if (pope::sim_fwd_simt(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
-  g_last_path = "simt";
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((tc ? pope::sim_fwd_tc(*a, st) : pope::sim_fwd_simt(*a, st)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = tc ? "tcgen05" : "simt";
   return POPE_OK;
 }
 

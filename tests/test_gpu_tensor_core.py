@@ -109,3 +109,28 @@ def test_backward_tc_matches_exact_family(b, h, hk, n, d, r, causal, masked, dty
         for name, a1, a0 in (("dbias", db1, db0), ("dfreqs", df1, df0)):
             rel = float((a1 - a0).abs().max() / a0.abs().max().clamp_min(1.0))
             assert rel <= 2e-2, f"{name}: {rel}"
+
+
+@pytest.mark.parametrize("n,d,r,dtype", [(1024, 64, 64, torch.float32), (776, 64, 32, torch.float32),
+                                          (512, 128, 64, torch.float32), (1024, 64, 64, torch.bfloat16)])
+def test_similarity_tc_matches_exact_family(n, d, r, dtype):
+    """The split-precision tensor-core similarity against the fp32 FMA kernel: 1e-4 of max|sim| for fp32."""
+    g = torch.Generator().manual_seed(n + d + r)
+    q, k = (torch.randn(1, 8, n, d, generator=g).to(dtype).to(DEV) for _ in range(2))
+    pope = PoPE(r, heads=8)
+    with torch.no_grad():
+        pope.bias.uniform_(-6.0, 0.0, generator=g)
+    e = pope(n)
+    freqs, bias = e.freqs.to(DEV), e.bias.detach().to(DEV)
+    os.environ["POPE_B200_FORCE_SIMT"] = "0"
+    s_tc = _native.sim_forward(q, k, freqs, bias)
+    path_tc = _native.last_path()
+    os.environ["POPE_B200_FORCE_SIMT"] = "1"
+    try:
+        s_ex = _native.sim_forward(q, k, freqs, bias)
+        path_ex = _native.last_path()
+    finally:
+        os.environ["POPE_B200_FORCE_SIMT"] = "0"
+    assert path_tc == "tcgen05" and path_ex == "simt" and _native.device_status() == 0
+    tol = 1e-4 if dtype == torch.float32 else 1e-2
+    assert float((s_tc.float() - s_ex.float()).abs().max()) <= tol * float(s_ex.float().abs().max())
