@@ -26,6 +26,23 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// softplus(x) = max(x,0) + log1p(exp(-|x|)); beyond x = 20 the second term is below 2.1e-9,
+// i.e. the reference's cut-over to the identity is reproduced to fp32 rounding.
+__device__ __forceinline__ float softplus_fast(float x) {
+  const float t = ex2_approx(-fabsf(x) * 1.4426950408889634f);
+  return fmaxf(x, 0.f) + lg2_approx(1.f + t) * 0.6931471805599453f;
+}
+
 // Addressing of one (batch, head) unit of a strided tensor.
 struct Strides {
   int64_t b, h, n;

@@ -267,6 +267,178 @@ cudaError_t attn_bwd_delta(const PopeAttnBwdArgs& a, float* delta, cudaStream_t 
   }
 }
 
+// ---- decode: one query row against a long key range ------------------------------------------------
+// Memory-bound (every K and V row is read once per unit), so the work is laid out for coalescing: a warp
+// takes one key at a time, lane l holds features 4l .. 4l+3 (and 128 + 4l .. for d > 128) of the key, of V and
+// of the accumulator; the score is a warp reduction.  Key phases come from fp32 (cos f, sin f) tables built
+// once per call and shared by all units, rotated by the head's bias held in registers.  Each (unit, key
+// range) CTA writes a partial (o, m, l) that attn_fwd_combine_kernel merges.
+constexpr int DEC_WARPS = 8;
+
+struct DecodeP {
+  int H, Hk, Nk, d, r, nsplit, split_len;
+  float scale;
+  const void *q, *k, *v;
+  Strides sq, sk, sv;
+  const float *freqs, *bias, *ctab, *stab;   // freqs: query row only; tables: keys
+  int64_t sfn, bias_sh;
+  const uint8_t* mask;
+  int64_t msb, msn;
+  float *part_o, *part_ml;
+  int HDP;
+};
+
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&x)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&x)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[4]) {
+  const uint2 a = *reinterpret_cast<const uint2*>(p);
+  x[0] = __uint_as_float(a.x << 16), x[1] = __uint_as_float(a.x & 0xffff0000u);
+  x[2] = __uint_as_float(a.y << 16), x[3] = __uint_as_float(a.y & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void load4<__half>(const __half* p, float (&x)[4]) {
+  const uint2 a = *reinterpret_cast<const uint2*>(p);
+  const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&a.x)), hi = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+  x[0] = lo.x, x[1] = lo.y, x[2] = hi.x, x[3] = hi.y;
+}
+
+template <typename T, int DM>   // DM = feature groups of 128 (1: d <= 128, 2: d <= 256)
+__global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(DecodeP p) {
+  __shared__ float red_o[DEC_WARPS][DM * 128];
+  __shared__ float red_ml[DEC_WARPS][2];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
+  const T* qrow = (const T*)p.q + b * p.sq.b + h * p.sq.h;            // the single query row
+  const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
+  const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
+  const uint8_t* mask = p.mask ? p.mask + b * p.msb : nullptr;
+  const int kb = blockIdx.x * p.split_len, ke = min(p.Nk, kb + p.split_len);
+
+  // this lane's slice of q' (exact transform, phase of the last position) and of the bias rotation
+  float qc[DM][4], qs[DM][4], cb[DM][4], sb[DM][4];
+  bool live[DM], rot[DM];
+#pragma unroll
+  for (int m = 0; m < DM; ++m) {
+    const int c0 = m * 128 + lane * 4;
+    live[m] = c0 < p.d, rot[m] = c0 < p.r;     // d and r are multiples of 4: a lane's 4 features share their fate
+#pragma unroll
+    for (int e = 0; e < 4; ++e) qc[m][e] = qs[m][e] = cb[m][e] = sb[m][e] = 0.f;
+    if (live[m]) {
+      float x[4];
+      load4<T>(qrow + c0, x);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (rot[m]) {
+          float sn, cs;
+          sincosf(p.freqs[(int64_t)(p.Nk - 1) * p.sfn + c0 + e], &sn, &cs);
+          const float a = softplus_f(x[e]);
+          qc[m][e] = a * cs, qs[m][e] = a * sn;
+          sincosf(p.bias[hk * p.bias_sh + c0 + e], &sb[m][e], &cb[m][e]);
+        } else {
+          qc[m][e] = x[e];
+        }
+      }
+    }
+  }
+
+  float mrun = -CUDART_INF_F, lrun = 0.f, o[DM][4];
+#pragma unroll
+  for (int m = 0; m < DM; ++m)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[m][e] = 0.f;
+
+  for (int j = kb + w; j < ke; j += DEC_WARPS) {
+    float part = 0.f, vv[DM][4];
+#pragma unroll
+    for (int m = 0; m < DM; ++m) {
+      const int c0 = m * 128 + lane * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) vv[m][e] = 0.f;
+      if (!live[m]) continue;
+      float x[4];
+      load4<T>(kbase + (int64_t)j * p.sk.n + c0, x);
+      load4<T>(vbase + (int64_t)j * p.sv.n + c0, vv[m]);
+      if (rot[m]) {
+        float ct[4], stt[4];
+        load4<float>(p.ctab + (int64_t)j * p.r + c0, ct);
+        load4<float>(p.stab + (int64_t)j * p.r + c0, stt);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float a = softplus_fast(x[e]);   // ex2.approx / lg2.approx: 2^-22, a sixth of the instructions
+          const float kc = a * (ct[e] * cb[m][e] - stt[e] * sb[m][e]);
+          const float ks = a * (stt[e] * cb[m][e] + ct[e] * sb[m][e]);
+          part = fmaf(qc[m][e], kc, fmaf(qs[m][e], ks, part));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) part = fmaf(qc[m][e], x[e], part);
+      }
+    }
+    const float sc = warp_sum(part) * p.scale;
+    if (mask && !mask[(int64_t)j * p.msn]) continue;   // warp-uniform
+    const float mnew = fmaxf(mrun, sc);
+    const float alpha = expf(mrun - mnew), pj = expf(sc - mnew);
+    lrun = lrun * alpha + pj;
+    mrun = mnew;
+#pragma unroll
+    for (int m = 0; m < DM; ++m)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[m][e] = fmaf(pj, vv[m][e], o[m][e] * alpha);
+  }
+
+  // merge the 8 warps of the CTA, then hand the partial to the cross-split combine
+#pragma unroll
+  for (int m = 0; m < DM; ++m)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) red_o[w][m * 128 + lane * 4 + e] = o[m][e];
+  if (lane == 0) red_ml[w][0] = mrun, red_ml[w][1] = lrun;
+  __syncthreads();
+  float M = -CUDART_INF_F;
+#pragma unroll
+  for (int ww = 0; ww < DEC_WARPS; ++ww) M = fmaxf(M, red_ml[ww][0]);
+  const int64_t slot = (int64_t)u * p.nsplit + blockIdx.x;     // Nq = 1
+  for (int c = tid; c < p.HDP; c += DEC_WARPS * 32) {
+    float acc = 0.f;
+    if (c < DM * 128)
+#pragma unroll
+      for (int ww = 0; ww < DEC_WARPS; ++ww)
+        acc += red_ml[ww][0] == -CUDART_INF_F ? 0.f : red_o[ww][c] * expf(red_ml[ww][0] - M);
+    p.part_o[slot * p.HDP + c] = acc;
+  }
+  if (tid == 0) {
+    float L = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < DEC_WARPS; ++ww) L += red_ml[ww][0] == -CUDART_INF_F ? 0.f : red_ml[ww][1] * expf(red_ml[ww][0] - M);
+    p.part_ml[slot * 2] = M, p.part_ml[slot * 2 + 1] = L;
+  }
+}
+
+static bool decode_applies(const PopeAttnArgs& a) {
+  const PopeShape& s = a.shape;
+  if (s.Nq != 1 || a.causal || s.Nk < 1024 || s.d > 256 || s.d % 4 != 0 || s.r % 4 != 0) return false;
+  if (s.r > 0 && (a.embed.sf.b != 0 || a.embed.sf.h != 0)) return false;
+  const int esz = s.dtype == POPE_F32 ? 4 : 2;
+  auto ok = [&](const void* ptr, const PopeStride3& st) {
+    const int al = 4 * esz;   // 4 features per lane
+    return reinterpret_cast<uintptr_t>(ptr) % al == 0 && (st.b * esz) % al == 0 && (st.h * esz) % al == 0 && (st.n * esz) % al == 0;
+  };
+  return ok(a.q, a.sq) && ok(a.k, a.sk) && ok(a.v, a.sv);
+}
+
+static void decode_plan(const PopeShape& s, int& nsplit, int& split_len) {
+  const int64_t units = (int64_t)s.B * s.H;
+  int want = (int)((8 * 148 + units - 1) / units);      // about eight CTAs per SM in flight
+  const int maxs = s.Nk / 256;
+  nsplit = want < maxs ? want : maxs;
+  if (nsplit < 1) nsplit = 1;
+  split_len = (s.Nk + nsplit - 1) / nsplit;
+  nsplit = (s.Nk + split_len - 1) / split_len;
+}
+
+cudaError_t launch_trig_table_f32(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, cudaStream_t st);
+
 // ---- forward launch --------------------------------------------------------------------------
 static void plan_split(const PopeShape& s, int causal, int& nsplit, int& split_len) {
   // Few query tiles against a long key range: split the keys so every SM has work.
@@ -283,6 +455,13 @@ static void plan_split(const PopeShape& s, int causal, int& nsplit, int& split_l
 }
 
 size_t attn_fwd_simt_workspace(const PopeAttnArgs& a) {
+  if (decode_applies(a)) {
+    int dns, dsl;
+    decode_plan(a.shape, dns, dsl);
+    const int HDP = simt_dch(a.shape.d) * 32;
+    const size_t slots = (size_t)a.shape.B * a.shape.H * dns;
+    return slots * (HDP + 2) * sizeof(float) + 256 + (size_t)a.shape.Nk * a.shape.r * 2 * sizeof(float);
+  }
   int ns, sl;
   plan_split(a.shape, a.causal, ns, sl);
   if (ns == 1) return 0;
@@ -321,8 +500,39 @@ static cudaError_t launch_attn_fwd(const PopeAttnArgs& a, cudaStream_t st) {
 }
 
 template <typename T>
+static cudaError_t launch_decode(const PopeAttnArgs& a, cudaStream_t st) {
+  const PopeShape& s = a.shape;
+  DecodeP p = {};
+  p.H = s.H, p.Hk = s.Hk, p.Nk = s.Nk, p.d = s.d, p.r = s.r, p.scale = a.softmax_scale;
+  decode_plan(s, p.nsplit, p.split_len);
+  p.q = a.q, p.k = a.k, p.v = a.v, p.sq = a.sq, p.sk = a.sk, p.sv = a.sv;
+  p.freqs = a.embed.freqs, p.bias = a.embed.bias, p.sfn = a.embed.sf.n, p.bias_sh = a.embed.bias_stride_h;
+  p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
+  p.HDP = simt_dch(s.d) * 32;
+  const size_t slots = (size_t)s.B * s.H * p.nsplit;
+  p.part_o = (float*)a.workspace;
+  p.part_ml = p.part_o + slots * p.HDP;
+  float* ctab = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.workspace) + (slots * (p.HDP + 2) * sizeof(float) + 255) / 256 * 256);
+  float* stab = ctab + (size_t)s.Nk * s.r;
+  p.ctab = ctab, p.stab = stab;
+  cudaError_t e = cudaSuccess;
+  if (s.r > 0 && (e = launch_trig_table_f32(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, ctab, stab, st)) != cudaSuccess) return e;
+  dim3 grid(p.nsplit, s.B * s.H);
+  if (s.d <= 128) attn_decode_kernel<T, 1><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+  else attn_decode_kernel<T, 2><<<grid, DEC_WARPS * 32, 0, st>>>(p);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  AttnP c = {};
+  c.B = s.B, c.H = s.H, c.Nq = 1, c.d = s.d, c.nsplit = p.nsplit, c.so = a.so, c.o = a.out, c.lse = a.lse;
+  c.part_o = p.part_o, c.part_ml = p.part_ml;
+  const int64_t rows = (int64_t)s.B * s.H;
+  attn_fwd_combine_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(c, p.HDP);
+  return cudaGetLastError();
+}
+
+template <typename T>
 static cudaError_t attn_fwd_dch(const PopeAttnArgs& a, cudaStream_t st) {
   if (a.shape.d > 256) return cudaErrorInvalidValue;
+  if (decode_applies(a)) return launch_decode<T>(a, st);
   switch (simt_dch(a.shape.d)) {
     case 1: return launch_attn_fwd<T, 1>(a, st);
     case 2: return launch_attn_fwd<T, 2>(a, st);

@@ -40,23 +40,6 @@ template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
   return __half22float2(*reinterpret_cast<__half2*>(&u));
 }
 
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ float lg2_approx(float x) {
-  float y;
-  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-// softplus(x) = max(x,0) + log1p(exp(-|x|)); beyond x = 20 the second term is below 2.1e-9,
-// i.e. the reference's cut-over to the identity is reproduced to fp32 rounding.
-__device__ __forceinline__ float softplus_fast(float x) {
-  const float t = ex2_approx(-fabsf(x) * 1.4426950408889634f);
-  return fmaxf(x, 0.f) + lg2_approx(1.f + t) * 0.6931471805599453f;
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));

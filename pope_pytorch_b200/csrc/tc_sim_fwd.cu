@@ -45,6 +45,12 @@ __global__ void pope_trig_table_f32_kernel(const float* freqs, int64_t sfn, int 
   sincosf(freqs[pos * sfn + c], &stab[idx], &ctab[idx]);
 }
 
+cudaError_t launch_trig_table_f32(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, cudaStream_t st) {
+  const int64_t total = (int64_t)n * r;
+  pope_trig_table_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(freqs, sfn, n, r, ctab, stab);
+  return cudaGetLastError();
+}
+
 template <typename T> struct Load8;
 template <> struct Load8<float> {
   static __device__ __forceinline__ void run(const float* p, float (&x)[8]) {
