@@ -2,7 +2,7 @@
 namespace pope {
 
 template <int D, typename T>
-__global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int KD = D + p.r, KSTEPS = KD >> 4;
   uint8_t* Ks = smem;                          // [KD/8][128][16 B]  resident K' (phase fk + bias)
@@ -13,161 +13,208 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
   uint8_t* Ps = Gb + 2 * VBUF;                 // [8 chunks][128][16 B] P^T  (A operand, K = 64 queries)
   uint8_t* Ds = Ps + BQ * BT * 2;              // [8 chunks][128][16 B] dS^T
   float* rowstat = reinterpret_cast<float*>(Ds + BQ * BT * 2);  // 2 bufs x (64 lse*log2e, 64 delta)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(rowstat + 2 * 128);   // [0] scores ready, [1] accumulation done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rowstat + 2 * 128);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BB_COUNT + 1);
   float* bias_cb = reinterpret_cast<float*>(Ps);   // only needed while the resident K' is built: borrows the P^T tile
   float* bias_sb = bias_cb + 128;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.Hk, hk = u % p.Hk;
   const int j0 = blockIdx.x * BQ;
   const int qoff = p.Nk - p.Nq;
   const int groups = p.H / p.Hk;
   const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
-  const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
-  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
   const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
+  const T* tab = static_cast<const T*>(p.table);
 
-  if (warp == 0) {
+  if (warp == BWD_M_WARP) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(&bars[0], 1), mbar_init(&bars[1], 1);
+    mbar_init(&bars[BB_FULL], BWD_P_WARPS), mbar_init(&bars[BB_FULL + 1], BWD_P_WARPS);
+    mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1), mbar_init(&bars[BB_ACC + 1], 1);
+    mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
+    mbar_init(&bars[BB_RESIDENT], BWD_E_WARPS);
     mbar_init_fence();
   }
-  load_bias_trig(biasr, p.r, 1.f, bias_cb, bias_sb, tid);
-  __syncthreads();
-  stage_xform<D, BQ, T, true>(kbase, p.sk.n, j0, p.Nk, static_cast<const T*>(p.table), p.Nk, 0, p.r, bias_cb, bias_sb, Ks, tid);
-  stage_plain<D, BQ, T>(vbase, p.sv.n, j0, p.Nk, Vs, tid);
-
   // query tiles: under the causal mask rows i < j0 see none of this CTA's keys
   const int m_begin = p.causal ? (j0 / BT) * BT : 0;
   const int tiles_per_group = m_begin < p.Nq ? (p.Nq - m_begin + BT - 1) / BT : 0;
   const int T_tiles = tiles_per_group * groups;
-
-  auto stage = [&](int jt) {
-    const int buf = jt & 1, g = jt / tiles_per_group, m0 = m_begin + (jt % tiles_per_group) * BT;
-    const int h = g * p.Hk + hk;
-    const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
-    const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
-    stage_xform<D, BT, T, false>(qbase, p.sq.n, m0, p.Nq, static_cast<const T*>(p.table), p.Nk, qoff, p.r, nullptr, nullptr, Qb + buf * KBUF, tid);
-    stage_plain<D, BT, T>(gbase, p.sdo.n, m0, p.Nq, Gb + buf * VBUF, tid);
-    if (tid < BT) {
-      const int gi = m0 + tid;
-      const int64_t uq = (int64_t)(b * p.H + h) * p.Nq + gi;
-      const float lse_i = gi < p.Nq ? p.lse[uq] : -CUDART_INF_F;
-      rowstat[buf * 128 + tid] = lse_i == -CUDART_INF_F ? CUDART_INF_F : lse_i * LOG2E;   // +inf: P becomes exactly 0
-      rowstat[buf * 128 + 64 + tid] = gi < p.Nq ? p.delta[uq] : 0.f;
-    }
+  // tile j -> (query head of the group, first query row); rotated per CTA like the dq kernel's key order
+  const int rot = tiles_per_group > 0 ? (u * 5 + blockIdx.x * 3) % tiles_per_group : 0;
+  auto tile_head = [&](int j) { return (j / tiles_per_group) * p.Hk + hk; };
+  auto tile_start = [&](int j) {
+    int t = j % tiles_per_group + rot;
+    if (t >= tiles_per_group) t -= tiles_per_group;
+    return m_begin + t * BT;
   };
-
-  const int row = tid & 127, half = tid >> 7;          // thread = (key row, 32-query half)
-  const int gj = j0 + row;
-  const bool key_ok = gj < p.Nk && (!maskb || maskb[(int64_t)gj * p.msn] != 0);
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   bool failed = false;
-
-  if (T_tiles > 0) stage(0);
-  fence_async_smem();
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   // TMEM columns: S^T [0,64), dP^T [64,128), dV [128, 128+D), dK' [256, 256+KD)
-  const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
-  const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
-  const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
-  const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
-  const uint32_t ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
 
-  auto issue_scores = [&](int jt) {
-    const int buf = jt & 1;
-    for (int ks = 0; ks < KSTEPS; ++ks)
-      mma_ss(tmem, smem_desc(ks_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
-             smem_desc(qb_addr + buf * KBUF + ks * 2 * CS64, CS64, 128), idesc_s, ks > 0);
-    for (int ks = 0; ks < D / 16; ++ks)
-      mma_ss(tmem + 64, smem_desc(vs_addr + ks * 2 * (BQ * 16), BQ * 16, 128),
-             smem_desc(gb_addr + buf * VBUF + ks * 2 * CS64, CS64, 128), idesc_s, ks > 0);
-    mma_commit(&bars[0]);
-  };
-  if (tid == 0 && T_tiles > 0) issue_scores(0);
+  if (warp >= BWD_E_WARPS && warp < BWD_M_WARP) {
+    // =============================== producers: Q' and dO tiles, lse / delta ====================
+    const int pw = warp - BWD_E_WARPS, ptid = tid - BWD_E_WARPS * 32;
+    for (int j = 0; j < T_tiles; ++j) {
+      const int buf = j & 1, m0 = tile_start(j), h = tile_head(j);
+      const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
+      const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
+      auto wait_free = [&]() {   // buffer j & 1 was last read by the accumulation step of tile j-2
+        if (j >= 2 && !failed) failed = !mbar_wait(&bars[BB_ACC + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+      };
+      produce_tile<D, T>(qbase, p.sq.n, gbase, p.sdo.n, m0, p.Nq, tab, p.Nk, qoff, p.r, Qb + buf * KBUF, Gb + buf * VBUF,
+                         pw, lane, wait_free);
+      if (ptid < BT) {
+        const int gi = m0 + ptid;
+        const int64_t uq = (int64_t)(b * p.H + h) * p.Nq + gi;
+        const float lse_i = gi < p.Nq ? p.lse[uq] : -CUDART_INF_F;
+        rowstat[buf * 128 + ptid] = lse_i == -CUDART_INF_F ? CUDART_INF_F : lse_i * LOG2E;   // +inf: P becomes exactly 0
+        rowstat[buf * 128 + 64 + ptid] = gi < p.Nq ? p.delta[uq] : 0.f;
+      }
+      fence_async_smem();
+      warp_arrive(&bars[BB_FULL + buf], lane);
+    }
+  } else if (warp == BWD_M_WARP) {
+    // =============================== MMA issue ===================================================
+    if (lane == 0 && T_tiles > 0) {
+      const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
+      const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
+      const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
+      const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
+      const uint32_t ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
+      auto issue_scores = [&](int jt) {
+        const int buf = jt & 1;
+        uint64_t ad = smem_desc(ks_addr, BQ * 16, 128), bd = smem_desc(qb_addr + buf * KBUF, CS64, 128);
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          mma_ss(tmem, ad, bd, idesc_s, ks > 0);
+          ad += (2 * BQ * 16) >> 4, bd += (2 * CS64) >> 4;
+        }
+        ad = smem_desc(vs_addr, BQ * 16, 128), bd = smem_desc(gb_addr + buf * VBUF, CS64, 128);
+        for (int ks = 0; ks < D / 16; ++ks) {
+          mma_ss(tmem + 64, ad, bd, idesc_s, ks > 0);
+          ad += (2 * BQ * 16) >> 4, bd += (2 * CS64) >> 4;
+        }
+        mma_commit(&bars[BB_SCORES]);
+      };
+      if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
+      if (!mbar_wait(&bars[BB_FULL], 0, WAIT_LIMIT)) failed = true;
+      fence_after_sync();
+      issue_scores(0);
+      for (int j = 0; j < T_tiles; ++j) {
+        const int buf = j & 1;
+        if (j + 1 < T_tiles) {
+          if (!failed) failed = !mbar_wait(&bars[BB_FULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
+          if (!failed) failed = !mbar_wait(&bars[BB_CONSUMED], j & 1, WAIT_LIMIT);
+          fence_after_sync();
+          issue_scores(j + 1);
+        }
+        if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
+        fence_after_sync();
+        uint64_t pa = smem_desc(ps_addr, BQ * 16, 128), da = smem_desc(ds_addr, BQ * 16, 128);
+        uint64_t gd = smem_desc(gb_addr + buf * VBUF, 128, CS64), qd = smem_desc(qb_addr + buf * KBUF, 128, CS64);
+#pragma unroll
+        for (int ks = 0; ks < BT / 16; ++ks) {
+          mma_ss(tmem + 128, pa, gd, idesc_v, (j > 0 || ks > 0) ? 1u : 0u);
+          mma_ss(tmem + 256, da, qd, idesc_k, (j > 0 || ks > 0) ? 1u : 0u);
+          pa += (2 * BQ * 16) >> 4, da += (2 * BQ * 16) >> 4, gd += (2 * 128) >> 4, qd += (2 * 128) >> 4;
+        }
+        mma_commit(&bars[BB_ACC + buf]);
+      }
+      if (failed) atomicOr(p.status, 1u);
+    }
+    __syncwarp();
+  }
+  if (warp >= BWD_E_WARPS) {
+    fence_before_sync();
+    __syncthreads();
+    if (warp == BWD_M_WARP) tmem_dealloc(tmem, 512);
+    return;
+  }
+
+  // =============================== elementwise warps ================================================
+  const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
+  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
+  load_bias_trig(biasr, p.r, 1.f, bias_cb, bias_sb, tid);
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  stage_xform<D, BQ, T, true>(kbase, p.sk.n, j0, p.Nk, tab, p.Nk, 0, p.r, bias_cb, bias_sb, Ks, tid);
+  stage_plain<D, BQ, T>(vbase, p.sv.n, j0, p.Nk, Vs, tid);
+  asm volatile("bar.sync 1, 256;" ::: "memory");   // the bias trig borrowed the P^T tile: everyone is done reading it
+  fence_async_smem();
+  warp_arrive(&bars[BB_RESIDENT], lane);
+
+  const int row = tid & 127, half = tid >> 7;          // thread = (key row, 32-query half)
+  const int gj = j0 + row;
+  const bool key_ok = gj < p.Nk && (!maskb || maskb[(int64_t)gj * p.msn] != 0);
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
   for (int j = 0; j < T_tiles; ++j) {
     const int buf = j & 1;
-    const int m0 = m_begin + (j % tiles_per_group) * BT;
-    if (!failed) failed = !mbar_wait(&bars[0], j & 1, WAIT_LIMIT);
+    const int m0 = tile_start(j);
+    if (!failed) failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the lse / delta read
+    if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
     fence_after_sync();
-    uint32_t sv[32], dv[32];
-    tmem_ld32(tmem + lane_base + half * 32, sv);
-    tmem_ld32(tmem + lane_base + 64 + half * 32, dv);
-    tmem_ld_wait();
-    // P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
-    if (j >= 1 && !failed) failed = !mbar_wait(&bars[1], (j - 1) & 1, WAIT_LIMIT);
     const float* st = rowstat + buf * 128 + half * 32;
     // interior tile for this warp: every key row valid and (causal) every key at or before every query column;
     // out-of-range queries and rows without any visible key carry lse = +inf, which makes P exactly 0
     const int gj_hi = j0 + (warp & 3) * 32 + 31, gi_lo = m0 + half * 32;
     const bool interior = __all_sync(0xffffffffu, key_ok) && (!p.causal || gj_hi <= gi_lo);
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-      const float4 la = *reinterpret_cast<const float4*>(st + cc * 8), lb = *reinterpret_cast<const float4*>(st + cc * 8 + 4);
-      const float4 da = *reinterpret_cast<const float4*>(st + 64 + cc * 8), db = *reinterpret_cast<const float4*>(st + 64 + cc * 8 + 4);
-      const float l2v[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-      const float dlv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-      uint32_t pw[4], dw[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float pv[2], dsv[2];
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const int col = cc * 8 + e * 2 + t;            // query column within this thread's half
-          float pr = ex2_approx(fmaf(__uint_as_float(sv[col]), p.scale_log2, -l2v[e * 2 + t]));
-          if (!interior) pr = (key_ok && (!p.causal || gj <= gi_lo + col)) ? pr : 0.f;
-          pv[t] = pr;
-          dsv[t] = pr * (__uint_as_float(dv[col]) - dlv[e * 2 + t]) * p.scale;
-        }
-        pw[e] = pack2<T>(pv[0], pv[1]);
-        dw[e] = pack2<T>(dsv[0], dsv[1]);
+    for (int hh = 0; hh < 2; ++hh) {   // 16 query columns at a time
+      uint32_t sv[16], dv[16];
+      tmem_ld16(tmem + lane_base + half * 32 + hh * 16, sv);
+      tmem_ld16(tmem + lane_base + 64 + half * 32 + hh * 16, dv);
+      tmem_ld_wait();
+      if (hh == 1) {   // every score of this tile is in registers
+        fence_before_sync();
+        warp_arrive(&bars[BB_CONSUMED], lane);
+      } else if (j >= 1 && !failed) {
+        // the P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
+        failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
       }
-      const int chunk = half * 4 + cc;
-      *reinterpret_cast<uint4*>(Ps + chunk * (BQ * 16) + row * 16) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-      *reinterpret_cast<uint4*>(Ds + chunk * (BQ * 16) + row * 16) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int cq = hh * 16 + cc * 8;   // first query column of this 8-wide chunk within the thread's half
+        const float4 la = *reinterpret_cast<const float4*>(st + cq), lb = *reinterpret_cast<const float4*>(st + cq + 4);
+        const float4 da = *reinterpret_cast<const float4*>(st + 64 + cq), db = *reinterpret_cast<const float4*>(st + 64 + cq + 4);
+        const float l2v[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+        const float dlv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+        uint32_t pw[4], dw[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int cl = cc * 8 + e * 2 + t;          // index into sv / dv
+            float pr = ex2_approx(fmaf(__uint_as_float(sv[cl]), p.scale_log2, -l2v[e * 2 + t]));
+            if (!interior) pr = (key_ok && (!p.causal || gj <= gi_lo + cq + e * 2 + t)) ? pr : 0.f;
+            pv[t] = pr;
+            dsv[t] = pr * (__uint_as_float(dv[cl]) - dlv[e * 2 + t]) * p.scale;
+          }
+          pw[e] = pack2<T>(pv[0], pv[1]);
+          dw[e] = pack2<T>(dsv[0], dsv[1]);
+        }
+        const int chunk = half * 4 + hh * 2 + cc;
+        *reinterpret_cast<uint4*>(Ps + chunk * (BQ * 16) + row * 16) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        *reinterpret_cast<uint4*>(Ds + chunk * (BQ * 16) + row * 16) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+      }
     }
     fence_async_smem();
-    fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      fence_after_sync();
-      for (int ks = 0; ks < BT / 16; ++ks) {
-        const uint64_t pa = smem_desc(ps_addr + ks * 2 * (BQ * 16), BQ * 16, 128);
-        const uint64_t da = smem_desc(ds_addr + ks * 2 * (BQ * 16), BQ * 16, 128);
-        mma_ss(tmem + 128, pa, smem_desc(gb_addr + buf * VBUF + ks * 2 * 128, 128, CS64), idesc_v,
-               (j > 0 || ks > 0) ? 1u : 0u);
-        mma_ss(tmem + 256, da, smem_desc(qb_addr + buf * KBUF + ks * 2 * 128, 128, CS64), idesc_k,
-               (j > 0 || ks > 0) ? 1u : 0u);
-      }
-      mma_commit(&bars[1]);
-    }
-    if (j + 1 < T_tiles) {
-      stage(j + 1);  // buffers 1-buf were last read by the accumulation step of tile j-1 (waited for above)
-      fence_async_smem();
-      fence_before_sync();
-      __syncthreads();
-      if (tid == 0) {
-        fence_after_sync();
-        issue_scores(j + 1);
-      }
-    }
+    warp_arrive(&bars[BB_GRAD], lane);
   }
 
   // ---- epilogue ---------------------------------------------------------------------------------
-  if (T_tiles > 0 && !failed) failed = !mbar_wait(&bars[1], (T_tiles - 1) & 1, WAIT_LIMIT);
+  if (T_tiles > 0 && !failed)
+    failed = !mbar_wait(&bars[BB_ACC + ((T_tiles - 1) & 1)], ((T_tiles - 1) >> 1) & 1, WAIT_LIMIT);
   fence_after_sync();
-  __syncthreads();                       // all MMAs done: the streamed buffers can be reused
+  asm volatile("bar.sync 1, 256;" ::: "memory");   // every MMA is done: the streamed buffers can be reused
   float* red = reinterpret_cast<float*>(Qb);   // [r] per-CTA sum of the key-phase gradient
   for (int c = tid; c < p.r; c += 256) red[c] = 0.f;
-  __syncthreads();
+  asm volatile("bar.sync 1, 256;" ::: "memory");
   {
     constexpr int HW = D / 2;
     const uint32_t accv = tmem + lane_base + 128, acck = tmem + lane_base + 256;
@@ -226,13 +273,12 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
     }
   }
   if (p.dbias && p.r > 0) {
-    __syncthreads();
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     for (int c = tid; c < p.r; c += 256) atomicAdd(p.dbias + hk * p.dbias_sh + c, red[c]);
   }
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  __syncthreads();   // the issuing warp frees the tensor memory after this barrier
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -284,7 +330,7 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const int KD = s.d + s.r;
   const size_t streamed = 2 * (size_t)(KD / 8) * CS64 + 2 * (size_t)(D / 8) * CS64;
   size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + (BB_COUNT + 1) * 8 + 4 * 4 + 16 + 1024;
-  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + 2 * BQ * BT * 2 + 256 * 4 + 2 * 8 + 16 + 16;
+  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + 2 * BQ * BT * 2 + 256 * 4 + (BB_COUNT + 1) * 8 + 16 + 16;
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;
@@ -292,7 +338,7 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   if ((e = cudaFuncSetAttribute(attn_bwd_dkdv_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k)) != cudaSuccess) return e;
   attn_bwd_dq_tc_kernel<D, T><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), BWD_THREADS, smem_q, st>>>(p);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), 256, smem_k, st>>>(p);
+  attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, st>>>(p);
   return cudaGetLastError();
 }
 
