@@ -17,7 +17,8 @@ from typing import Optional
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libpope_b200.so")
+# POPE_B200_LIBRARY points the loader at another build of the same ABI (e.g. one compiled with debug defines)
+LIB_PATH = os.environ.get("POPE_B200_LIBRARY") or os.path.join(_PKG_DIR, "libpope_b200.so")
 
 OP_SIM_FWD, OP_SIM_BWD, OP_ATTN_FWD, OP_ATTN_BWD = 0, 1, 2, 3
 _DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}

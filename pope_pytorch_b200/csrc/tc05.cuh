@@ -39,12 +39,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
       : "memory");
   return ok != 0;
 }
+#ifndef POPE_WAIT_HINT_NS
+#define POPE_WAIT_HINT_NS 10000u
+#endif
 // Bounded wait: gives up after `limit` parked tries (about limit x 10 us in the worst case) and returns
 // false; the caller records the failure in a status word and unwinds.  A healthy wait takes microseconds.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 17)) {
   for (uint32_t i = 0; i < limit; ++i)
-    if (mbar_try_wait(bar, parity, 10000u)) return true;
+    if (mbar_try_wait(bar, parity, POPE_WAIT_HINT_NS)) return true;
   return false;
+}
+
+// ---- TMA: tiled bulk tensor load into this CTA's shared memory (no multicast) -------------------
+// `tmap` is the address of a CUtensorMap kernel parameter (__grid_constant__).  The innermost coordinate
+// times the element size must be a multiple of 16 bytes.  Rows outside the tensor arrive as zeros.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Untiled bulk copy global -> this CTA's shared memory; both addresses and the size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // ---- fences ----------------------------------------------------------------------------------

@@ -14,10 +14,23 @@
 // operand is resident.  A streamed tile in shared memory serves two MMAs: as the K-major B
 // operand of the score product and, re-described as MN-major, as the B operand of the gradient
 // product -- the 8x16-byte core-matrix layout is symmetric under that exchange.
+#include <cstdio>
+
 #include "kernels.h"
 #include "tc_common.cuh"
 
 namespace pope {
+
+// Optional phase timers of one CTA (compile with -DPOPE_DBG_PHASES): clock64 deltas per phase, printed at the end.
+#ifdef POPE_DBG_PHASES
+#define PH_DECL long long _t0 = clock64(), _t1; long long _acc[8] = {}
+#define PH(i) do { _t1 = clock64(); _acc[i] += _t1 - _t0; _t0 = _t1; } while (0)
+#define PH_PRINT(tag, n) do { if (blockIdx.x == 7 && blockIdx.y == 3) printf("%s tiles %d: %lld %lld %lld %lld %lld %lld %lld %lld\n", tag, n, _acc[0] / (n), _acc[1] / (n), _acc[2] / (n), _acc[3] / (n), _acc[4] / (n), _acc[5] / (n), _acc[6] / (n), _acc[7] / (n)); } while (0)
+#else
+#define PH_DECL
+#define PH(i)
+#define PH_PRINT(tag, n)
+#endif
 
 struct TcBwdP {
   int H, Hk, Nq, Nk, r, causal;
@@ -28,6 +41,11 @@ struct TcBwdP {
   const float *freqs, *bias, *lse, *delta;
   int64_t sfn, bias_sh, dbias_sh;
   const void* table;   // cos / sin tables in the dtype of q, k, v
+  const uint8_t* kimg;   // expanded K' image tiles, (B * Hk) units (no phase bias)
+  const uint8_t* qimg;   // expanded Q' image tiles, (B * H) units (no phase bias)
+  const uint8_t* vimg;   // V re-laid as image tiles, (B * Hk) units
+  const uint8_t* gimg;   // dO re-laid as image tiles, (B * H) units
+  const float* rowstat;  // per 64-query tile of every (batch, head): 64 x lse * log2(e) (+inf for empty rows), 64 x delta
   const uint8_t* mask;
   int64_t msb, msn;
   float *dfreqs, *dbias;
@@ -40,14 +58,15 @@ constexpr int BT = 64;   // streamed rows per step
 // ================================================================================================
 // dq
 // ================================================================================================
-// Warp roles of both backward kernels (17 warps, 544 threads)
-constexpr int BWD_E_WARPS = 8;     // warps 0-7  : elementwise work (P, dS) and the epilogue; build the resident operands
-constexpr int BWD_P_WARPS = 8;     // warps 8-15 : expand / copy the streamed tiles
-constexpr int BWD_M_WARP = 16;     // warp 16    : issues every MMA
+// Warp roles of both backward kernels (10 warps, 320 threads)
+constexpr int BWD_E_WARPS = 8;     // warps 0-7 : elementwise work (P, dS) and the epilogue; build the resident operands
+constexpr int BWD_L_WARP = 8;      // warp 8    : one lane issues the bulk / tensor copies of the streamed tiles
+constexpr int BWD_M_WARP = 9;      // warp 9    : one lane issues every MMA; owns the TMEM allocation
 constexpr int BWD_THREADS = 32 * (BWD_M_WARP + 1);
+constexpr int BCS = BT * 16;       // bytes of one 16-byte chunk column of a streamed tile
 
 // mbarrier slots shared by both backward kernels
-enum { BB_FULL = 0,      // [2] 8 producer warps: streamed tile j is in buffer j & 1
+enum { BB_FULL = 0,      // [2] streamed tile j has landed in buffer j & 1 (transaction bytes of all its copies)
        BB_SCORES = 2,    // tcgen05.commit: the two score products of the current tile are in TMEM
        BB_ACC = 3,       // [2] tcgen05.commit: the accumulation step of tile j has finished (slot j & 1; a waiter
                          //     may lag two tiles behind, which a single barrier's phase parity cannot express)
@@ -61,57 +80,17 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   if (lane == 0) mbar_arrive(bar);
 }
 
-// All eight producer warps share every tile.  (Two groups of four on alternate tiles were measured slower:
-// 2.34 ms against 1.83 ms for the dq kernel at the training shape.)
-constexpr int BWD_PG_WARPS = BWD_P_WARPS;
-
-// One streamed tile by the producer warps: BT rows of X expanded with the phase table (rows pos0 + row) into Xb,
-// BT rows of Y copied into Yb, in batches whose loads are all issued before their first store; `wait_free`
-// runs after the first batch of loads and before the first shared-memory store.
-template <int D, typename T, typename Wait>
-__device__ __forceinline__ void produce_tile(const T* xbase, int64_t xsn, const T* ybase, int64_t ysn, int row0, int nrows,
-                                             const T* tab, int tab_n, int pos0, int r, uint8_t* Xb, uint8_t* Yb, int pw,
-                                             int lane, Wait wait_free) {
-  constexpr int NT = (BT * D / 256) / BWD_PG_WARPS;   // warp tasks (32 chunks of 16 B) per warp and operand
-  constexpr int NB = NT % 4 == 0 ? 4 : (NT % 3 == 0 ? 3 : 2);
-  const T* tab_s = tab + (int64_t)tab_n * r;
-#pragma unroll
-  for (int b0 = 0; b0 < NT; b0 += NB) {
-    XTask xt[NB];
-    uint4 yr[NB];
-#pragma unroll
-    for (int it = 0; it < NB; ++it) {
-      const int wt = pw + BWD_PG_WARPS * (b0 + it);
-      xtask_load<D, BT, T>(xt[it], xbase, xsn, row0, nrows, tab, tab_s, pos0, r, wt, lane);
-      int row, c;
-      stage_coords<BT, D / 8>(wt, lane, row, c);
-      yr[it] = make_uint4(0, 0, 0, 0);
-      if (row0 + row < nrows) yr[it] = __ldg(reinterpret_cast<const uint4*>(ybase + (int64_t)(row0 + row) * ysn + c * 8));
-    }
-    if (b0 == 0) wait_free();
-#pragma unroll
-    for (int it = 0; it < NB; ++it) {
-      const int wt = pw + BWD_PG_WARPS * (b0 + it);
-      xtask_store_packed<D, BT, T>(xt[it], r, Xb, wt, lane);
-      int row, c;
-      stage_coords<BT, D / 8>(wt, lane, row, c);
-      *reinterpret_cast<uint4*>(Yb + c * CS64 + row * 16) = yr[it];
-    }
-  }
-}
-
 template <int D, typename T>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int KD = D + p.r, KSTEPS = KD >> 4;
   uint8_t* Qs = smem;                          // [KD/8][128][16 B]  resident Q'
   uint8_t* Gs = Qs + BQ * KD * 2;              // [D/8][128][16 B]   resident dO
-  const int KBUF = (KD / 8) * CS64, VBUF = (D / 8) * CS64;  // one streamed buffer (padded chunk stride)
-  uint8_t* Ks = Gs + BQ * D * 2;               // 2 x [KD/8][64][16 B]
-  uint8_t* Vs = Ks + 2 * KBUF;                 // 2 x [D/8][64][16 B]
+  const int KBUF = (KD / 8) * BCS, VBUF = (D / 8) * BCS;  // one streamed buffer
+  uint8_t* Ks = Gs + BQ * D * 2;               // 2 x [KD/8][64][16 B]  (one K' image tile each)
+  uint8_t* Vs = Ks + 2 * KBUF;                 // 2 x [D/8][64][16 B]   (one V image tile each)
   uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);
-  uint32_t* kbits = reinterpret_cast<uint32_t*>(bars + BB_COUNT + 1);  // [2 bufs][2 words]
-  uint32_t* tmem_slot = kbits + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BB_COUNT + 1);
   float* bias_cb = reinterpret_cast<float*>(tmem_slot + 4);
   float* bias_sb = bias_cb + 128;
 
@@ -128,7 +107,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(&bars[BB_FULL], BWD_PG_WARPS), mbar_init(&bars[BB_FULL + 1], BWD_PG_WARPS);
+    mbar_init(&bars[BB_FULL], 1), mbar_init(&bars[BB_FULL + 1], 1);
     mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1), mbar_init(&bars[BB_ACC + 1], 1);
     mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
     mbar_init(&bars[BB_RESIDENT], BWD_E_WARPS);
@@ -137,8 +116,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   int n_end = p.Nk;
   if (p.causal) n_end = min(n_end, min(i0 + BQ, p.Nq));
   const int T_tiles = (n_end + BT - 1) / BT;
-  // Key tiles are visited in an order rotated per unit: the CTAs resident at one time belong to different
-  // units and would otherwise all ask L2 for the same phase-table lines at the same moment.
+  // Key tiles are visited in an order rotated per unit, which spreads the CTAs resident at one time over
+  // different image tiles.
   const int rot = (u * 5 + blockIdx.x * 3) % T_tiles;
   auto tile_start = [&](int j) { int t = j + rot; if (t >= T_tiles) t -= T_tiles; return t * BT; };
   bool failed = false;
@@ -148,29 +127,23 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   const uint32_t tmem = *tmem_slot;
   // TMEM columns: S [0,64), dP [64,128), dS (bf16 pairs) [128,160), dQ' [256, 256+KD)
 
-  if (warp >= BWD_E_WARPS && warp < BWD_M_WARP) {
-    // =============================== producers: K' and V tiles =================================
-    const int pw = warp - BWD_E_WARPS;
-    const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
-    const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
-    const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
-    for (int j = 0; j < T_tiles; ++j) {
-      const int buf = j & 1, n0 = tile_start(j);
-      // buffer j & 1 was last read by the accumulation step of tile j-2 (its score products finished earlier)
-      auto wait_free = [&]() {
+  if (warp == BWD_L_WARP) {
+    // =============================== copies: K' and V image tiles ================================
+    if (lane == 0) {
+      const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * KBUF;
+      const uint8_t* vimg = p.vimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * VBUF;
+      for (int j = 0; j < T_tiles; ++j) {
+        const int buf = j & 1, n0 = tile_start(j);
+        // buffer j & 1 was last read by the accumulation step of tile j-2 (its score products finished earlier)
         if (j >= 2 && !failed) failed = !mbar_wait(&bars[BB_ACC + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
-      };
-      produce_tile<D, T>(kbase, p.sk.n, vbase, p.sv.n, n0, p.Nk, tab, p.Nk, 0, p.r, Ks + buf * KBUF, Vs + buf * VBUF, pw,
-                         lane, wait_free);
-      if (pw < 2) {
-        const int jk = n0 + pw * 32 + lane;
-        const bool ok = jk < p.Nk && (!maskb || maskb[(int64_t)jk * p.msn] != 0);
-        const uint32_t bits = __ballot_sync(0xffffffffu, ok);
-        if (lane == 0) kbits[buf * 2 + pw] = bits;
+        if (failed) break;
+        mbar_expect_tx(&bars[BB_FULL + buf], KBUF + VBUF);
+        bulk_load(Ks + buf * KBUF, kimg + (int64_t)(n0 / BT) * KBUF, KBUF, &bars[BB_FULL + buf]);
+        bulk_load(Vs + buf * VBUF, vimg + (int64_t)(n0 / BT) * VBUF, VBUF, &bars[BB_FULL + buf]);
       }
-      fence_async_smem();
-      warp_arrive(&bars[BB_FULL + buf], lane);
+      if (failed) atomicOr(p.status, 1u);
     }
+    __syncwarp();
   } else if (warp == BWD_M_WARP) {
     // =============================== MMA issue ===================================================
     if (lane == 0) {
@@ -179,40 +152,51 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       const uint32_t qs_addr = smem_u32(Qs), gs_addr = smem_u32(Gs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
       auto issue_scores = [&](int jt) {
         const int buf = jt & 1;
-        uint64_t ad = smem_desc(qs_addr, BQ * 16, 128), bd = smem_desc(ks_addr + buf * KBUF, CS64, 128);
+        uint64_t ad = smem_desc(qs_addr, BQ * 16, 128), bd = smem_desc(ks_addr + buf * KBUF, BCS, 128);
+#ifndef POPE_DBG_NO_SCORES
         for (int ks = 0; ks < KSTEPS; ++ks) {
           mma_ss(tmem, ad, bd, idesc_s, ks > 0);
-          ad += (2 * BQ * 16) >> 4, bd += (2 * CS64) >> 4;
+          ad += (2 * BQ * 16) >> 4, bd += (2 * BCS) >> 4;
         }
-        ad = smem_desc(gs_addr, BQ * 16, 128), bd = smem_desc(vs_addr + buf * VBUF, CS64, 128);
+        ad = smem_desc(gs_addr, BQ * 16, 128), bd = smem_desc(vs_addr + buf * VBUF, BCS, 128);
         for (int ks = 0; ks < D / 16; ++ks) {
           mma_ss(tmem + 64, ad, bd, idesc_s, ks > 0);
-          ad += (2 * BQ * 16) >> 4, bd += (2 * CS64) >> 4;
+          ad += (2 * BQ * 16) >> 4, bd += (2 * BCS) >> 4;
         }
+#endif
         mma_commit(&bars[BB_SCORES]);
       };
       if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
       if (!mbar_wait(&bars[BB_FULL], 0, WAIT_LIMIT)) failed = true;
       fence_after_sync();
       issue_scores(0);
+      PH_DECL;
       for (int j = 0; j < T_tiles; ++j) {
         const int buf = j & 1;
         if (j + 1 < T_tiles) {
           if (!failed) failed = !mbar_wait(&bars[BB_FULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
+          PH(0);
           if (!failed) failed = !mbar_wait(&bars[BB_CONSUMED], j & 1, WAIT_LIMIT);
+          PH(1);
           fence_after_sync();
           issue_scores(j + 1);
+          PH(2);
         }
         if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
+        PH(3);
         fence_after_sync();
-        uint64_t bd = smem_desc(ks_addr + buf * KBUF, 128, CS64);
+        uint64_t bd = smem_desc(ks_addr + buf * KBUF, 128, BCS);
+#ifndef POPE_DBG_NO_ACC
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks) {
           mma_ts(tmem + 256, tmem + 128 + ks * 8, bd, idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
           bd += (2 * 128) >> 4;
         }
+#endif
         mma_commit(&bars[BB_ACC + buf]);
+        PH(4);
       }
+      PH_PRINT("dq mma [wait full, wait consumed, issue scores, wait grad, issue acc]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -236,17 +220,33 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   }
   const int row = tid & 127, half = tid >> 7;           // thread = (query row, 32-key half)
   const int gi = i0 + row;
+  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   const float lse2 = gi < p.Nq ? p.lse[(int64_t)u * p.Nq + gi] * LOG2E : -CUDART_INF_F;
   const float lse_use = lse2 == -CUDART_INF_F ? 0.f : lse2;
   const float dlt = gi < p.Nq ? p.delta[(int64_t)u * p.Nq + gi] : 0.f;
 
+  PH_DECL;
   for (int j = 0; j < T_tiles; ++j) {
     const int buf = j & 1, n0 = tile_start(j);
-    if (!failed) failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the kbits read
+    // key visibility of this thread's 32-key half (key-padding mask, ragged end): the same for every row
+    uint32_t vis = 0xffffffffu;
+    if (maskb || n0 + BT > p.Nk) {
+      const int jk = n0 + half * 32 + lane;
+      vis = __ballot_sync(0xffffffffu, jk < p.Nk && (!maskb || maskb[(int64_t)jk * p.msn] != 0));
+    }
     if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
     fence_after_sync();
-    uint32_t vis = kbits[buf * 2 + half];
+    PH(0);
+#ifdef POPE_DBG_NO_ELEM
+    if (p.Nq > 0) {
+      fence_before_sync();
+      warp_arrive(&bars[BB_CONSUMED], lane);
+      if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+      warp_arrive(&bars[BB_GRAD], lane);
+      continue;
+    }
+#endif
     if (p.causal) {
       const int lim = gi - (n0 + half * 32);  // columns <= lim visible
       vis &= lim >= 31 ? 0xffffffffu : (lim < 0 ? 0u : ((2u << lim) - 1u));
@@ -277,13 +277,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         pk[hh * 8 + e] = pack2<T>(d0, d1);
       }
     }
+    PH(1);
     // the dS columns were read by the accumulation step of tile j-1
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+    PH(2);
     tmem_st16(tmem + lane_base + 128 + half * 16, pk);
     tmem_st_wait();
     fence_before_sync();
     warp_arrive(&bars[BB_GRAD], lane);
+    PH(3);
   }
+  if (tid == 0) PH_PRINT("dq elem [wait scores, ld+math, wait acc, st+arrive]", T_tiles);
 
   // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
   if (!failed) failed = !mbar_wait(&bars[BB_ACC + ((T_tiles - 1) & 1)], ((T_tiles - 1) >> 1) & 1, WAIT_LIMIT);

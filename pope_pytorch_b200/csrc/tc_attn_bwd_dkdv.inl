@@ -7,7 +7,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const int KD = D + p.r, KSTEPS = KD >> 4;
   uint8_t* Ks = smem;                          // [KD/8][128][16 B]  resident K' (phase fk + bias)
   uint8_t* Vs = Ks + BQ * KD * 2;              // [D/8][128][16 B]   resident V
-  const int KBUF = (KD / 8) * CS64, VBUF = (D / 8) * CS64;  // one streamed buffer (padded chunk stride)
+  const int KBUF = (KD / 8) * BCS, VBUF = (D / 8) * BCS;  // one streamed buffer
   uint8_t* Qb = Vs + BQ * D * 2;               // 2 x [KD/8][64][16 B] streamed Q'
   uint8_t* Gb = Qb + 2 * KBUF;                 // 2 x [D/8][64][16 B]  streamed dO
   uint8_t* Ps = Gb + 2 * VBUF;                 // [8 chunks][128][16 B] P^T  (A operand, K = 64 queries)
@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(&bars[BB_FULL], BWD_P_WARPS), mbar_init(&bars[BB_FULL + 1], BWD_P_WARPS);
+    mbar_init(&bars[BB_FULL], 1), mbar_init(&bars[BB_FULL + 1], 1);
     mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1), mbar_init(&bars[BB_ACC + 1], 1);
     mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
     mbar_init(&bars[BB_RESIDENT], BWD_E_WARPS);
@@ -57,28 +57,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const uint32_t tmem = *tmem_slot;
   // TMEM columns: S^T [0,64), dP^T [64,128), dV [128, 128+D), dK' [256, 256+KD)
 
-  if (warp >= BWD_E_WARPS && warp < BWD_M_WARP) {
-    // =============================== producers: Q' and dO tiles, lse / delta ====================
-    const int pw = warp - BWD_E_WARPS, ptid = tid - BWD_E_WARPS * 32;
-    for (int j = 0; j < T_tiles; ++j) {
-      const int buf = j & 1, m0 = tile_start(j), h = tile_head(j);
-      const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
-      const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
-      auto wait_free = [&]() {   // buffer j & 1 was last read by the accumulation step of tile j-2
+  if (warp == BWD_L_WARP) {
+    // =============================== copies: Q' and dO image tiles, lse / delta rows =============
+    if (lane == 0) {
+      const int64_t qtiles = (int64_t)image_tiles(p.Nq);
+      for (int j = 0; j < T_tiles; ++j) {
+        const int buf = j & 1, m0 = tile_start(j), h = tile_head(j);
+        const int64_t t = (int64_t)(b * p.H + h) * qtiles + m0 / BT;
+        // buffer j & 1 was last read by the accumulation step of tile j-2
         if (j >= 2 && !failed) failed = !mbar_wait(&bars[BB_ACC + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
-      };
-      produce_tile<D, T>(qbase, p.sq.n, gbase, p.sdo.n, m0, p.Nq, tab, p.Nk, qoff, p.r, Qb + buf * KBUF, Gb + buf * VBUF,
-                         pw, lane, wait_free);
-      if (ptid < BT) {
-        const int gi = m0 + ptid;
-        const int64_t uq = (int64_t)(b * p.H + h) * p.Nq + gi;
-        const float lse_i = gi < p.Nq ? p.lse[uq] : -CUDART_INF_F;
-        rowstat[buf * 128 + ptid] = lse_i == -CUDART_INF_F ? CUDART_INF_F : lse_i * LOG2E;   // +inf: P becomes exactly 0
-        rowstat[buf * 128 + 64 + ptid] = gi < p.Nq ? p.delta[uq] : 0.f;
+        if (failed) break;
+        mbar_expect_tx(&bars[BB_FULL + buf], KBUF + VBUF + 2 * BT * 4);
+        bulk_load(Qb + buf * KBUF, p.qimg + t * KBUF, KBUF, &bars[BB_FULL + buf]);
+        bulk_load(rowstat + buf * 128, p.rowstat + t * 128, 2 * BT * 4, &bars[BB_FULL + buf]);
+        bulk_load(Gb + buf * VBUF, p.gimg + t * VBUF, VBUF, &bars[BB_FULL + buf]);
       }
-      fence_async_smem();
-      warp_arrive(&bars[BB_FULL + buf], lane);
+      if (failed) atomicOr(p.status, 1u);
     }
+    __syncwarp();
   } else if (warp == BWD_M_WARP) {
     // =============================== MMA issue ===================================================
     if (lane == 0 && T_tiles > 0) {
@@ -89,15 +85,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       const uint32_t ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
       auto issue_scores = [&](int jt) {
         const int buf = jt & 1;
-        uint64_t ad = smem_desc(ks_addr, BQ * 16, 128), bd = smem_desc(qb_addr + buf * KBUF, CS64, 128);
+        uint64_t ad = smem_desc(ks_addr, BQ * 16, 128), bd = smem_desc(qb_addr + buf * KBUF, BCS, 128);
         for (int ks = 0; ks < KSTEPS; ++ks) {
           mma_ss(tmem, ad, bd, idesc_s, ks > 0);
-          ad += (2 * BQ * 16) >> 4, bd += (2 * CS64) >> 4;
+          ad += (2 * BQ * 16) >> 4, bd += (2 * BCS) >> 4;
         }
-        ad = smem_desc(vs_addr, BQ * 16, 128), bd = smem_desc(gb_addr + buf * VBUF, CS64, 128);
+        ad = smem_desc(vs_addr, BQ * 16, 128), bd = smem_desc(gb_addr + buf * VBUF, BCS, 128);
         for (int ks = 0; ks < D / 16; ++ks) {
           mma_ss(tmem + 64, ad, bd, idesc_s, ks > 0);
-          ad += (2 * BQ * 16) >> 4, bd += (2 * CS64) >> 4;
+          ad += (2 * BQ * 16) >> 4, bd += (2 * BCS) >> 4;
         }
         mma_commit(&bars[BB_SCORES]);
       };
@@ -116,7 +112,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
         if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
         fence_after_sync();
         uint64_t pa = smem_desc(ps_addr, BQ * 16, 128), da = smem_desc(ds_addr, BQ * 16, 128);
-        uint64_t gd = smem_desc(gb_addr + buf * VBUF, 128, CS64), qd = smem_desc(qb_addr + buf * KBUF, 128, CS64);
+        uint64_t gd = smem_desc(gb_addr + buf * VBUF, 128, BCS), qd = smem_desc(qb_addr + buf * KBUF, 128, BCS);
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks) {
           mma_ss(tmem + 128, pa, gd, idesc_v, (j > 0 || ks > 0) ? 1u : 0u);
@@ -302,20 +298,54 @@ bool attn_bwd_tc_supported(const PopeAttnBwdArgs& a) {
   return true;
 }
 
-static size_t delta_bytes(const PopeShape& s) { return ((size_t)s.B * s.H * s.Nq * sizeof(float) + 255) / 256 * 256; }
+// lse and delta of every 64-query tile in the order the dk/dv kernel consumes them, padded to whole tiles so
+// that one aligned 512-byte bulk copy brings a tile's rows: [unit][tile][64 x lse * log2(e) | 64 x delta].
+// Empty rows (lse = -inf) and rows past Nq carry +inf, which makes their probabilities exactly 0.
+__global__ void bwd_rowstat_kernel(const float* __restrict__ lse, const float* __restrict__ delta, int Nq, float* __restrict__ out) {
+  const int t = threadIdx.x, tile = blockIdx.x, u = blockIdx.y, i = tile * BT + t;
+  const float l = i < Nq ? lse[(int64_t)u * Nq + i] : -CUDART_INF_F;
+  float* o = out + ((int64_t)u * gridDim.x + tile) * (2 * BT);
+  o[t] = l == -CUDART_INF_F ? CUDART_INF_F : l * LOG2E;
+  o[BT + t] = i < Nq ? delta[(int64_t)u * Nq + i] : 0.f;
+}
+
+// workspace: [delta][16-bit cos / sin table][K' images][Q' images][V images][dO images][row statistics], each
+// rounded up to 256 bytes
+static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+static size_t delta_bytes(const PopeShape& s) { return up256((size_t)s.B * s.H * s.Nq * sizeof(float)); }
+static size_t bwd_table_bytes(const PopeShape& s) { return up256(trig_table_bytes(s.Nk, s.r)); }
+static size_t rowstat_bytes(const PopeShape& s) { return up256((size_t)s.B * s.H * image_tiles(s.Nq) * 2 * BT * sizeof(float)); }
 
 size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
-  return delta_bytes(a.shape) + trig_table_bytes(a.shape.Nk, a.shape.r);
+  const PopeShape& s = a.shape;
+  return delta_bytes(s) + bwd_table_bytes(s) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) +
+         up256(image_bytes(s.B * s.H, s.Nq, s.d + s.r)) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d)) +
+         up256(image_bytes(s.B * s.H, s.Nq, s.d)) + rowstat_bytes(s);
 }
 
 template <int D, typename T>
 static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
-  float* delta = reinterpret_cast<float*>(a.workspace);
-  void* table = reinterpret_cast<uint8_t*>(a.workspace) + delta_bytes(s);
+  const int KD = s.d + s.r;
+  const bool bf16 = s.dtype == POPE_BF16;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(a.workspace);
+  float* delta = reinterpret_cast<float*>(ws);
+  void* table = ws + delta_bytes(s);
+  uint8_t* kimg = ws + delta_bytes(s) + bwd_table_bytes(s);
+  uint8_t* qimg = kimg + up256(image_bytes(s.B * s.Hk, s.Nk, KD));
+  uint8_t* vimg = qimg + up256(image_bytes(s.B * s.H, s.Nq, KD));
+  uint8_t* gimg = vimg + up256(image_bytes(s.B * s.Hk, s.Nk, s.d));
+  float* rowstat = reinterpret_cast<float*>(gimg + up256(image_bytes(s.B * s.H, s.Nq, s.d)));
   cudaError_t e = attn_bwd_delta(a, delta, st);
   if (e != cudaSuccess) return e;
-  if (s.r > 0 && (e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, table, s.dtype == POPE_BF16, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, table, bf16, st)) != cudaSuccess) return e;
+  if ((e = launch_expand_images(a.k, a.sk, s.B, s.Hk, s.Nk, s.d, s.r, bf16, table, s.Nk, 0, kimg, st)) != cudaSuccess) return e;
+  if ((e = launch_expand_images(a.q, a.sq, s.B, s.H, s.Nq, s.d, s.r, bf16, table, s.Nk, s.Nk - s.Nq, qimg, st)) != cudaSuccess) return e;
+  // V and dO: the same tiles without any rotated features (a pure re-layout)
+  if ((e = launch_expand_images(a.v, a.sv, s.B, s.Hk, s.Nk, s.d, 0, bf16, table, s.Nk, 0, vimg, st)) != cudaSuccess) return e;
+  if ((e = launch_expand_images(a.dout, a.sdo, s.B, s.H, s.Nq, s.d, 0, bf16, table, s.Nk, 0, gimg, st)) != cudaSuccess) return e;
+  bwd_rowstat_kernel<<<dim3((unsigned)image_tiles(s.Nq), s.B * s.H), BT, 0, st>>>(a.lse, delta, s.Nq, rowstat);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
   TcBwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
   p.scale = a.softmax_scale, p.scale_log2 = a.softmax_scale * LOG2E;
@@ -323,13 +353,13 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.sdo = a.sdo, p.sdq = a.sdq, p.sdk = a.sdk, p.sdv = a.sdv, p.sdf = a.sdf;
   p.freqs = a.embed.freqs, p.bias = a.embed.bias, p.lse = a.lse, p.delta = delta;
   p.sfn = a.embed.sf.n, p.bias_sh = a.embed.bias_stride_h, p.dbias_sh = a.dbias_stride_h;
-  p.table = table, p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
+  p.table = table, p.kimg = kimg, p.qimg = qimg, p.vimg = vimg, p.gimg = gimg, p.rowstat = rowstat;
+  p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   p.dfreqs = s.r > 0 ? a.dfreqs : nullptr, p.dbias = s.r > 0 ? a.dbias : nullptr;
   p.status = tc_status_ptr();
   if (!p.status) return cudaErrorInvalidSymbol;
-  const int KD = s.d + s.r;
-  const size_t streamed = 2 * (size_t)(KD / 8) * CS64 + 2 * (size_t)(D / 8) * CS64;
-  size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + (BB_COUNT + 1) * 8 + 4 * 4 + 16 + 1024;
+  const size_t streamed = 2 * (size_t)BT * KD * 2 + 2 * (size_t)BT * D * 2;
+  size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + (BB_COUNT + 1) * 8 + 16 + 1024;
   size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + 2 * BQ * BT * 2 + 256 * 4 + (BB_COUNT + 1) * 8 + 16 + 16;
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;

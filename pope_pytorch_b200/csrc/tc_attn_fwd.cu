@@ -19,6 +19,7 @@
 //
 // Semantics follow PoPE_pytorch/triton_pope_flash_attn.py:23-117 (top-left causal mask,
 // bottom-right positions, mask True = keep, zero output and -inf LSE for empty rows).
+#include <cstring>
 #include <mutex>
 
 #include "kernels.h"
@@ -88,6 +89,37 @@ cudaError_t launch_trig_table(const float* freqs, int64_t sfn, int n, int r, voi
   return cudaGetLastError();
 }
 
+bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
+                     int64_t sh, int64_t sb, int box_rows) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      encode = reinterpret_cast<EncodeFn>(fn);
+  });
+  if (!encode) return false;
+  // a size-1 axis may come with any stride: give it a valid dummy (multiple of 16 bytes, increasing)
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
+  int64_t st[3] = {sn, sh, sb};
+  if (rows == 1 || st[0] <= 0) st[0] = d;
+  if (heads == 1 || st[1] <= 0) st[1] = st[0] * rows;
+  if (batch == 1 || st[2] <= 0) st[2] = st[1] * heads;
+  cuuint64_t strides[3] = {(cuuint64_t)st[0] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[2] * 2};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] % 16 != 0) return false;
+  cuuint32_t box[4] = {8, (cuuint32_t)box_rows, 1, 1}, estr[4] = {1, 1, 1, 1};
+  const CUresult rc = encode(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
 struct TcFwdP {
   int H, Hk, Nq, Nk, r, causal;
   float scale_log2;  // softmax_scale * log2(e)
@@ -100,52 +132,51 @@ struct TcFwdP {
   const float* bias;
   int64_t bias_sh;
   const void* table;   // cos / sin in the dtype of q, k, v
+  const uint8_t* kimg; // expanded K' image tiles, (B * Hk) units
   const uint8_t* mask;
   int64_t msb, msn;
 };
 
 constexpr int TQ = 128;   // rows per MMA tile
-constexpr int TK = 64;    // keys per step
+constexpr int TK = 64;    // keys per step (= IMAGE_ROWS)
+static_assert(TK == IMAGE_ROWS, "a streamed K' tile is one image tile");
 
-// Warp roles of the forward kernel (17 warps, 544 threads)
-constexpr int FWD_SOFTMAX_WARPS = 8;   // warps 0-7  : one query row per thread (two 128-row tiles)
-constexpr int FWD_PRODUCER_WARPS = 8;  // warps 8-15 : expand K tiles, stage V, publish key-validity bits
-constexpr int FWD_MMA_WARP = FWD_SOFTMAX_WARPS + FWD_PRODUCER_WARPS;   // warp 16 issues every MMA
+// Warp roles of the forward kernel (10 warps, 320 threads)
+constexpr int FWD_SOFTMAX_WARPS = 8;               // warps 0-7 : one query row per thread (two 128-row tiles)
+constexpr int FWD_LOAD_WARP = FWD_SOFTMAX_WARPS;   // warp 8    : one lane issues every bulk / tensor copy
+constexpr int FWD_MMA_WARP = FWD_LOAD_WARP + 1;    // warp 9    : one lane issues every MMA; owns the TMEM allocation
 constexpr int FWD_THREADS = 32 * (FWD_MMA_WARP + 1);
 
 // mbarrier slots
-enum { B_KFULL = 0, B_SFULL = 2, B_PVDONE = 4, B_PFULL = 6 /* [buf][tile] */, B_QFULL = 10, B_COUNT = 11 };
-
-struct WaitBuffer {   // producer hook: block until the K'/V buffer of tile j has been consumed (PV(j-2) done)
-  uint64_t* bar;
-  uint32_t parity;
-  bool enabled;
-  bool* failed;
-  __device__ __forceinline__ void operator()() const {
-    if (enabled && !*failed) *failed = !mbar_wait(bar, parity, WAIT_LIMIT);
-  }
+enum {
+  B_KFULL = 0,   // [2] K' image tile landed (transaction bytes)
+  B_VFULL = 2,   // [2] V tile landed (transaction bytes)
+  B_SFULL = 4,   // [2] scores of both row tiles written to TMEM (tcgen05.commit)
+  B_PVDONE = 6,  // [2] O += P V of both row tiles done (tcgen05.commit)
+  B_PFULL = 8,   // [buf][row tile] probabilities written to TMEM (4 softmax warps)
+  B_QFULL = 12,  // the resident Q' tiles are in shared memory
+  B_COUNT = 13
 };
 
 template <int D, typename T>
-__global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
+__global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, const __grid_constant__ CUtensorMap tmap_v) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int KD = D + p.r, KSTEPS = KD >> 4;
-  uint8_t* Qs = smem;                              // 2 tiles x [KD/8 chunks][128 rows][16 B]
-  uint8_t* Ks = Qs + 2 * TQ * KD * 2;              // 2 bufs  x [KD/8 chunks][64 rows][16 B]
-  const int KBUF = (KD / 8) * CS64, VBUF = (D / 8) * CS64;   // bytes of one streamed K' / V buffer (padded chunks)
-  uint8_t* Vs = Ks + 2 * KBUF;                     // 2 bufs  x [D/8 chunks][64 keys][16 B]
+  constexpr int CS = TK * 16;                       // bytes of one 16-byte chunk column of a streamed tile
+  const int KBUF = (KD / 8) * CS;                   // one K' tile = one image tile
+  constexpr int VBUF = (D / 8) * CS;
+  uint8_t* Qs = smem;                               // 2 tiles x [KD/8 chunks][128 rows][16 B]
+  uint8_t* Ks = Qs + 2 * TQ * KD * 2;               // 2 bufs  x [KD/8 chunks][64 keys][16 B]
+  uint8_t* Vs = Ks + 2 * KBUF;                      // 2 bufs  x [D/8 chunks][64 keys][16 B]; 128-byte aligned (KD % 16 == 0)
   uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);
-  uint32_t* kbits = reinterpret_cast<uint32_t*>(bars + B_COUNT + 1);  // [2 bufs][2 words]
-  uint32_t* tmem_slot = kbits + 4;
-  float* bias_cb = reinterpret_cast<float*>(tmem_slot + 4);           // cos / sin of the head's phase bias
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT + 1);
+  float* bias_cb = reinterpret_cast<float*>(tmem_slot + 4);            // cos / sin of the head's phase bias
   float* bias_sb = bias_cb + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
   const int i0 = (gridDim.x - 1 - blockIdx.x) * (2 * TQ);  // heavy (late) row blocks first
   const int qoff = p.Nk - p.Nq;
-  const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
-  const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
 
   int n_end = p.Nk;
   if (p.causal) n_end = min(n_end, min(i0 + 2 * TQ, p.Nq));
@@ -160,9 +191,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(&bars[B_KFULL], FWD_PRODUCER_WARPS), mbar_init(&bars[B_KFULL + 1], FWD_PRODUCER_WARPS);
-    mbar_init(&bars[B_SFULL], 1), mbar_init(&bars[B_SFULL + 1], 1);
-    mbar_init(&bars[B_PVDONE], 1), mbar_init(&bars[B_PVDONE + 1], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars[B_KFULL + i], 1), mbar_init(&bars[B_VFULL + i], 1);
+      mbar_init(&bars[B_SFULL + i], 1), mbar_init(&bars[B_PVDONE + i], 1);
+    }
     for (int i = 0; i < 4; ++i) mbar_init(&bars[B_PFULL + i], 4);
     mbar_init(&bars[B_QFULL], FWD_SOFTMAX_WARPS);
     mbar_init_fence();
@@ -173,83 +205,37 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
   const uint32_t tmem = *tmem_slot;
   bool failed = false;
 
-  if (warp >= FWD_SOFTMAX_WARPS && warp < FWD_SOFTMAX_WARPS + FWD_PRODUCER_WARPS) {
-    // =============================== producers ===============================================
-    const int pw = warp - FWD_SOFTMAX_WARPS;
-    const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
-    PROF_DECL;
-    // Work of one tile for this warp: NT expand tasks (8 rows x 4 chunks each) and NT plain V tasks.  A window
-    // of W expand tasks stays in flight in registers, across tile boundaries, so the loads of the next tasks
-    // travel while the current one is being expanded; V is loaded at the start of a tile and stored at its end.
-    constexpr int NT = (TK * D / 256) / FWD_PRODUCER_WARPS;
-    constexpr int W = (NT % 2 == 0) ? 2 : 3;
-    static_assert(NT % W == 0, "window must divide the per-tile task count");
-    const T* tab = static_cast<const T*>(p.table);
-    const T* tab_s = tab + (int64_t)p.Nk * p.r;
-    XTask win[W];
-    for (int j = 0; j < T_tiles; ++j) {
-      const int buf = j & 1, n0 = j * TK;
-      uint8_t* Kb = Ks + buf * KBUF;
-      uint8_t* Vb = Vs + buf * VBUF;
-      PROF(0);
-      // every load of a tile is issued inside that tile's iteration: the proxy fence that closes an
-      // iteration waits for all of the thread's outstanding loads, so loads carried across it would
-      // only stall it
-#pragma unroll
-      for (int it = 0; it < W; ++it)
-        xtask_load<D, TK, T>(win[it], kbase, p.sk.n, n0, p.Nk, tab, tab_s, 0, p.r, pw + FWD_PRODUCER_WARPS * it, lane);
-      uint4 vreg[NT];
-#pragma unroll
-      for (int it = 0; it < NT; ++it) {
-        int row, c;
-        stage_coords<TK, D / 8>(pw + FWD_PRODUCER_WARPS * it, lane, row, c);
-        vreg[it] = make_uint4(0, 0, 0, 0);
-        if (n0 + row < p.Nk) vreg[it] = __ldg(reinterpret_cast<const uint4*>(vbase + (int64_t)(n0 + row) * p.sv.n + c * 8));
-      }
-      PROF(1);
-      // the K' buffer of tile j was last read by S(j-2), the V buffer by PV(j-2)
-#ifndef POPE_DBG_PRODUCER_ONLY
-      if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_SFULL + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+  if (warp == FWD_LOAD_WARP) {
+    // =============================== copies ==================================================
+    // K'(j) is one contiguous image tile; V(j) arrives as D/8 boxes of 64 keys x 16 bytes, each landing on its
+    // chunk column.  A buffer is refilled as soon as the MMA that read it has completed.
+    if (lane == 0) {
+      const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * KBUF;
+      for (int j = 0; j < T_tiles; ++j) {
+        const int buf = j & 1, n0 = j * TK;
+        if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_SFULL + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        if (failed) break;
+#ifdef POPE_DBG_NO_KLOAD
+        mbar_arrive(&bars[B_KFULL + buf]);
+#else
+        mbar_expect_tx(&bars[B_KFULL + buf], KBUF);
+        bulk_load(Ks + buf * KBUF, kimg + (int64_t)j * KBUF, KBUF, &bars[B_KFULL + buf]);
 #endif
-      PROF(12);
+        if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        if (failed) break;
+#ifdef POPE_DBG_NO_VLOAD
+        mbar_arrive(&bars[B_VFULL + buf]);
+#else
+        mbar_expect_tx(&bars[B_VFULL + buf], VBUF);
 #pragma unroll
-      for (int it = 0; it < NT; ++it) {
-        xtask_store_packed<D, TK, T>(win[it % W], p.r, Kb, pw + FWD_PRODUCER_WARPS * it, lane);
-        const int nit = it + W;   // refill the slot with the task W ahead
-        if (nit < NT)
-          xtask_load<D, TK, T>(win[it % W], kbase, p.sk.n, n0, p.Nk, tab, tab_s, 0, p.r,
-                            pw + FWD_PRODUCER_WARPS * nit, lane);
-      }
-      PROF(2);
-#ifndef POPE_DBG_PRODUCER_ONLY
-      if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        for (int c = 0; c < D / 8; ++c) tma_load_4d(Vs + buf * VBUF + c * CS, &tmap_v, &bars[B_VFULL + buf], c * 8, n0, hk, b);
 #endif
-      PROF(13);
-#pragma unroll
-      for (int it = 0; it < NT; ++it) {
-        int row, c;
-        stage_coords<TK, D / 8>(pw + FWD_PRODUCER_WARPS * it, lane, row, c);
-        *reinterpret_cast<uint4*>(Vb + c * CS64 + row * 16) = vreg[it];
       }
-      if (pw < 2) {
-        const int jk = n0 + pw * 32 + lane;
-        const bool ok = jk < p.Nk && (!maskb || maskb[(int64_t)jk * p.msn] != 0);
-        const uint32_t bits = __ballot_sync(0xffffffffu, ok);
-        if (lane == 0) kbits[buf * 2 + pw] = bits;
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_KFULL + buf]);
-      PROF(0);
     }
-    if (warp == FWD_SOFTMAX_WARPS && lane == 0) { PROF_FLUSH(0, 3); PROF_FLUSH(12, 14); PROF_COUNT(14, 1); PROF_COUNT(15, T_tiles); }
+    __syncwarp();
   } else if (warp == FWD_MMA_WARP) {
     // =============================== MMA issue ================================================
-#ifdef POPE_DBG_PRODUCER_ONLY
-    if (false) {
-#else
     if (lane == 0) {
-#endif
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, TQ, TK, false, false);
       const uint32_t idesc_o = instr_desc(TcFmt<T>::fmt, TQ, D, false, true);
       const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
@@ -259,57 +245,55 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
           if (jt >= (t == 0 ? T0 : T1)) continue;
           const uint32_t d = tmem + (buf * 2 + t) * 64;
           uint64_t ad = smem_desc(qs_addr + t * (TQ * KD * 2), TQ * 16, 128);
-          uint64_t bd = smem_desc(ks_addr + buf * KBUF, CS64, 128);
+          uint64_t bd = smem_desc(ks_addr + buf * KBUF, CS, 128);
+#ifndef POPE_DBG_NO_QK
           mma_ss(d, ad, bd, idesc_s, 0u);
           for (int ks = 1; ks < KSTEPS; ++ks) {
-            ad += (2 * TQ * 16) >> 4, bd += (2 * CS64) >> 4;
+            ad += (2 * TQ * 16) >> 4, bd += (2 * CS) >> 4;
             mma_ss(d, ad, bd, idesc_s, 1u);
           }
+#endif
         }
         mma_commit(&bars[B_SFULL + buf]);
       };
-      PROF_DECL;
       if (!mbar_wait(&bars[B_QFULL], 0, WAIT_LIMIT)) failed = true;
       if (!mbar_wait(&bars[B_KFULL], 0, WAIT_LIMIT)) failed = true;
       fence_after_sync();
       issue_s(0);
-      PROF(3);
       for (int j = 0; j < T_tiles; ++j) {
         const int buf = j & 1;
         if (j + 1 < T_tiles) {
           if (!failed) failed = !mbar_wait(&bars[B_KFULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
-          PROF(4);
           // score buffer 1-buf still holds P(j-1) until PV(j-1) has read it
           if (j >= 1 && !failed) failed = !mbar_wait(&bars[B_PVDONE + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
           fence_after_sync();
-          PROF(5);
           issue_s(j + 1);
-          PROF(6);
         }
+        if (!failed) failed = !mbar_wait(&bars[B_VFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
         for (int t = 0; t < 2; ++t) {
           if (j >= (t == 0 ? T0 : T1)) continue;
           if (!failed) failed = !mbar_wait(&bars[B_PFULL + buf * 2 + t], (j >> 1) & 1, WAIT_LIMIT);
           fence_after_sync();
-          PROF(7);
           const uint32_t d = tmem + 256 + t * 128;
           const uint32_t a = tmem + (buf * 2 + t) * 64;
-          uint64_t bd = smem_desc(vs_addr + buf * VBUF, 128, CS64);
+          uint64_t bd = smem_desc(vs_addr + buf * VBUF, 128, CS);
+#ifndef POPE_DBG_NO_PV
 #pragma unroll
           for (int ks = 0; ks < TK / 16; ++ks) {
             mma_ts(d, a + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
             bd += (2 * 128) >> 4;
           }
-          PROF(8);
+#endif
         }
         mma_commit(&bars[B_PVDONE + buf]);
       }
-      PROF_FLUSH(3, 9);
     }
     __syncwarp();
   } else {
     // =============================== softmax ==================================================
     const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
     const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
+    const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
     load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
     asm volatile("bar.sync 1, 256;" ::: "memory");
     const T* qtab = static_cast<const T*>(p.table);
@@ -322,50 +306,52 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
 
     const int tile = warp >> 2;
     const int row = i0 + tid;
-#ifdef POPE_DBG_PRODUCER_ONLY
-    const int T_mine = 0;
-#else
     const int T_mine = tile == 0 ? T0 : T1;
-#endif
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     float m_run = -CUDART_INF_F, l_run = 0.f;
-    PROF_DECL;
-    PROF(9);
 
     for (int j = 0; j < T_mine; ++j) {
       const int buf = j & 1, n0 = j * TK;
-      if (!failed) failed = !mbar_wait(&bars[B_KFULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the kbits read
-      if (!failed) failed = !mbar_wait(&bars[B_SFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
-      fence_after_sync();
-      PROF(10);
-      const uint32_t s_addr = tmem + lane_base + (buf * 2 + tile) * 64;
-      // visibility of the 64 keys of this tile for this row
-      uint64_t vis = ((uint64_t)kbits[buf * 2 + 1] << 32) | kbits[buf * 2];
+      // key visibility of this tile (key-padding mask, ragged end): one bit per key, the same for every row
+      uint64_t vis = ~0ull;
+      if (maskb || n0 + TK > p.Nk) {
+        const int j0 = n0 + lane, j1 = j0 + 32;
+        const bool ok0 = j0 < p.Nk && (!maskb || maskb[(int64_t)j0 * p.msn] != 0);
+        const bool ok1 = j1 < p.Nk && (!maskb || maskb[(int64_t)j1 * p.msn] != 0);
+        vis = ((uint64_t)__ballot_sync(0xffffffffu, ok1) << 32) | __ballot_sync(0xffffffffu, ok0);
+      }
       if (p.causal) {
         const int lim = row - n0;  // columns <= lim are visible
         vis &= lim >= 63 ? ~0ull : (lim < 0 ? 0ull : ((2ull << lim) - 1ull));
       }
       const bool all_vis = __all_sync(0xffffffffu, vis == ~0ull);
-      // pass 1: row maximum (four independent chains per 32 columns)
-      float mx = -CUDART_INF_F;
+      if (!failed) failed = !mbar_wait(&bars[B_SFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
+      fence_after_sync();
+      const uint32_t s_addr = tmem + lane_base + (buf * 2 + tile) * 64;
+#ifdef POPE_DBG_NO_SOFTMAX
+      if (p.Nq > 0) { __syncwarp(); if (lane == 0) mbar_arrive(&bars[B_PFULL + buf * 2 + tile]); continue; }
+#endif
+      uint32_t s0[32], s1[32];
+      tmem_ld32(s_addr, s0);
+      tmem_ld32(s_addr + 32, s1);
+      tmem_ld_wait();
+      // row maximum (four independent chains)
+      float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+      if (all_vis) {
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t sv[32];
-        tmem_ld32(s_addr + hh * 32, sv);
-        tmem_ld_wait();
-        const uint32_t vh = (uint32_t)(vis >> (32 * hh));
-        float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-        if (all_vis) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2)
-            m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if ((vh >> i) & 1u) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[i]));
+        for (int i = 0; i < 32; i += 2) {
+          m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+          m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
         }
-        mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+      } else {
+        const uint32_t v0 = (uint32_t)vis, v1 = (uint32_t)(vis >> 32);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if ((v0 >> i) & 1u) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(s0[i]));
+          if ((v1 >> i) & 1u) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(s1[i]));
+        }
       }
+      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
       // keep a stale maximum while it is within 2^8 of the true one: P stays below 256 and the
       // output accumulator needs no rescale on most steps
@@ -392,20 +378,18 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
         }
         tmem_st_wait();
       }
-      // pass 2: P = 2^(s*c - m), written over the scores (16 packed columns per 32 scores)
+      // P = 2^(s*c - m), written over the scores (16 packed columns per 32 scores)
       const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        uint32_t sv[32];
-        tmem_ld32(s_addr + hh * 32, sv);
-        tmem_ld_wait();
         const uint32_t vh = (uint32_t)(vis >> (32 * hh));
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, -m_use));
-          float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, -m_use));
+          const uint32_t x0 = hh ? s1[2 * i] : s0[2 * i], x1 = hh ? s1[2 * i + 1] : s0[2 * i + 1];
+          float p0 = ex2_approx(fmaf(__uint_as_float(x0), p.scale_log2, -m_use));
+          float p1 = ex2_approx(fmaf(__uint_as_float(x1), p.scale_log2, -m_use));
           if (!all_vis) {
             p0 = ((vh >> (2 * i)) & 1u) ? p0 : 0.f;
             p1 = ((vh >> (2 * i + 1)) & 1u) ? p1 : 0.f;
@@ -420,9 +404,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p) {
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[B_PFULL + buf * 2 + tile]);
-      PROF(11);
     }
-    if (warp == 4 && lane == 0) PROF_FLUSH(9, 12);
 
     // ---- epilogue: O / l, LSE ---------------------------------------------------------------------
     if (T_mine > 0) {
@@ -475,8 +457,12 @@ bool attn_fwd_tc_supported(const PopeAttnArgs& a) {
   return true;
 }
 
+// workspace: [16-bit cos / sin table, rounded up to 256 bytes][K' image tiles of all (batch, key head) units]
+static size_t fwd_table_bytes(const PopeShape& s) { return (trig_table_bytes(s.Nk, s.r) + 255) & ~(size_t)255; }
+
 size_t attn_fwd_tc_workspace(const PopeAttnArgs& a) {
-  return trig_table_bytes(a.shape.Nk, a.shape.r);
+  const PopeShape& s = a.shape;
+  return fwd_table_bytes(s) + image_bytes(s.B * s.Hk, s.Nk, s.d + s.r);
 }
 
 template <int D, typename T>
@@ -484,27 +470,32 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
   TcFwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
-  p.scale_log2 = a.softmax_scale * 1.4426950408889634f;
+  p.scale_log2 = a.softmax_scale * LOG2E;
   p.q = a.q, p.k = a.k, p.v = a.v, p.o = a.out, p.lse = a.lse;
   p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.so = a.so;
   p.freqs = a.embed.freqs, p.sfn = a.embed.sf.n, p.bias = a.embed.bias, p.bias_sh = a.embed.bias_stride_h;
   p.table = a.workspace;
+  p.kimg = static_cast<const uint8_t*>(a.workspace) + fwd_table_bytes(s);
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
+  const bool bf16 = s.dtype == POPE_BF16;
+  cudaError_t e;
   if (s.r > 0) {
-    const int64_t n = (int64_t)s.Nk * s.r;
-    (void)n;
-    cudaError_t e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, a.workspace, s.dtype == POPE_BF16, st);
+    e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, a.workspace, bf16, st);
     if (e != cudaSuccess) return e;
   }
+  e = launch_expand_images(a.k, a.sk, s.B, s.Hk, s.Nk, s.d, s.r, bf16, a.workspace, s.Nk, 0, const_cast<uint8_t*>(p.kimg), st);
+  if (e != cudaSuccess) return e;
+  CUtensorMap tmap_v;
+  if (!make_chunk_tmap(&tmap_v, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, TK)) return cudaErrorNotSupported;
   const int KD = s.d + s.r;
-  size_t smem = (size_t)2 * TQ * KD * 2 + 2 * (KD / 8) * CS64 + 2 * (D / 8) * CS64 + (B_COUNT + 1) * 8 + 4 * 4 + 16 + 2 * 128 * 4;
+  size_t smem = (size_t)2 * TQ * KD * 2 + 2 * (size_t)TK * KD * 2 + 2 * (size_t)TK * D * 2 + (B_COUNT + 1) * 8 + 16 + 2 * 128 * 4;
   // every CTA allocates all 512 TMEM columns: ask for more than half of the SM's shared memory so
   // that two CTAs are never co-resident
   if (smem < 120 * 1024) smem = 120 * 1024;
-  cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   dim3 grid((s.Nq + 2 * TQ - 1) / (2 * TQ), s.B * s.H);
-  attn_fwd_tc_kernel<D, T><<<grid, FWD_THREADS, smem, st>>>(p);
+  attn_fwd_tc_kernel<D, T><<<grid, FWD_THREADS, smem, st>>>(p, tmap_v);
   return cudaGetLastError();
 }
 

@@ -5,6 +5,8 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include <cuda.h>   // CUtensorMap (types only; the encoder is fetched through the runtime's driver entry point)
+
 #include "common.cuh"
 #include "tc05.cuh"
 
@@ -70,9 +72,24 @@ template <> __device__ __forceinline__ uint32_t mul2<__half>(uint32_t a, uint32_
 
 // Phase tables built once per call in the workspace: cos(freqs[pos][c]) and sin(freqs[pos][c]) as two
 // half arrays [n][r], the sine array following the cosine array.
+// Tensor map of a (batch, head, row, feature) operand for box loads of `box_rows` rows x 8 features (one
+// 16-byte chunk column of the operand layout).  Returns false when the driver's encoder is unavailable or
+// rejects the geometry; callers then stage that operand with ordinary loads.
+bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
+                     int64_t sh, int64_t sb, int box_rows);
+
 // `as_bf16` selects bf16 instead of fp16 entries (the forward multiplies in the operand dtype).
 cudaError_t launch_trig_table(const float* freqs, int64_t sfn, int n, int r, void* table, bool as_bf16, cudaStream_t st);
 inline size_t trig_table_bytes(int n, int r) { return (size_t)n * r * 2 * sizeof(__half) + 16; }
+
+// Expanded-operand images (see tc_expand.cu): 64-row tiles [chunk][row][16 B], contiguous per (unit, tile).
+constexpr int IMAGE_ROWS = 64;
+__host__ __device__ inline size_t image_tiles(int rows) { return (size_t)(rows + IMAGE_ROWS - 1) / IMAGE_ROWS; }
+inline size_t image_bytes(int units, int rows, int kd) { return (size_t)units * image_tiles(rows) * IMAGE_ROWS * kd * 2; }
+// `table` = the 16-bit cos / sin table in the operand dtype ([tab_n][r] twice); row j of the operand takes table
+// row pos0 + j.
+cudaError_t launch_expand_images(const void* x, const PopeStride3& sx, int batch, int heads, int rows, int d, int r,
+                                 bool is_bf16, const void* table, int tab_n, int pos0, void* img, cudaStream_t st);
 
 // cos / sin of the per-head phase bias into shared memory (r floats each); `sign` = -1 folds the bias
 // into a query-side phase (f - b), +1 into a key-side phase (f + b).  Call before a __syncthreads().

@@ -145,10 +145,10 @@ def run_case(b, h, hk, nq, nk, d, r, dtype, causal, masked, seed, freqs=None, bi
             errs["dfreqs_rel"] = maxerr(fg.grad, ref["dfreqs"]) / max(1.0, float(ref["dfreqs"].abs().max()))
     assert out.dtype == dtype and not torch.isnan(out.float()).any()
     for name, e in errs.items():
-        # storing a result in bf16 alone costs 2^-9 of its magnitude: where a gradient exceeds ~5 in
-        # magnitude (grouped heads sum several query heads into dk/dv) the bound scales with it
+        # the tolerance applies to the value; storing it in a 16-bit format costs another half ulp, up to
+        # 2^-9 of its magnitude in bf16 (|dv| reaches 4-8 where grouped heads sum several query heads)
         mag = float(ref[name].abs().max()) if (name in ref and dtype != torch.float32) else 0.0
-        bound = max(tol, 2.0 ** -8 * mag)
+        bound = tol + 2.0 ** -9 * mag
         assert e <= bound, f"{name}: {e} > {bound} (all: {errs})"
     return errs
 
