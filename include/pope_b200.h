@@ -188,8 +188,8 @@ POPE_API int pope_b200_attn_bwd(const PopeAttnBwdArgs* args, void* stream);
  * (No counterpart in the reference: its wrappers always allocate through torch.)
  *
  * Same arguments and results as pope_b200_attn_fwd, but `workspace` / `workspace_bytes` are
- * ignored: the kernel's scratch (its position phase table) lives in a fixed array inside the
- * library instead.  Meant for hosts that may not touch a device allocator where they call us --
+ * ignored: the kernel's scratch (the position phase table and the expanded operand tiles of q
+ * and k) lives in a fixed array inside the library instead.  Meant for hosts that may not touch a device allocator where they call us --
  * an inference loop whose memory plan is frozen, a plugin that is only ever handed input and
  * output buffers, a latency-critical thread that must not take the allocator's lock.  The call
  * itself performs no device allocation or free of any kind.
@@ -197,7 +197,9 @@ POPE_API int pope_b200_attn_bwd(const PopeAttnBwdArgs* args, void* stream);
  * Limits and rules
  *   - Only the tensor-core shapes are served (bf16/fp16, d in {64,96,128}, r % 16 == 0, Nq >= 64,
  *     2-D freqs, 16-byte aligned rows); anything else returns POPE_ERR_UNSUPPORTED.
- *   - The table needs Nk * r * 4 + 16 bytes; more than POPE_B200_NOALLOC_MAX_SCRATCH returns
+ *   - The scratch a call needs is what pope_b200_workspace_bytes reports for the forward
+ *     (8 Nk r bytes of table plus 2 (d + r) bytes per query and key row of every head, rows
+ *     padded to a multiple of 256); more than POPE_B200_NOALLOC_MAX_SCRATCH returns
  *     POPE_ERR_TOO_LARGE and launches nothing.  Every GPU that loads the library holds that many
  *     bytes until the process exits.
  *   - The first call on each device looks up the array's device address (a one-time runtime
@@ -205,7 +207,7 @@ POPE_API int pope_b200_attn_bwd(const PopeAttnBwdArgs* args, void* stream);
  *   - All calls on a device share the one array and each call rewrites the part it uses, so
  *     nothing is carried over between calls -- but two calls whose kernels overlap on the GPU
  *     (different streams, no ordering) race on it.  Serialise them. */
-#define POPE_B200_NOALLOC_MAX_SCRATCH (4u << 20)
+#define POPE_B200_NOALLOC_MAX_SCRATCH (16u << 20)
 POPE_API int pope_b200_attn_fwd_noalloc(const PopeAttnArgs* args, void* stream);
 
 #ifdef __cplusplus

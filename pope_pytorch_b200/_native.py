@@ -327,7 +327,7 @@ def attn_backward(dout, q, k, v, out, lse, freqs, bias, mask, causal, scale, nee
     return dq, dk, dv, dfreqs, dbias
 
 
-NOALLOC_MAX_SCRATCH = 4 << 20
+NOALLOC_MAX_SCRATCH = 16 << 20
 
 
 def attn_forward_noalloc(q, k, v, freqs, bias, mask, causal, scale, out, lse):

@@ -14,23 +14,10 @@
 // operand is resident.  A streamed tile in shared memory serves two MMAs: as the K-major B
 // operand of the score product and, re-described as MN-major, as the B operand of the gradient
 // product -- the 8x16-byte core-matrix layout is symmetric under that exchange.
-#include <cstdio>
-
 #include "kernels.h"
 #include "tc_common.cuh"
 
 namespace pope {
-
-// Optional phase timers of one CTA (compile with -DPOPE_DBG_PHASES): clock64 deltas per phase, printed at the end.
-#ifdef POPE_DBG_PHASES
-#define PH_DECL long long _t0 = clock64(), _t1; long long _acc[8] = {}
-#define PH(i) do { _t1 = clock64(); _acc[i] += _t1 - _t0; _t0 = _t1; } while (0)
-#define PH_PRINT(tag, n) do { if (blockIdx.x == 7 && blockIdx.y == 3) printf("%s tiles %d: %lld %lld %lld %lld %lld %lld %lld %lld\n", tag, n, _acc[0] / (n), _acc[1] / (n), _acc[2] / (n), _acc[3] / (n), _acc[4] / (n), _acc[5] / (n), _acc[6] / (n), _acc[7] / (n)); } while (0)
-#else
-#define PH_DECL
-#define PH(i)
-#define PH_PRINT(tag, n)
-#endif
 
 struct TcBwdP {
   int H, Hk, Nq, Nk, r, causal;
@@ -40,7 +27,7 @@ struct TcBwdP {
   Strides sq, sk, sv, sdo, sdq, sdk, sdv, sdf;
   const float *freqs, *bias, *lse, *delta;
   int64_t sfn, bias_sh, dbias_sh;
-  const void* table;   // cos / sin tables in the dtype of q, k, v
+  const float *ctab, *stab;   // fp32 cos / sin of the phase table, [Nk][r]
   const uint8_t* kimg;   // expanded K' image tiles, (B * Hk) units (no phase bias)
   const uint8_t* qimg;   // expanded Q' image tiles, (B * H) units (no phase bias)
   const uint8_t* vimg;   // V re-laid as image tiles, (B * Hk) units
@@ -53,64 +40,61 @@ struct TcBwdP {
 };
 
 constexpr int BQ = 128;  // resident rows per CTA
-constexpr int BT = 64;   // streamed rows per step
+constexpr int BT = 64;   // streamed rows per step (= IMAGE_ROWS)
+static_assert(BT == IMAGE_ROWS, "a streamed tile is one image tile");
 
-// ================================================================================================
-// dq
-// ================================================================================================
 // Warp roles of both backward kernels (10 warps, 320 threads)
-constexpr int BWD_E_WARPS = 8;     // warps 0-7 : elementwise work (P, dS) and the epilogue; build the resident operands
-constexpr int BWD_L_WARP = 8;      // warp 8    : one lane issues the bulk / tensor copies of the streamed tiles
+constexpr int BWD_E_WARPS = 8;     // warps 0-7 : elementwise work (P, dS) and the epilogue
+constexpr int BWD_L_WARP = 8;      // warp 8    : issues the bulk copies of the resident and the streamed tiles
 constexpr int BWD_M_WARP = 9;      // warp 9    : one lane issues every MMA; owns the TMEM allocation
 constexpr int BWD_THREADS = 32 * (BWD_M_WARP + 1);
 constexpr int BCS = BT * 16;       // bytes of one 16-byte chunk column of a streamed tile
 
-// mbarrier slots shared by both backward kernels
-enum { BB_FULL = 0,      // [2] streamed tile j has landed in buffer j & 1 (transaction bytes of all its copies)
-       BB_SCORES = 2,    // tcgen05.commit: the two score products of the current tile are in TMEM
-       BB_ACC = 3,       // [2] tcgen05.commit: the accumulation step of tile j has finished (slot j & 1; a waiter
-                         //     may lag two tiles behind, which a single barrier's phase parity cannot express)
-       BB_CONSUMED = 5,  // 8 warps: scores copied to registers, the score columns may be overwritten
-       BB_GRAD = 6,      // 8 warps: dS (and P) of the current tile are written
-       BB_RESIDENT = 7,  // 8 warps: the resident operands are in shared memory
-       BB_COUNT = 8 };
+// mbarrier slots shared by both backward kernels; a streamed tile j lives in stage j % NST
+enum { BB_FULL = 0,      // [3] streamed tile j has landed in its stage (transaction bytes of all its copies)
+       BB_ACC = 3,       // [3] tcgen05.commit: the accumulation step of tile j has finished; its stage is free
+       BB_SCORES = 6,    // tcgen05.commit: the two score products of the current tile are in TMEM
+       BB_CONSUMED = 7,  // 8 warps: scores copied to registers, the score columns may be overwritten
+       BB_GRAD = 8,      // 8 warps: dS (and P) of the current tile are written
+       BB_RESIDENT = 9,  // the resident operands are in place (copies' transaction bytes, plus the warps that wrote TMEM)
+       BB_COUNT = 10 };
 
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
 }
 
+// ================================================================================================
+// dq: three stages of (K' tile, V tile); Q' resident in shared memory, dO resident in TMEM
+// ================================================================================================
+constexpr int DQ_NST = 3;
+
 template <int D, typename T>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int KD = D + p.r, KSTEPS = KD >> 4;
+  const int KBUF = (KD / 8) * BCS;             // one K' image tile
+  constexpr int VBUF = (D / 8) * BCS;          // one V image tile
   uint8_t* Qs = smem;                          // [KD/8][128][16 B]  resident Q'
-  uint8_t* Gs = Qs + BQ * KD * 2;              // [D/8][128][16 B]   resident dO
-  const int KBUF = (KD / 8) * BCS, VBUF = (D / 8) * BCS;  // one streamed buffer
-  uint8_t* Ks = Gs + BQ * D * 2;               // 2 x [KD/8][64][16 B]  (one K' image tile each)
-  uint8_t* Vs = Ks + 2 * KBUF;                 // 2 x [D/8][64][16 B]   (one V image tile each)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);
+  uint8_t* Ks = Qs + BQ * KD * 2;              // DQ_NST x [KD/8][64][16 B]
+  uint8_t* Vs = Ks + DQ_NST * KBUF;            // DQ_NST x [D/8][64][16 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + DQ_NST * VBUF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BB_COUNT + 1);
-  float* bias_cb = reinterpret_cast<float*>(tmem_slot + 4);
-  float* bias_sb = bias_cb + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
   const int i0 = (gridDim.x - 1 - blockIdx.x) * BQ;
   const int qoff = p.Nk - p.Nq;
-  const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
-  const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
-  const T* tab = static_cast<const T*>(p.table);
 
   if (warp == BWD_M_WARP) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(&bars[BB_FULL], 1), mbar_init(&bars[BB_FULL + 1], 1);
-    mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1), mbar_init(&bars[BB_ACC + 1], 1);
+    for (int i = 0; i < DQ_NST; ++i) mbar_init(&bars[BB_FULL + i], 1), mbar_init(&bars[BB_ACC + i], 1);
+    mbar_init(&bars[BB_SCORES], 1);
     mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
-    mbar_init(&bars[BB_RESIDENT], BWD_E_WARPS);
+    mbar_init(&bars[BB_RESIDENT], 1 + BWD_E_WARPS);
     mbar_init_fence();
   }
   int n_end = p.Nk;
@@ -125,21 +109,29 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  // TMEM columns: S [0,64), dP [64,128), dS (bf16 pairs) [128,160), dQ' [256, 256+KD)
+  // TMEM columns: S [0,64), dP [64,128), dS (16-bit pairs) [128,160), dO (16-bit pairs) [160,160+D/2), dQ' [256,256+KD)
+  constexpr uint32_t TC_S = 0, TC_DP = 64, TC_DS = 128, TC_DO = 160, TC_DQ = 256;
 
   if (warp == BWD_L_WARP) {
-    // =============================== copies: K' and V image tiles ================================
+    // =============================== copies: resident Q', then K' and V image tiles ===============
+    {
+      const uint8_t* qimg = p.qimg + ((int64_t)u * (int64_t)image_tiles(p.Nq) + i0 / BT) * KBUF;
+      if (lane == 0) mbar_expect_tx(&bars[BB_RESIDENT], BQ * KD * 2);
+      __syncwarp();
+      copy_resident_tiles(Qs, qimg, KD / 8, &bars[BB_RESIDENT], lane);
+    }
     if (lane == 0) {
-      const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * KBUF;
-      const uint8_t* vimg = p.vimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * VBUF;
+      const int64_t ktiles = (int64_t)image_tiles(p.Nk);
+      const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * ktiles * KBUF;
+      const uint8_t* vimg = p.vimg + (int64_t)(b * p.Hk + hk) * ktiles * VBUF;
       for (int j = 0; j < T_tiles; ++j) {
-        const int buf = j & 1, n0 = tile_start(j);
-        // buffer j & 1 was last read by the accumulation step of tile j-2 (its score products finished earlier)
-        if (j >= 2 && !failed) failed = !mbar_wait(&bars[BB_ACC + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        const int st = j % DQ_NST, n0 = tile_start(j);
+        // the stage was last read by the accumulation step of tile j - NST
+        if (j >= DQ_NST && !failed) failed = !mbar_wait(&bars[BB_ACC + st], ((j - DQ_NST) / DQ_NST) & 1, WAIT_LIMIT);
         if (failed) break;
-        mbar_expect_tx(&bars[BB_FULL + buf], KBUF + VBUF);
-        bulk_load(Ks + buf * KBUF, kimg + (int64_t)(n0 / BT) * KBUF, KBUF, &bars[BB_FULL + buf]);
-        bulk_load(Vs + buf * VBUF, vimg + (int64_t)(n0 / BT) * VBUF, VBUF, &bars[BB_FULL + buf]);
+        mbar_expect_tx(&bars[BB_FULL + st], KBUF + VBUF);
+        bulk_load(Ks + st * KBUF, kimg + (int64_t)(n0 / BT) * KBUF, KBUF, &bars[BB_FULL + st]);
+        bulk_load(Vs + st * VBUF, vimg + (int64_t)(n0 / BT) * VBUF, VBUF, &bars[BB_FULL + st]);
       }
       if (failed) atomicOr(p.status, 1u);
     }
@@ -149,21 +141,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
       const uint32_t idesc_q = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
-      const uint32_t qs_addr = smem_u32(Qs), gs_addr = smem_u32(Gs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
-      auto issue_scores = [&](int jt) {
-        const int buf = jt & 1;
-        uint64_t ad = smem_desc(qs_addr, BQ * 16, 128), bd = smem_desc(ks_addr + buf * KBUF, BCS, 128);
-#ifndef POPE_DBG_NO_SCORES
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-          mma_ss(tmem, ad, bd, idesc_s, ks > 0);
-          ad += (2 * BQ * 16) >> 4, bd += (2 * BCS) >> 4;
+      const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+      const uint64_t qd = smem_desc(qs_addr, BQ * 16, 128);
+      auto issue_scores = [&](int jt) {   // S = Q' K'^T (both from shared memory), dP = dO V^T (dO from TMEM)
+        const int st = jt % DQ_NST;
+        const uint64_t kd = smem_desc(ks_addr + st * KBUF, BCS, 128), vd = smem_desc(vs_addr + st * VBUF, BCS, 128);
+        uint32_t alo = desc_lo(qd), blo = desc_lo(kd);
+        mma_ss_lh(tmem + TC_S, alo, desc_hi(qd), blo, desc_hi(kd), idesc_s, 0u);
+#pragma unroll 4
+        for (int ks = 1; ks < KSTEPS; ++ks) {
+          alo += (2 * BQ * 16) >> 4, blo += (2 * BCS) >> 4;
+          mma_ss_lh(tmem + TC_S, alo, desc_hi(qd), blo, desc_hi(kd), idesc_s, 1u);
         }
-        ad = smem_desc(gs_addr, BQ * 16, 128), bd = smem_desc(vs_addr + buf * VBUF, BCS, 128);
-        for (int ks = 0; ks < D / 16; ++ks) {
-          mma_ss(tmem + 64, ad, bd, idesc_s, ks > 0);
-          ad += (2 * BQ * 16) >> 4, bd += (2 * BCS) >> 4;
-        }
-#endif
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          mma_ts_lh(tmem + TC_DP, tmem + TC_DO + ks * 8, desc_lo(vd) + ks * ((2 * BCS) >> 4), desc_hi(vd), idesc_s, ks > 0);
         mma_commit(&bars[BB_SCORES]);
       };
       if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
@@ -172,9 +164,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       issue_scores(0);
       PH_DECL;
       for (int j = 0; j < T_tiles; ++j) {
-        const int buf = j & 1;
+        const int st = j % DQ_NST;
         if (j + 1 < T_tiles) {
-          if (!failed) failed = !mbar_wait(&bars[BB_FULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
+          if (!failed) failed = !mbar_wait(&bars[BB_FULL + (j + 1) % DQ_NST], ((j + 1) / DQ_NST) & 1, WAIT_LIMIT);
           PH(0);
           if (!failed) failed = !mbar_wait(&bars[BB_CONSUMED], j & 1, WAIT_LIMIT);
           PH(1);
@@ -185,18 +177,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
         PH(3);
         fence_after_sync();
-        uint64_t bd = smem_desc(ks_addr + buf * KBUF, 128, BCS);
-#ifndef POPE_DBG_NO_ACC
+        // dQ' += dS K'  (dS from TMEM; the K' tile re-described as an MN-major B operand)
+        const uint64_t bd = smem_desc(ks_addr + st * KBUF, 128, BCS);
 #pragma unroll
-        for (int ks = 0; ks < BT / 16; ++ks) {
-          mma_ts(tmem + 256, tmem + 128 + ks * 8, bd, idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
-          bd += (2 * 128) >> 4;
-        }
-#endif
-        mma_commit(&bars[BB_ACC + buf]);
+        for (int ks = 0; ks < BT / 16; ++ks)
+          mma_ts_lh(tmem + TC_DQ, tmem + TC_DS + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_q,
+                    (j > 0 || ks > 0) ? 1u : 0u);
+        mma_commit(&bars[BB_ACC + st]);
         PH(4);
       }
-      PH_PRINT("dq mma [wait full, wait consumed, issue scores, wait grad, issue acc]", T_tiles);
+      PH_PRINT("dq mma  [wait full, wait consumed, issue scores, wait grad, issue acc]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -209,95 +199,95 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   }
 
   // =============================== elementwise warps ================================================
-  {
-    const T* gbase = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h;
-    load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    stage_xform<D, BQ, T, true>(qbase, p.sq.n, i0, p.Nq, tab, p.Nk, qoff, p.r, bias_cb, bias_sb, Qs, tid);
-    stage_plain<D, BQ, T>(gbase, p.sdo.n, i0, p.Nq, Gs, tid);
-    fence_async_smem();
-    warp_arrive(&bars[BB_RESIDENT], lane);
-  }
   const int row = tid & 127, half = tid >> 7;           // thread = (query row, 32-key half)
   const int gi = i0 + row;
-  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
+  {
+    // dO rows into TMEM, the A operand of dP = dO V^T: 16 columns (32 features) per step, the two threads
+    // of a row take alternate steps
+    const T* grow = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h + (int64_t)gi * p.sdo.n;
+#pragma unroll
+    for (int g = 0; g < D / 32; ++g) {
+      if ((g & 1) != half) continue;
+      uint32_t w[16];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 v4 = make_uint4(0, 0, 0, 0);
+        if (gi < p.Nq) v4 = __ldg(reinterpret_cast<const uint4*>(grow + g * 32 + q4 * 8));
+        w[q4 * 4] = v4.x, w[q4 * 4 + 1] = v4.y, w[q4 * 4 + 2] = v4.z, w[q4 * 4 + 3] = v4.w;
+      }
+      tmem_st16(tmem + lane_base + TC_DO + g * 16, w);
+    }
+    tmem_st_wait();
+    fence_before_sync();
+    warp_arrive(&bars[BB_RESIDENT], lane);
+  }
   const float lse2 = gi < p.Nq ? p.lse[(int64_t)u * p.Nq + gi] * LOG2E : -CUDART_INF_F;
   const float lse_use = lse2 == -CUDART_INF_F ? 0.f : lse2;
   const float dlt = gi < p.Nq ? p.delta[(int64_t)u * p.Nq + gi] : 0.f;
 
   PH_DECL;
   for (int j = 0; j < T_tiles; ++j) {
-    const int buf = j & 1, n0 = tile_start(j);
+    const int n0 = tile_start(j);
     // key visibility of this thread's 32-key half (key-padding mask, ragged end): the same for every row
     uint32_t vis = 0xffffffffu;
     if (maskb || n0 + BT > p.Nk) {
       const int jk = n0 + half * 32 + lane;
       vis = __ballot_sync(0xffffffffu, jk < p.Nk && (!maskb || maskb[(int64_t)jk * p.msn] != 0));
     }
-    if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
-    fence_after_sync();
-    PH(0);
-#ifdef POPE_DBG_NO_ELEM
-    if (p.Nq > 0) {
-      fence_before_sync();
-      warp_arrive(&bars[BB_CONSUMED], lane);
-      if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
-      warp_arrive(&bars[BB_GRAD], lane);
-      continue;
-    }
-#endif
     if (p.causal) {
       const int lim = gi - (n0 + half * 32);  // columns <= lim visible
       vis &= lim >= 31 ? 0xffffffffu : (lim < 0 ? 0u : ((2u << lim) - 1u));
     }
     if (lse2 == -CUDART_INF_F) vis = 0u;
     const bool all_vis = __all_sync(0xffffffffu, vis == 0xffffffffu);   // interior tile: no masking work
+    if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
+    fence_after_sync();
+    PH(0);
+    uint32_t sv[32], dv[32];
+    tmem_ld32(tmem + lane_base + TC_S + half * 32, sv);
+    tmem_ld32(tmem + lane_base + TC_DP + half * 32, dv);
+    tmem_ld_wait();
+    // every score of this tile is in registers: the next score products may overwrite them
+    fence_before_sync();
+    warp_arrive(&bars[BB_CONSUMED], lane);
+    PH(1);
     uint32_t pk[16];
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {   // 16 key columns at a time keeps the register footprint small
-      uint32_t sv[16], dv[16];
-      tmem_ld16(tmem + lane_base + half * 32 + hh * 16, sv);
-      tmem_ld16(tmem + lane_base + 64 + half * 32 + hh * 16, dv);
-      tmem_ld_wait();
-      if (hh == 1) {   // every score of this tile is in registers: the next score products may overwrite them
-        fence_before_sync();
-        warp_arrive(&bars[BB_CONSUMED], lane);
+    for (int e = 0; e < 16; ++e) {
+      float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse_use));
+      float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse_use));
+      if (!all_vis) {
+        p0 = ((vis >> (2 * e)) & 1u) ? p0 : 0.f;
+        p1 = ((vis >> (2 * e + 1)) & 1u) ? p1 : 0.f;
       }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse_use));
-        float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse_use));
-        if (!all_vis) {
-          p0 = ((vis >> (hh * 16 + 2 * e)) & 1u) ? p0 : 0.f;
-          p1 = ((vis >> (hh * 16 + 2 * e + 1)) & 1u) ? p1 : 0.f;
-        }
-        const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
-        const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
-        pk[hh * 8 + e] = pack2<T>(d0, d1);
-      }
+      const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
+      const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
+      pk[e] = pack2<T>(d0, d1);
     }
-    PH(1);
-    // the dS columns were read by the accumulation step of tile j-1
-    if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
     PH(2);
-    tmem_st16(tmem + lane_base + 128 + half * 16, pk);
+    // the dS columns were read by the accumulation step of tile j-1
+    if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (j - 1) % DQ_NST], ((j - 1) / DQ_NST) & 1, WAIT_LIMIT);
+    PH(3);
+    tmem_st16(tmem + lane_base + TC_DS + half * 16, pk);
     tmem_st_wait();
     fence_before_sync();
     warp_arrive(&bars[BB_GRAD], lane);
-    PH(3);
+    PH(4);
   }
-  if (tid == 0) PH_PRINT("dq elem [wait scores, ld+math, wait acc, st+arrive]", T_tiles);
+  if (tid == 0) PH_PRINT("dq elem [wait scores, ld+arrive, math, wait acc, st+arrive]", T_tiles);
+  PH(5);
 
   // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
-  if (!failed) failed = !mbar_wait(&bars[BB_ACC + ((T_tiles - 1) & 1)], ((T_tiles - 1) >> 1) & 1, WAIT_LIMIT);
+  if (!failed) failed = !mbar_wait(&bars[BB_ACC + (T_tiles - 1) % DQ_NST], ((T_tiles - 1) / DQ_NST) & 1, WAIT_LIMIT);
   fence_after_sync();
   {
     constexpr int HW = D / 2;  // features handled by this thread: [half*HW, half*HW + HW)
-    const uint32_t acc = tmem + lane_base + 256;
-    const T* qrow = qbase + (int64_t)gi * p.sq.n;
+    const uint32_t acc = tmem + lane_base + TC_DQ;
+    const T* qrow = (const T*)p.q + b * p.sq.b + h * p.sq.h + (int64_t)gi * p.sq.n;
     T* dqrow = (T*)p.dq + b * p.sdq.b + h * p.sdq.h + (int64_t)gi * p.sdq.n;
-    const float* frow = p.r > 0 ? p.freqs + (int64_t)(qoff + gi) * p.sfn : nullptr;
+    const int64_t trow = (int64_t)(qoff + gi) * p.r;   // row of the fp32 cos / sin tables
     float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + h * p.sdf.h + (int64_t)(qoff + gi) * p.sdf.n : nullptr;
 #pragma unroll
     for (int c0 = 0; c0 < HW; c0 += 16) {
@@ -309,30 +299,40 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       tmem_ld_wait();
       if (gi < p.Nq) {
         uint32_t outw[8];
+        if (rot) {
+          const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(qrow + cbase)), q1 = __ldg(reinterpret_cast<const uint4*>(qrow + cbase + 8));
+          const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+          float cf[16], sf[16];
 #pragma unroll
-        for (int e = 0; e < 16; e += 2) {
-          float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
-          if (rot) {
-            const uint32_t qw = *reinterpret_cast<const uint32_t*>(qrow + cbase + e);
-            const float2 x = unpack2<T>(qw);
-            float s0, c0f, s1, c1f;
-            sincosf(frow[cbase + e] - biasr[cbase + e], &s0, &c0f);
-            sincosf(frow[cbase + e + 1] - biasr[cbase + e + 1], &s1, &c1f);
+          for (int e4 = 0; e4 < 4; ++e4) {
+            const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.ctab + trow + cbase) + e4);
+            const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.stab + trow + cbase) + e4);
+            cf[e4 * 4] = c4.x, cf[e4 * 4 + 1] = c4.y, cf[e4 * 4 + 2] = c4.z, cf[e4 * 4 + 3] = c4.w;
+            sf[e4 * 4] = s4.x, sf[e4 * 4 + 1] = s4.y, sf[e4 * 4 + 2] = s4.z, sf[e4 * 4 + 3] = s4.w;
+          }
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) {
+            const float2 x = unpack2<T>(qw[e >> 1]);
+            const float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
             const float h0 = __uint_as_float(gs[e]), h1 = __uint_as_float(gs[e + 1]);
             if (dfrow) {
-              atomicAdd(dfrow + cbase + e, softplus_f(x.x) * (h0 * c0f - g0 * s0));
-              atomicAdd(dfrow + cbase + e + 1, softplus_f(x.y) * (h1 * c1f - g1 * s1));
+              atomicAdd(dfrow + cbase + e, softplus_fast(x.x) * (h0 * cf[e] - g0 * sf[e]));
+              atomicAdd(dfrow + cbase + e + 1, softplus_fast(x.y) * (h1 * cf[e + 1] - g1 * sf[e + 1]));
             }
-            g0 = (g0 * c0f + h0 * s0) * sigmoid_f(x.x);
-            g1 = (g1 * c1f + h1 * s1) * sigmoid_f(x.y);
+            outw[e >> 1] = pack2<T>((g0 * cf[e] + h0 * sf[e]) * sigmoid_fast(x.x),
+                                    (g1 * cf[e + 1] + h1 * sf[e + 1]) * sigmoid_fast(x.y));
           }
-          outw[e >> 1] = pack2<T>(g0, g1);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; e += 2) outw[e >> 1] = pack2<T>(__uint_as_float(gc[e]), __uint_as_float(gc[e + 1]));
         }
         *reinterpret_cast<uint4*>(dqrow + cbase) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
         *reinterpret_cast<uint4*>(dqrow + cbase + 8) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
       }
     }
   }
+  PH(6);
+  if (tid == 0) PH_PRINT("dq elem [.. 5: print, 6: epilogue TOTAL clk / tiles]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier

@@ -15,8 +15,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   float* rowstat = reinterpret_cast<float*>(Ds + BQ * BT * 2);  // 2 bufs x (64 lse*log2e, 64 delta)
   uint64_t* bars = reinterpret_cast<uint64_t*>(rowstat + 2 * 128);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BB_COUNT + 1);
-  float* bias_cb = reinterpret_cast<float*>(Ps);   // only needed while the resident K' is built: borrows the P^T tile
-  float* bias_sb = bias_cb + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.Hk, hk = u % p.Hk;
@@ -25,7 +23,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const int groups = p.H / p.Hk;
   const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
   const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
-  const T* tab = static_cast<const T*>(p.table);
 
   if (warp == BWD_M_WARP) {
     tmem_alloc(tmem_slot, 512);
@@ -35,7 +32,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     mbar_init(&bars[BB_FULL], 1), mbar_init(&bars[BB_FULL + 1], 1);
     mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1), mbar_init(&bars[BB_ACC + 1], 1);
     mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
-    mbar_init(&bars[BB_RESIDENT], BWD_E_WARPS);
+    mbar_init(&bars[BB_RESIDENT], 1);
     mbar_init_fence();
   }
   // query tiles: under the causal mask rows i < j0 see none of this CTA's keys
@@ -59,6 +56,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
 
   if (warp == BWD_L_WARP) {
     // =============================== copies: Q' and dO image tiles, lse / delta rows =============
+    {   // resident K' (phase bias folded in) and V: two image tiles each, one 1 KB copy per chunk column and 64 rows
+      const int64_t t0 = (int64_t)u * (int64_t)image_tiles(p.Nk) + j0 / BT;
+      if (T_tiles > 0) {   // (a CTA without any visible query row would leave with these copies in flight)
+        if (lane == 0) mbar_expect_tx(&bars[BB_RESIDENT], BQ * KD * 2 + BQ * D * 2);
+        __syncwarp();
+        copy_resident_tiles(Ks, p.kimg + t0 * KBUF, KD / 8, &bars[BB_RESIDENT], lane);
+        copy_resident_tiles(Vs, p.vimg + t0 * VBUF, D / 8, &bars[BB_RESIDENT], lane);
+      }
+    }
     if (lane == 0) {
       const int64_t qtiles = (int64_t)image_tiles(p.Nq);
       for (int j = 0; j < T_tiles; ++j) {
@@ -85,42 +91,52 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       const uint32_t ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
       auto issue_scores = [&](int jt) {
         const int buf = jt & 1;
-        uint64_t ad = smem_desc(ks_addr, BQ * 16, 128), bd = smem_desc(qb_addr + buf * KBUF, BCS, 128);
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-          mma_ss(tmem, ad, bd, idesc_s, ks > 0);
-          ad += (2 * BQ * 16) >> 4, bd += (2 * BCS) >> 4;
+        const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128), qb = smem_desc(qb_addr + buf * KBUF, BCS, 128);
+        const uint64_t va = smem_desc(vs_addr, BQ * 16, 128), gb = smem_desc(gb_addr + buf * VBUF, BCS, 128);
+        uint32_t alo = desc_lo(ka), blo = desc_lo(qb);
+        mma_ss_lh(tmem, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 0u);
+#pragma unroll 4
+        for (int ks = 1; ks < KSTEPS; ++ks) {
+          alo += (2 * BQ * 16) >> 4, blo += (2 * BCS) >> 4;
+          mma_ss_lh(tmem, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 1u);
         }
-        ad = smem_desc(vs_addr, BQ * 16, 128), bd = smem_desc(gb_addr + buf * VBUF, BCS, 128);
-        for (int ks = 0; ks < D / 16; ++ks) {
-          mma_ss(tmem + 64, ad, bd, idesc_s, ks > 0);
-          ad += (2 * BQ * 16) >> 4, bd += (2 * BCS) >> 4;
-        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          mma_ss_lh(tmem + 64, desc_lo(va) + ks * ((2 * BQ * 16) >> 4), desc_hi(va), desc_lo(gb) + ks * ((2 * BCS) >> 4),
+                    desc_hi(gb), idesc_s, ks > 0);
         mma_commit(&bars[BB_SCORES]);
       };
       if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
       if (!mbar_wait(&bars[BB_FULL], 0, WAIT_LIMIT)) failed = true;
       fence_after_sync();
       issue_scores(0);
+      PH_DECL;
       for (int j = 0; j < T_tiles; ++j) {
         const int buf = j & 1;
         if (j + 1 < T_tiles) {
           if (!failed) failed = !mbar_wait(&bars[BB_FULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
+          PH(0);
           if (!failed) failed = !mbar_wait(&bars[BB_CONSUMED], j & 1, WAIT_LIMIT);
+          PH(1);
           fence_after_sync();
           issue_scores(j + 1);
+          PH(2);
         }
         if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
+        PH(3);
         fence_after_sync();
-        uint64_t pa = smem_desc(ps_addr, BQ * 16, 128), da = smem_desc(ds_addr, BQ * 16, 128);
-        uint64_t gd = smem_desc(gb_addr + buf * VBUF, 128, BCS), qd = smem_desc(qb_addr + buf * KBUF, 128, BCS);
+        const uint64_t pa = smem_desc(ps_addr, BQ * 16, 128), da = smem_desc(ds_addr, BQ * 16, 128);
+        const uint64_t gd = smem_desc(gb_addr + buf * VBUF, 128, BCS), qd = smem_desc(qb_addr + buf * KBUF, 128, BCS);
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks) {
-          mma_ss(tmem + 128, pa, gd, idesc_v, (j > 0 || ks > 0) ? 1u : 0u);
-          mma_ss(tmem + 256, da, qd, idesc_k, (j > 0 || ks > 0) ? 1u : 0u);
-          pa += (2 * BQ * 16) >> 4, da += (2 * BQ * 16) >> 4, gd += (2 * 128) >> 4, qd += (2 * 128) >> 4;
+          const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u, astep = ks * ((2 * BQ * 16) >> 4), bstep = ks * ((2 * 128) >> 4);
+          mma_ss_lh(tmem + 256, desc_lo(da) + astep, desc_hi(da), desc_lo(qd) + bstep, desc_hi(qd), idesc_k, acc);
+          mma_ss_lh(tmem + 128, desc_lo(pa) + astep, desc_hi(pa), desc_lo(gd) + bstep, desc_hi(gd), idesc_v, acc);
         }
         mma_commit(&bars[BB_ACC + buf]);
+        PH(4);
       }
+      PH_PRINT("dkdv mma  [wait full, wait consumed, issue scores, wait grad, issue acc]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -133,75 +149,69 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   }
 
   // =============================== elementwise warps ================================================
-  const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
   const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
-  load_bias_trig(biasr, p.r, 1.f, bias_cb, bias_sb, tid);
-  asm volatile("bar.sync 1, 256;" ::: "memory");
-  stage_xform<D, BQ, T, true>(kbase, p.sk.n, j0, p.Nk, tab, p.Nk, 0, p.r, bias_cb, bias_sb, Ks, tid);
-  stage_plain<D, BQ, T>(vbase, p.sv.n, j0, p.Nk, Vs, tid);
-  asm volatile("bar.sync 1, 256;" ::: "memory");   // the bias trig borrowed the P^T tile: everyone is done reading it
-  fence_async_smem();
-  warp_arrive(&bars[BB_RESIDENT], lane);
 
   const int row = tid & 127, half = tid >> 7;          // thread = (key row, 32-query half)
   const int gj = j0 + row;
   const bool key_ok = gj < p.Nk && (!maskb || maskb[(int64_t)gj * p.msn] != 0);
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-
+  PH_DECL;
   for (int j = 0; j < T_tiles; ++j) {
     const int buf = j & 1;
     const int m0 = tile_start(j);
     if (!failed) failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the lse / delta read
     if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
     fence_after_sync();
+    PH(0);
     const float* st = rowstat + buf * 128 + half * 32;
     // interior tile for this warp: every key row valid and (causal) every key at or before every query column;
     // out-of-range queries and rows without any visible key carry lse = +inf, which makes P exactly 0
     const int gj_hi = j0 + (warp & 3) * 32 + 31, gi_lo = m0 + half * 32;
     const bool interior = __all_sync(0xffffffffu, key_ok) && (!p.causal || gj_hi <= gi_lo);
+    uint32_t sv[32], dv[32];
+    tmem_ld32(tmem + lane_base + half * 32, sv);
+    tmem_ld32(tmem + lane_base + 64 + half * 32, dv);
+    tmem_ld_wait();
+    // every score of this tile is in registers: the next score products may overwrite them
+    fence_before_sync();
+    warp_arrive(&bars[BB_CONSUMED], lane);
+    PH(1);
+    uint32_t pw[16], dw[16];   // P^T and dS^T of this thread's 32 query columns, packed in pairs
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {   // 16 query columns at a time
-      uint32_t sv[16], dv[16];
-      tmem_ld16(tmem + lane_base + half * 32 + hh * 16, sv);
-      tmem_ld16(tmem + lane_base + 64 + half * 32 + hh * 16, dv);
-      tmem_ld_wait();
-      if (hh == 1) {   // every score of this tile is in registers
-        fence_before_sync();
-        warp_arrive(&bars[BB_CONSUMED], lane);
-      } else if (j >= 1 && !failed) {
-        // the P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
-        failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
-      }
+    for (int c4 = 0; c4 < 8; ++c4) {
+      const float4 l4 = *reinterpret_cast<const float4*>(st + c4 * 4), d4 = *reinterpret_cast<const float4*>(st + 64 + c4 * 4);
+      const float l2v[4] = {l4.x, l4.y, l4.z, l4.w}, dlv[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int cq = hh * 16 + cc * 8;   // first query column of this 8-wide chunk within the thread's half
-        const float4 la = *reinterpret_cast<const float4*>(st + cq), lb = *reinterpret_cast<const float4*>(st + cq + 4);
-        const float4 da = *reinterpret_cast<const float4*>(st + 64 + cq), db = *reinterpret_cast<const float4*>(st + 64 + cq + 4);
-        const float l2v[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
-        const float dlv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-        uint32_t pw[4], dw[4];
+      for (int e = 0; e < 2; ++e) {
+        float pv[2], dsv[2];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const int cl = cc * 8 + e * 2 + t;          // index into sv / dv
-            float pr = ex2_approx(fmaf(__uint_as_float(sv[cl]), p.scale_log2, -l2v[e * 2 + t]));
-            if (!interior) pr = (key_ok && (!p.causal || gj <= gi_lo + cq + e * 2 + t)) ? pr : 0.f;
-            pv[t] = pr;
-            dsv[t] = pr * (__uint_as_float(dv[cl]) - dlv[e * 2 + t]) * p.scale;
-          }
-          pw[e] = pack2<T>(pv[0], pv[1]);
-          dw[e] = pack2<T>(dsv[0], dsv[1]);
+        for (int t = 0; t < 2; ++t) {
+          const int cl = c4 * 4 + e * 2 + t;   // query column within the thread's half
+          float pr = ex2_approx(fmaf(__uint_as_float(sv[cl]), p.scale_log2, -l2v[e * 2 + t]));
+          if (!interior) pr = (key_ok && (!p.causal || gj <= gi_lo + cl)) ? pr : 0.f;
+          pv[t] = pr;
+          dsv[t] = pr * (__uint_as_float(dv[cl]) - dlv[e * 2 + t]) * p.scale;
         }
-        const int chunk = half * 4 + hh * 2 + cc;
-        *reinterpret_cast<uint4*>(Ps + chunk * (BQ * 16) + row * 16) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-        *reinterpret_cast<uint4*>(Ds + chunk * (BQ * 16) + row * 16) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+        pw[c4 * 2 + e] = pack2<T>(pv[0], pv[1]);
+        dw[c4 * 2 + e] = pack2<T>(dsv[0], dsv[1]);
       }
+    }
+    PH(2);
+    // the P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
+    if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+    PH(3);
+#pragma unroll
+    for (int c8 = 0; c8 < 4; ++c8) {
+      const int chunk = half * 4 + c8;
+      *reinterpret_cast<uint4*>(Ps + chunk * (BQ * 16) + row * 16) = make_uint4(pw[c8 * 4], pw[c8 * 4 + 1], pw[c8 * 4 + 2], pw[c8 * 4 + 3]);
+      *reinterpret_cast<uint4*>(Ds + chunk * (BQ * 16) + row * 16) = make_uint4(dw[c8 * 4], dw[c8 * 4 + 1], dw[c8 * 4 + 2], dw[c8 * 4 + 3]);
     }
     fence_async_smem();
     warp_arrive(&bars[BB_GRAD], lane);
+    PH(4);
   }
+  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [wait scores, ld+arrive, math, wait acc, st+arrive]", T_tiles);
+  PH(5);
 
   // ---- epilogue ---------------------------------------------------------------------------------
   if (T_tiles > 0 && !failed)
@@ -209,7 +219,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   fence_after_sync();
   asm volatile("bar.sync 1, 256;" ::: "memory");   // every MMA is done: the streamed buffers can be reused
   float* red = reinterpret_cast<float*>(Qb);   // [r] per-CTA sum of the key-phase gradient
-  for (int c = tid; c < p.r; c += 256) red[c] = 0.f;
+  float* bias_cb = red + 128;                  // cos / sin of the head's phase bias
+  float* bias_sb = red + 256;
+  for (int c = tid; c < p.r; c += 256) {
+    red[c] = 0.f;
+    sincosf(biasr[c], &bias_sb[c], &bias_cb[c]);
+  }
   asm volatile("bar.sync 1, 256;" ::: "memory");
   {
     constexpr int HW = D / 2;
@@ -217,7 +232,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     const T* krow = kbase + (int64_t)gj * p.sk.n;
     T* dkrow = (T*)p.dk + b * p.sdk.b + hk * p.sdk.h + (int64_t)gj * p.sdk.n;
     T* dvrow = (T*)p.dv + b * p.sdv.b + hk * p.sdv.h + (int64_t)gj * p.sdv.n;
-    const float* frow = p.r > 0 ? p.freqs + (int64_t)gj * p.sfn : nullptr;
+    const int64_t trow = (int64_t)gj * p.r;   // row of the fp32 cos / sin tables
     float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + hk * p.sdf.h + (int64_t)gj * p.sdf.n : nullptr;
     const bool live = gj < p.Nk;
 #pragma unroll
@@ -236,29 +251,48 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       }
       uint32_t wv[8], wk[8];
 #pragma unroll
-      for (int e = 0; e < 16; e += 2) {
-        wv[e >> 1] = pack2<T>(__uint_as_float(gv[e]), __uint_as_float(gv[e + 1]));
-        float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
-        if (rot) {
+      for (int e = 0; e < 16; e += 2) wv[e >> 1] = pack2<T>(__uint_as_float(gv[e]), __uint_as_float(gv[e + 1]));
+      if (rot) {
+        uint32_t kw[8] = {};
+        float cf[16], sf[16];
+        if (live) {
+          const uint4 k0 = __ldg(reinterpret_cast<const uint4*>(krow + cbase)), k1 = __ldg(reinterpret_cast<const uint4*>(krow + cbase + 8));
+          kw[0] = k0.x, kw[1] = k0.y, kw[2] = k0.z, kw[3] = k0.w, kw[4] = k1.x, kw[5] = k1.y, kw[6] = k1.z, kw[7] = k1.w;
+#pragma unroll
+          for (int e4 = 0; e4 < 4; ++e4) {
+            const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.ctab + trow + cbase) + e4);
+            const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.stab + trow + cbase) + e4);
+            const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {   // cos(f + b), sin(f + b)
+              const float cb = bias_cb[cbase + e4 * 4 + t], sb = bias_sb[cbase + e4 * 4 + t];
+              cf[e4 * 4 + t] = cc[t] * cb - ss[t] * sb;
+              sf[e4 * 4 + t] = ss[t] * cb + cc[t] * sb;
+            }
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
           float d0 = 0.f, d1 = 0.f;
           if (live) {
-            const float2 x = unpack2<T>(*reinterpret_cast<const uint32_t*>(krow + cbase + e));
-            float s0, c0f, s1, c1f;
-            sincosf(frow[cbase + e] + biasr[cbase + e], &s0, &c0f);
-            sincosf(frow[cbase + e + 1] + biasr[cbase + e + 1], &s1, &c1f);
+            const float2 x = unpack2<T>(kw[e >> 1]);
             const float h0 = __uint_as_float(gs[e]), h1 = __uint_as_float(gs[e + 1]);
-            d0 = softplus_f(x.x) * (h0 * c0f - g0 * s0);
-            d1 = softplus_f(x.y) * (h1 * c1f - g1 * s1);
+            d0 = softplus_fast(x.x) * (h0 * cf[e] - g0 * sf[e]);
+            d1 = softplus_fast(x.y) * (h1 * cf[e + 1] - g1 * sf[e + 1]);
             if (dfrow) atomicAdd(dfrow + cbase + e, d0), atomicAdd(dfrow + cbase + e + 1, d1);
-            g0 = (g0 * c0f + h0 * s0) * sigmoid_f(x.x);
-            g1 = (g1 * c1f + h1 * s1) * sigmoid_f(x.y);
+            g0 = (g0 * cf[e] + h0 * sf[e]) * sigmoid_fast(x.x);
+            g1 = (g1 * cf[e + 1] + h1 * sf[e + 1]) * sigmoid_fast(x.y);
           }
           if (p.dbias) {   // warp-uniform branch: sum over the 32 key rows of this warp
             d0 = warp_sum(d0), d1 = warp_sum(d1);
             if ((tid & 31) == 0) atomicAdd(&red[cbase + e], d0), atomicAdd(&red[cbase + e + 1], d1);
           }
+          wk[e >> 1] = pack2<T>(g0, g1);
         }
-        wk[e >> 1] = pack2<T>(g0, g1);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) wk[e >> 1] = pack2<T>(__uint_as_float(gc[e]), __uint_as_float(gc[e + 1]));
       }
       if (live) {
         *reinterpret_cast<uint4*>(dvrow + cbase) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
@@ -272,6 +306,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     asm volatile("bar.sync 1, 256;" ::: "memory");
     for (int c = tid; c < p.r; c += 256) atomicAdd(p.dbias + hk * p.dbias_sh + c, red[c]);
   }
+  PH(6);
+  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [.. 5: print, 6: epilogue TOTAL clk / tiles]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier
@@ -309,11 +345,11 @@ __global__ void bwd_rowstat_kernel(const float* __restrict__ lse, const float* _
   o[BT + t] = i < Nq ? delta[(int64_t)u * Nq + i] : 0.f;
 }
 
-// workspace: [delta][16-bit cos / sin table][K' images][Q' images][V images][dO images][row statistics], each
+// workspace: [delta][fp32 cos / sin table][K' images][Q' images][V images][dO images][row statistics], each
 // rounded up to 256 bytes
 static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 static size_t delta_bytes(const PopeShape& s) { return up256((size_t)s.B * s.H * s.Nq * sizeof(float)); }
-static size_t bwd_table_bytes(const PopeShape& s) { return up256(trig_table_bytes(s.Nk, s.r)); }
+static size_t bwd_table_bytes(const PopeShape& s) { return trig_table_f32_bytes(s.Nk, s.r); }
 static size_t rowstat_bytes(const PopeShape& s) { return up256((size_t)s.B * s.H * image_tiles(s.Nq) * 2 * BT * sizeof(float)); }
 
 size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
@@ -330,7 +366,8 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const bool bf16 = s.dtype == POPE_BF16;
   uint8_t* ws = reinterpret_cast<uint8_t*>(a.workspace);
   float* delta = reinterpret_cast<float*>(ws);
-  void* table = ws + delta_bytes(s);
+  float* ctab = reinterpret_cast<float*>(ws + delta_bytes(s));
+  float* stab = ctab + (size_t)s.Nk * s.r;
   uint8_t* kimg = ws + delta_bytes(s) + bwd_table_bytes(s);
   uint8_t* qimg = kimg + up256(image_bytes(s.B * s.Hk, s.Nk, KD));
   uint8_t* vimg = qimg + up256(image_bytes(s.B * s.H, s.Nq, KD));
@@ -338,12 +375,14 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   float* rowstat = reinterpret_cast<float*>(gimg + up256(image_bytes(s.B * s.H, s.Nq, s.d)));
   cudaError_t e = attn_bwd_delta(a, delta, st);
   if (e != cudaSuccess) return e;
-  if (s.r > 0 && (e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, table, bf16, st)) != cudaSuccess) return e;
-  if ((e = launch_expand_images(a.k, a.sk, s.B, s.Hk, s.Nk, s.d, s.r, bf16, table, s.Nk, 0, kimg, st)) != cudaSuccess) return e;
-  if ((e = launch_expand_images(a.q, a.sq, s.B, s.H, s.Nq, s.d, s.r, bf16, table, s.Nk, s.Nk - s.Nq, qimg, st)) != cudaSuccess) return e;
-  // V and dO: the same tiles without any rotated features (a pure re-layout)
-  if ((e = launch_expand_images(a.v, a.sv, s.B, s.Hk, s.Nk, s.d, 0, bf16, table, s.Nk, 0, vimg, st)) != cudaSuccess) return e;
-  if ((e = launch_expand_images(a.dout, a.sdo, s.B, s.H, s.Nq, s.d, 0, bf16, table, s.Nk, 0, gimg, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_table_f32(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, ctab, stab, st)) != cudaSuccess) return e;
+  // K' (phase bias folded in), Q', and V / dO as the same tiles without rotated features (a pure re-layout)
+  ExpandJobs jobs;
+  jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg);
+  jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg);
+  jobs.job[2] = expand_job(a.v, a.sv, s.B, s.Hk, s.Nk, 0, 0, nullptr, 0, vimg);
+  jobs.job[3] = expand_job(a.dout, a.sdo, s.B, s.H, s.Nq, 0, 0, nullptr, 0, gimg);
+  if ((e = launch_expand_images(jobs, 4, s.d, bf16, ctab, stab, st)) != cudaSuccess) return e;
   bwd_rowstat_kernel<<<dim3((unsigned)image_tiles(s.Nq), s.B * s.H), BT, 0, st>>>(a.lse, delta, s.Nq, rowstat);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   TcBwdP p = {};
@@ -353,14 +392,14 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.sdo = a.sdo, p.sdq = a.sdq, p.sdk = a.sdk, p.sdv = a.sdv, p.sdf = a.sdf;
   p.freqs = a.embed.freqs, p.bias = a.embed.bias, p.lse = a.lse, p.delta = delta;
   p.sfn = a.embed.sf.n, p.bias_sh = a.embed.bias_stride_h, p.dbias_sh = a.dbias_stride_h;
-  p.table = table, p.kimg = kimg, p.qimg = qimg, p.vimg = vimg, p.gimg = gimg, p.rowstat = rowstat;
+  p.ctab = ctab, p.stab = stab, p.kimg = kimg, p.qimg = qimg, p.vimg = vimg, p.gimg = gimg, p.rowstat = rowstat;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   p.dfreqs = s.r > 0 ? a.dfreqs : nullptr, p.dbias = s.r > 0 ? a.dbias : nullptr;
   p.status = tc_status_ptr();
   if (!p.status) return cudaErrorInvalidSymbol;
-  const size_t streamed = 2 * (size_t)BT * KD * 2 + 2 * (size_t)BT * D * 2;
-  size_t smem_q = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + (BB_COUNT + 1) * 8 + 16 + 1024;
-  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + streamed + 2 * BQ * BT * 2 + 256 * 4 + (BB_COUNT + 1) * 8 + 16 + 16;
+  const size_t stage = (size_t)BT * KD * 2 + (size_t)BT * D * 2;
+  size_t smem_q = (size_t)BQ * KD * 2 + DQ_NST * stage + (BB_COUNT + 1) * 8 + 16;
+  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + 2 * stage + 2 * BQ * BT * 2 + 256 * 4 + (BB_COUNT + 1) * 8 + 16 + 16;
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;

@@ -67,28 +67,6 @@ unsigned int tc_read_status() {
   return v;
 }
 
-// ---- pre-pass: cos / sin tables of freqs as 16-bit arrays [n][r] -------------------------------------
-template <typename TT>
-__global__ void pope_trig_table_kernel(const float* freqs, int64_t sfn, int n, int r, TT* table) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)n * r) return;
-  const int pos = idx / r, c = idx % r;
-  float sn, cs;
-  sincosf(freqs[pos * sfn + c], &sn, &cs);
-  table[idx] = from_f32<TT>(cs);
-  table[(int64_t)n * r + idx] = from_f32<TT>(sn);
-}
-
-cudaError_t launch_trig_table(const float* freqs, int64_t sfn, int n, int r, void* table, bool as_bf16, cudaStream_t st) {
-  const int64_t total = (int64_t)n * r;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (as_bf16)
-    pope_trig_table_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(freqs, sfn, n, r, static_cast<__nv_bfloat16*>(table));
-  else
-    pope_trig_table_kernel<__half><<<blocks, 256, 0, st>>>(freqs, sfn, n, r, static_cast<__half*>(table));
-  return cudaGetLastError();
-}
-
 bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
                      int64_t sh, int64_t sb, int box_rows) {
   typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -131,8 +109,8 @@ struct TcFwdP {
   int64_t sfn;
   const float* bias;
   int64_t bias_sh;
-  const void* table;   // cos / sin in the dtype of q, k, v
-  const uint8_t* kimg; // expanded K' image tiles, (B * Hk) units
+  const uint8_t* qimg; // expanded Q' image tiles, (B * H) units
+  const uint8_t* kimg; // expanded K' image tiles (phase bias folded in), (B * Hk) units
   const uint8_t* mask;
   int64_t msb, msn;
 };
@@ -170,13 +148,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
   uint8_t* Vs = Ks + 2 * KBUF;                      // 2 bufs  x [D/8 chunks][64 keys][16 B]; 128-byte aligned (KD % 16 == 0)
   uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT + 1);
-  float* bias_cb = reinterpret_cast<float*>(tmem_slot + 4);            // cos / sin of the head's phase bias
-  float* bias_sb = bias_cb + 128;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
   const int i0 = (gridDim.x - 1 - blockIdx.x) * (2 * TQ);  // heavy (late) row blocks first
-  const int qoff = p.Nk - p.Nq;
 
   int n_end = p.Nk;
   if (p.causal) n_end = min(n_end, min(i0 + 2 * TQ, p.Nq));
@@ -196,7 +171,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
       mbar_init(&bars[B_SFULL + i], 1), mbar_init(&bars[B_PVDONE + i], 1);
     }
     for (int i = 0; i < 4; ++i) mbar_init(&bars[B_PFULL + i], 4);
-    mbar_init(&bars[B_QFULL], FWD_SOFTMAX_WARPS);
+    mbar_init(&bars[B_QFULL], 1);
     mbar_init_fence();
   }
   fence_before_sync();
@@ -209,27 +184,27 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
     // =============================== copies ==================================================
     // K'(j) is one contiguous image tile; V(j) arrives as D/8 boxes of 64 keys x 16 bytes, each landing on its
     // chunk column.  A buffer is refilled as soon as the MMA that read it has completed.
+    // the two resident Q' tiles: four image tiles, one 1 KB copy per chunk column and 64 rows
+    {
+      const uint8_t* qimg = p.qimg + ((int64_t)u * (int64_t)image_tiles(p.Nq) + i0 / IMAGE_ROWS) * KBUF;
+      if (lane == 0) mbar_expect_tx(&bars[B_QFULL], 2 * TQ * KD * 2);
+      __syncwarp();
+      copy_resident_tiles(Qs, qimg, KD / 8, &bars[B_QFULL], lane);
+      copy_resident_tiles(Qs + TQ * KD * 2, qimg + 2 * KBUF, KD / 8, &bars[B_QFULL], lane);
+    }
     if (lane == 0) {
       const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * KBUF;
       for (int j = 0; j < T_tiles; ++j) {
         const int buf = j & 1, n0 = j * TK;
         if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_SFULL + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
         if (failed) break;
-#ifdef POPE_DBG_NO_KLOAD
-        mbar_arrive(&bars[B_KFULL + buf]);
-#else
         mbar_expect_tx(&bars[B_KFULL + buf], KBUF);
         bulk_load(Ks + buf * KBUF, kimg + (int64_t)j * KBUF, KBUF, &bars[B_KFULL + buf]);
-#endif
         if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
         if (failed) break;
-#ifdef POPE_DBG_NO_VLOAD
-        mbar_arrive(&bars[B_VFULL + buf]);
-#else
         mbar_expect_tx(&bars[B_VFULL + buf], VBUF);
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) tma_load_4d(Vs + buf * VBUF + c * CS, &tmap_v, &bars[B_VFULL + buf], c * 8, n0, hk, b);
-#endif
       }
     }
     __syncwarp();
@@ -244,15 +219,15 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
         for (int t = 0; t < 2; ++t) {
           if (jt >= (t == 0 ? T0 : T1)) continue;
           const uint32_t d = tmem + (buf * 2 + t) * 64;
-          uint64_t ad = smem_desc(qs_addr + t * (TQ * KD * 2), TQ * 16, 128);
-          uint64_t bd = smem_desc(ks_addr + buf * KBUF, CS, 128);
-#ifndef POPE_DBG_NO_QK
-          mma_ss(d, ad, bd, idesc_s, 0u);
+          const uint64_t ad = smem_desc(qs_addr + t * (TQ * KD * 2), TQ * 16, 128);
+          const uint64_t bd = smem_desc(ks_addr + buf * KBUF, CS, 128);
+          uint32_t alo = desc_lo(ad), blo = desc_lo(bd);
+          mma_ss_lh(d, alo, desc_hi(ad), blo, desc_hi(bd), idesc_s, 0u);
+#pragma unroll 4
           for (int ks = 1; ks < KSTEPS; ++ks) {
-            ad += (2 * TQ * 16) >> 4, bd += (2 * CS) >> 4;
-            mma_ss(d, ad, bd, idesc_s, 1u);
+            alo += (2 * TQ * 16) >> 4, blo += (2 * CS) >> 4;
+            mma_ss_lh(d, alo, desc_hi(ad), blo, desc_hi(bd), idesc_s, 1u);
           }
-#endif
         }
         mma_commit(&bars[B_SFULL + buf]);
       };
@@ -276,14 +251,10 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
           fence_after_sync();
           const uint32_t d = tmem + 256 + t * 128;
           const uint32_t a = tmem + (buf * 2 + t) * 64;
-          uint64_t bd = smem_desc(vs_addr + buf * VBUF, 128, CS);
-#ifndef POPE_DBG_NO_PV
+          const uint64_t bd = smem_desc(vs_addr + buf * VBUF, 128, CS);
 #pragma unroll
-          for (int ks = 0; ks < TK / 16; ++ks) {
-            mma_ts(d, a + ks * 8, bd, idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-            bd += (2 * 128) >> 4;
-          }
-#endif
+          for (int ks = 0; ks < TK / 16; ++ks)
+            mma_ts_lh(d, a + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
         }
         mma_commit(&bars[B_PVDONE + buf]);
       }
@@ -291,18 +262,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
     __syncwarp();
   } else {
     // =============================== softmax ==================================================
-    const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
-    const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
     const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
-    load_bias_trig(biasr, p.r, -1.f, bias_cb, bias_sb, tid);
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    const T* qtab = static_cast<const T*>(p.table);
-    stage_xform<D, TQ, T, true>(qbase, p.sq.n, i0, p.Nq, qtab, p.Nk, qoff, p.r, bias_cb, bias_sb, Qs, tid);
-    stage_xform<D, TQ, T, true>(qbase, p.sq.n, i0 + TQ, p.Nq, qtab, p.Nk, qoff, p.r, bias_cb, bias_sb,
-                                Qs + TQ * KD * 2, tid);
-    fence_async_smem();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&bars[B_QFULL]);
 
     const int tile = warp >> 2;
     const int row = i0 + tid;
@@ -328,9 +288,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
       if (!failed) failed = !mbar_wait(&bars[B_SFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
       fence_after_sync();
       const uint32_t s_addr = tmem + lane_base + (buf * 2 + tile) * 64;
-#ifdef POPE_DBG_NO_SOFTMAX
-      if (p.Nq > 0) { __syncwarp(); if (lane == 0) mbar_arrive(&bars[B_PFULL + buf * 2 + tile]); continue; }
-#endif
       uint32_t s0[32], s1[32];
       tmem_ld32(s_addr, s0);
       tmem_ld32(s_addr + 32, s1);
@@ -457,38 +414,41 @@ bool attn_fwd_tc_supported(const PopeAttnArgs& a) {
   return true;
 }
 
-// workspace: [16-bit cos / sin table, rounded up to 256 bytes][K' image tiles of all (batch, key head) units]
-static size_t fwd_table_bytes(const PopeShape& s) { return (trig_table_bytes(s.Nk, s.r) + 255) & ~(size_t)255; }
+// workspace: [fp32 cos / sin table][K' image tiles of all (batch, key head) units][Q' image tiles of all (batch, head) units]
+static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 size_t attn_fwd_tc_workspace(const PopeAttnArgs& a) {
   const PopeShape& s = a.shape;
-  return fwd_table_bytes(s) + image_bytes(s.B * s.Hk, s.Nk, s.d + s.r);
+  return trig_table_f32_bytes(s.Nk, s.r) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) + image_bytes(s.B * s.H, s.Nq, s.d + s.r);
 }
 
 template <int D, typename T>
 static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
+  const int KD = s.d + s.r;
+  const bool bf16 = s.dtype == POPE_BF16;
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  float* ctab = reinterpret_cast<float*>(ws);
+  float* stab = ctab + (size_t)s.Nk * s.r;
+  uint8_t* kimg = ws + trig_table_f32_bytes(s.Nk, s.r);
+  uint8_t* qimg = kimg + up256(image_bytes(s.B * s.Hk, s.Nk, KD));
   TcFwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
   p.scale_log2 = a.softmax_scale * LOG2E;
   p.q = a.q, p.k = a.k, p.v = a.v, p.o = a.out, p.lse = a.lse;
   p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.so = a.so;
   p.freqs = a.embed.freqs, p.sfn = a.embed.sf.n, p.bias = a.embed.bias, p.bias_sh = a.embed.bias_stride_h;
-  p.table = a.workspace;
-  p.kimg = static_cast<const uint8_t*>(a.workspace) + fwd_table_bytes(s);
+  p.qimg = qimg, p.kimg = kimg;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
-  const bool bf16 = s.dtype == POPE_BF16;
   cudaError_t e;
-  if (s.r > 0) {
-    e = launch_trig_table(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, a.workspace, bf16, st);
-    if (e != cudaSuccess) return e;
-  }
-  e = launch_expand_images(a.k, a.sk, s.B, s.Hk, s.Nk, s.d, s.r, bf16, a.workspace, s.Nk, 0, const_cast<uint8_t*>(p.kimg), st);
-  if (e != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_table_f32(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, ctab, stab, st)) != cudaSuccess) return e;
+  ExpandJobs jobs;
+  jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg);
+  jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg);
+  if ((e = launch_expand_images(jobs, 2, s.d, bf16, ctab, stab, st)) != cudaSuccess) return e;
   CUtensorMap tmap_v;
   if (!make_chunk_tmap(&tmap_v, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, TK)) return cudaErrorNotSupported;
-  const int KD = s.d + s.r;
-  size_t smem = (size_t)2 * TQ * KD * 2 + 2 * (size_t)TK * KD * 2 + 2 * (size_t)TK * D * 2 + (B_COUNT + 1) * 8 + 16 + 2 * 128 * 4;
+  size_t smem = (size_t)2 * TQ * KD * 2 + 2 * (size_t)TK * KD * 2 + 2 * (size_t)TK * D * 2 + (B_COUNT + 1) * 8 + 16;
   // every CTA allocates all 512 TMEM columns: ask for more than half of the SM's shared memory so
   // that two CTAs are never co-resident
   if (smem < 120 * 1024) smem = 120 * 1024;

@@ -9,73 +9,119 @@
 //     image[unit][tile][chunk c = 0 .. (d+r)/8)[row 0..64)[8 features]      (16 bytes per innermost group)
 //
 // so that a tile reaches shared memory as one contiguous bulk copy, and a 128-row resident operand as
-// (d+r)/8 copies of 1 KB per 64 rows.  Rows past the end of the operand are zero.  The per-head phase
-// bias is NOT part of an image: the kernels fold it into whichever operand they keep resident.
+// (d+r)/8 copies of 1 KB per 64 rows.  Rows past the end of the operand are zero, and every unit is padded to a
+// multiple of 256 rows.  The per-head phase offset (the learned bias of the keys, PoPE_pytorch/pope.py:75-79)
+// is folded into the key images; query images carry the bare table phase.
+#include <algorithm>
+
 #include "kernels.h"
 #include "tc_common.cuh"
 
 namespace pope {
 
-// grid (tiles, units), 256 threads; dynamic shared memory (d+r)/8 * CS64 bytes
-template <typename T>
-__global__ void __launch_bounds__(256) expand_image_kernel(const T* __restrict__ x, Strides sx, int heads, int rows, int d,
-                                                            int r, const T* __restrict__ tab, int tab_n, int pos0,
-                                                            uint8_t* __restrict__ img) {
+// grid (tiles, units, jobs), 256 threads; dynamic shared memory (d+r)/8 * CS64 bytes + 2 r floats.  One launch
+// builds the images of up to four operands (blockIdx.z picks the job); CTAs outside a job's tile / unit range leave.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) expand_image_kernel(ExpandJobs jobs, const float* __restrict__ ctab,
+                                                            const float* __restrict__ stab) {
   extern __shared__ __align__(16) uint8_t stage[];
+  const ExpandJob& jb = jobs.job[blockIdx.z];
   const int tid = threadIdx.x, tile = blockIdx.x, u = blockIdx.y;
-  const int DC = d >> 3, RC = r >> 3, KC = DC + RC;
-  const T* base = x + (int64_t)(u / heads) * sx.b + (int64_t)(u % heads) * sx.h;
-  const T* tab_s = tab + (int64_t)tab_n * r;
+  const int tiles = (int)image_tiles(jb.rows);
+  if (tile >= tiles || u >= jb.units) return;
+  const int r = jb.r, rows = jb.rows;
+  constexpr int DC = D >> 3;
+  const int RC = r >> 3, KC = DC + RC;
+  float* bias_c = reinterpret_cast<float*>(stage + KC * CS64);   // cos / sin of this head's phase offset
+  float* bias_s = bias_c + r;
+  const Strides sx(jb.sx);
+  const T* base = static_cast<const T*>(jb.x) + (int64_t)(u / jb.heads) * sx.b + (int64_t)(u % jb.heads) * sx.h;
+  const float* bias = jb.bias;
+  if (bias) {
+    for (int c = tid; c < r; c += 256) sincosf(bias[(int64_t)(u % jb.heads) * jb.bias_sh + c], &bias_s[c], &bias_c[c]);
+    __syncthreads();
+  }
   // phase 1: 16-byte groups in row-major order (a warp reads 512 contiguous bytes of a row pair); the
-  // padded chunk stride keeps the shared-memory stores of a warp on distinct banks
-  for (int f = tid; f < IMAGE_ROWS * DC; f += 256) {
-    const int row = f / DC, c = f - row * DC, j = tile * IMAGE_ROWS + row;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (j < rows) raw = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)j * sx.n + c * 8));
+  // padded chunk stride keeps the shared-memory stores of a warp on distinct banks.  All raw rows of the
+  // thread are requested before the first one is used.
+  constexpr int NIT = IMAGE_ROWS * DC / 256;
+  uint4 raw[NIT];
+#pragma unroll
+  for (int it = 0; it < NIT; ++it) {
+    const int f = tid + it * 256, row = f / DC, c = f - row * DC, j = tile * IMAGE_ROWS + row;
+    raw[it] = make_uint4(0, 0, 0, 0);
+    if (j < rows) raw[it] = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)j * sx.n + c * 8));
+  }
+#pragma unroll
+  for (int it = 0; it < NIT; ++it) {
+    const int f = tid + it * 256, row = f / DC, c = f - row * DC, j = tile * IMAGE_ROWS + row;
     if (c < RC) {
       uint4 oc = make_uint4(0, 0, 0, 0), os = oc;
       if (j < rows) {
-        const uint4 tc = __ldg(reinterpret_cast<const uint4*>(tab + (int64_t)(pos0 + j) * r + c * 8));
-        const uint4 ts = __ldg(reinterpret_cast<const uint4*>(tab_s + (int64_t)(pos0 + j) * r + c * 8));
-        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w}, cw[4] = {tc.x, tc.y, tc.z, tc.w}, sw[4] = {ts.x, ts.y, ts.z, ts.w};
+        const float4* cp = reinterpret_cast<const float4*>(ctab + (int64_t)(jb.pos0 + j) * r + c * 8);
+        const float4* sp = reinterpret_cast<const float4*>(stab + (int64_t)(jb.pos0 + j) * r + c * 8);
+        const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+        float co[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        float si[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        if (bias) {   // cos(f + b), sin(f + b)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float cb = bias_c[c * 8 + e], sb = bias_s[c * 8 + e], cf = co[e], sf = si[e];
+            co[e] = cf * cb - sf * sb;
+            si[e] = sf * cb + cf * sb;
+          }
+        }
+        const uint32_t rw[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
         uint32_t o1[4], o2[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float2 xv = unpack2<T>(rw[e]), co = unpack2<T>(cw[e]), si = unpack2<T>(sw[e]);
+          const float2 xv = unpack2<T>(rw[e]);
           const float a0 = softplus_fast(xv.x), a1 = softplus_fast(xv.y);
-          o1[e] = pack2<T>(a0 * co.x, a1 * co.y);
-          o2[e] = pack2<T>(a0 * si.x, a1 * si.y);
+          o1[e] = pack2<T>(a0 * co[2 * e], a1 * co[2 * e + 1]);
+          o2[e] = pack2<T>(a0 * si[2 * e], a1 * si[2 * e + 1]);
         }
         oc = make_uint4(o1[0], o1[1], o1[2], o1[3]), os = make_uint4(o2[0], o2[1], o2[2], o2[3]);
       }
       *reinterpret_cast<uint4*>(stage + c * CS64 + row * 16) = oc;
       *reinterpret_cast<uint4*>(stage + (DC + c) * CS64 + row * 16) = os;
     } else {
-      *reinterpret_cast<uint4*>(stage + c * CS64 + row * 16) = raw;
+      *reinterpret_cast<uint4*>(stage + c * CS64 + row * 16) = raw[it];
     }
   }
   __syncthreads();
   // phase 2: the image leaves in its own byte order, 16 bytes per thread, fully coalesced
-  uint4* out = reinterpret_cast<uint4*>(img + ((int64_t)u * gridDim.x + tile) * ((int64_t)IMAGE_ROWS * KC * 16));
+  uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(jb.img) + ((int64_t)u * tiles + tile) * ((int64_t)IMAGE_ROWS * KC * 16));
   for (int g = tid; g < IMAGE_ROWS * KC; g += 256) {
     const int c = g / IMAGE_ROWS, row = g - c * IMAGE_ROWS;
     out[g] = *reinterpret_cast<const uint4*>(stage + c * CS64 + row * 16);
   }
 }
 
-cudaError_t launch_expand_images(const void* x, const PopeStride3& sx, int batch, int heads, int rows, int d, int r,
-                                 bool is_bf16, const void* table, int tab_n, int pos0, void* img, cudaStream_t st) {
-  const dim3 grid((unsigned)image_tiles(rows), (unsigned)(batch * heads));
-  const size_t smem = (size_t)((d + r) / 8) * CS64;
-  if (is_bf16)
-    expand_image_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16*>(x), Strides(sx), heads, rows,
-                                                                 d, r, static_cast<const __nv_bfloat16*>(table), tab_n, pos0,
-                                                                 static_cast<uint8_t*>(img));
-  else
-    expand_image_kernel<__half><<<grid, 256, smem, st>>>(static_cast<const __half*>(x), Strides(sx), heads, rows, d, r,
-                                                          static_cast<const __half*>(table), tab_n, pos0,
-                                                          static_cast<uint8_t*>(img));
+template <typename T>
+static cudaError_t launch_expand_t(const ExpandJobs& jobs, int njobs, int d, const float* ctab, const float* stab,
+                                   cudaStream_t st) {
+  int tiles = 0, units = 0, rmax = 0;
+  for (int i = 0; i < njobs; ++i) {
+    tiles = std::max(tiles, (int)image_tiles(jobs.job[i].rows));
+    units = std::max(units, jobs.job[i].units);
+    rmax = std::max(rmax, jobs.job[i].r);
+  }
+  const dim3 grid((unsigned)tiles, (unsigned)units, (unsigned)njobs);
+  const size_t smem = (size_t)((d + rmax) / 8) * CS64 + 2 * (size_t)rmax * sizeof(float);
+  switch (d) {
+    case 64: expand_image_kernel<T, 64><<<grid, 256, smem, st>>>(jobs, ctab, stab); break;
+    case 96: expand_image_kernel<T, 96><<<grid, 256, smem, st>>>(jobs, ctab, stab); break;
+    case 128: expand_image_kernel<T, 128><<<grid, 256, smem, st>>>(jobs, ctab, stab); break;
+    default: return cudaErrorInvalidValue;
+  }
   return cudaGetLastError();
+}
+
+cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const float* ctab, const float* stab,
+                                 cudaStream_t st) {
+  if (njobs < 1 || njobs > 4) return cudaErrorInvalidValue;
+  return is_bf16 ? launch_expand_t<__nv_bfloat16>(jobs, njobs, d, ctab, stab, st)
+                 : launch_expand_t<__half>(jobs, njobs, d, ctab, stab, st);
 }
 
 }  // namespace pope

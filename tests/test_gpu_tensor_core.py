@@ -104,7 +104,9 @@ def test_backward_tc_matches_exact_family(b, h, hk, n, d, r, causal, masked, dty
     assert _native.device_status() == 0
     for name, a1, a0 in (("dq", dq1, dq0), ("dk", dk1, dk0), ("dv", dv1, dv0)):
         err = float((a1.float() - a0.float()).abs().max())
-        assert err <= max(2e-2, 2.0 ** -8 * float(a0.float().abs().max())), f"{name}: {err}"
+        # both sides are stored in 16 bits: two roundings of nearly equal values may land one ulp apart,
+        # which is up to 2^-7 of the magnitude in bf16
+        assert err <= max(2e-2, 2.0 ** -7 * float(a0.float().abs().max())), f"{name}: {err}"
     if r > 0:
         for name, a1, a0 in (("dbias", db1, db0), ("dfreqs", df1, df0)):
             rel = float((a1 - a0).abs().max() / a0.abs().max().clamp_min(1.0))
