@@ -14,6 +14,8 @@
 // operand is resident.  A streamed tile in shared memory serves two MMAs: as the K-major B
 // operand of the score product and, re-described as MN-major, as the B operand of the gradient
 // product -- the 8x16-byte core-matrix layout is symmetric under that exchange.
+#include <type_traits>
+
 #include "kernels.h"
 #include "tc_common.cuh"
 
@@ -254,18 +256,23 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     warp_arrive(&bars[BB_CONSUMED], lane);
     PH(1);
     uint32_t pk[16];
+    // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
+    auto elementwise = [&](auto masked) {
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse_use));
-      float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse_use));
-      if (!all_vis) {
-        p0 = ((vis >> (2 * e)) & 1u) ? p0 : 0.f;
-        p1 = ((vis >> (2 * e + 1)) & 1u) ? p1 : 0.f;
+      for (int e = 0; e < 16; ++e) {
+        float p0 = ex2_approx(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2, -lse_use));
+        float p1 = ex2_approx(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2, -lse_use));
+        if (decltype(masked)::value) {
+          p0 = ((vis >> (2 * e)) & 1u) ? p0 : 0.f;
+          p1 = ((vis >> (2 * e + 1)) & 1u) ? p1 : 0.f;
+        }
+        const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
+        const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
+        pk[e] = pack2<T>(d0, d1);
       }
-      const float d0 = p0 * (__uint_as_float(dv[2 * e]) - dlt) * p.scale;
-      const float d1 = p1 * (__uint_as_float(dv[2 * e + 1]) - dlt) * p.scale;
-      pk[e] = pack2<T>(d0, d1);
-    }
+    };
+    if (all_vis) elementwise(std::false_type());
+    else elementwise(std::true_type());
     PH(2);
     // the dS columns were read by the accumulation step of tile j-1
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (j - 1) % DQ_NST], ((j - 1) / DQ_NST) & 1, WAIT_LIMIT);

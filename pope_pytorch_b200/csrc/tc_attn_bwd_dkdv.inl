@@ -177,25 +177,30 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     warp_arrive(&bars[BB_CONSUMED], lane);
     PH(1);
     uint32_t pw[16], dw[16];   // P^T and dS^T of this thread's 32 query columns, packed in pairs
+    // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
+    auto elementwise = [&](auto masked) {
 #pragma unroll
-    for (int c4 = 0; c4 < 8; ++c4) {
-      const float4 l4 = *reinterpret_cast<const float4*>(st + c4 * 4), d4 = *reinterpret_cast<const float4*>(st + 64 + c4 * 4);
-      const float l2v[4] = {l4.x, l4.y, l4.z, l4.w}, dlv[4] = {d4.x, d4.y, d4.z, d4.w};
+      for (int c4 = 0; c4 < 8; ++c4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(st + c4 * 4), d4 = *reinterpret_cast<const float4*>(st + 64 + c4 * 4);
+        const float l2v[4] = {l4.x, l4.y, l4.z, l4.w}, dlv[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float pv[2], dsv[2];
+        for (int e = 0; e < 2; ++e) {
+          float pv[2], dsv[2];
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const int cl = c4 * 4 + e * 2 + t;   // query column within the thread's half
-          float pr = ex2_approx(fmaf(__uint_as_float(sv[cl]), p.scale_log2, -l2v[e * 2 + t]));
-          if (!interior) pr = (key_ok && (!p.causal || gj <= gi_lo + cl)) ? pr : 0.f;
-          pv[t] = pr;
-          dsv[t] = pr * (__uint_as_float(dv[cl]) - dlv[e * 2 + t]) * p.scale;
+          for (int t = 0; t < 2; ++t) {
+            const int cl = c4 * 4 + e * 2 + t;   // query column within the thread's half
+            float pr = ex2_approx(fmaf(__uint_as_float(sv[cl]), p.scale_log2, -l2v[e * 2 + t]));
+            if (decltype(masked)::value) pr = (key_ok && (!p.causal || gj <= gi_lo + cl)) ? pr : 0.f;
+            pv[t] = pr;
+            dsv[t] = pr * (__uint_as_float(dv[cl]) - dlv[e * 2 + t]) * p.scale;
+          }
+          pw[c4 * 2 + e] = pack2<T>(pv[0], pv[1]);
+          dw[c4 * 2 + e] = pack2<T>(dsv[0], dsv[1]);
         }
-        pw[c4 * 2 + e] = pack2<T>(pv[0], pv[1]);
-        dw[c4 * 2 + e] = pack2<T>(dsv[0], dsv[1]);
       }
-    }
+    };
+    if (interior) elementwise(std::false_type());
+    else elementwise(std::true_type());
     PH(2);
     // the P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);

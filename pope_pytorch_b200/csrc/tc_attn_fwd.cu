@@ -21,6 +21,7 @@
 // bottom-right positions, mask True = keep, zero output and -inf LSE for empty rows).
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "kernels.h"
 #include "tc_common.cuh"
@@ -129,11 +130,12 @@ constexpr int FWD_THREADS = 32 * (FWD_MMA_WARP + 1);
 enum {
   B_KFULL = 0,   // [2] K' image tile landed (transaction bytes)
   B_VFULL = 2,   // [2] V tile landed (transaction bytes)
-  B_SFULL = 4,   // [2] scores of both row tiles written to TMEM (tcgen05.commit)
+  B_KFREE = 4,   // [2] both score products of a key tile have completed: its K' buffer may be refilled
   B_PVDONE = 6,  // [2] O += P V of both row tiles done (tcgen05.commit)
   B_PFULL = 8,   // [buf][row tile] probabilities written to TMEM (4 softmax warps)
   B_QFULL = 12,  // the resident Q' tiles are in shared memory
-  B_COUNT = 13
+  B_SFULL = 13,  // [buf][row tile] scores of one row tile written to TMEM (tcgen05.commit)
+  B_COUNT = 17
 };
 
 template <int D, typename T>
@@ -168,9 +170,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[B_KFULL + i], 1), mbar_init(&bars[B_VFULL + i], 1);
-      mbar_init(&bars[B_SFULL + i], 1), mbar_init(&bars[B_PVDONE + i], 1);
+      mbar_init(&bars[B_KFREE + i], 1), mbar_init(&bars[B_PVDONE + i], 1);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[B_PFULL + i], 4);
+    for (int i = 0; i < 4; ++i) mbar_init(&bars[B_PFULL + i], 4), mbar_init(&bars[B_SFULL + i], 1);
     mbar_init(&bars[B_QFULL], 1);
     mbar_init_fence();
   }
@@ -196,7 +198,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
       const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * KBUF;
       for (int j = 0; j < T_tiles; ++j) {
         const int buf = j & 1, n0 = j * TK;
-        if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_SFULL + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_KFREE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
         if (failed) break;
         mbar_expect_tx(&bars[B_KFULL + buf], KBUF);
         bulk_load(Ks + buf * KBUF, kimg + (int64_t)j * KBUF, KBUF, &bars[B_KFULL + buf]);
@@ -228,26 +230,32 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
             alo += (2 * TQ * 16) >> 4, blo += (2 * CS) >> 4;
             mma_ss_lh(d, alo, desc_hi(ad), blo, desc_hi(bd), idesc_s, 1u);
           }
+          mma_commit(&bars[B_SFULL + buf * 2 + t]);   // this row tile's softmax may start
         }
-        mma_commit(&bars[B_SFULL + buf]);
+        mma_commit(&bars[B_KFREE + buf]);
       };
       if (!mbar_wait(&bars[B_QFULL], 0, WAIT_LIMIT)) failed = true;
       if (!mbar_wait(&bars[B_KFULL], 0, WAIT_LIMIT)) failed = true;
       fence_after_sync();
       issue_s(0);
+      PH_DECL;
       for (int j = 0; j < T_tiles; ++j) {
         const int buf = j & 1;
         if (j + 1 < T_tiles) {
           if (!failed) failed = !mbar_wait(&bars[B_KFULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
-          // score buffer 1-buf still holds P(j-1) until PV(j-1) has read it
-          if (j >= 1 && !failed) failed = !mbar_wait(&bars[B_PVDONE + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+          PH(0);
+          // Score buffer 1-buf still holds P(j-1), which PV(j-1) reads.  No wait is needed for that: the MMAs of
+          // one thread execute in issue order, and PV(j-1) was issued before these score products.
           fence_after_sync();
           issue_s(j + 1);
+          PH(1);
         }
         if (!failed) failed = !mbar_wait(&bars[B_VFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
+        PH(2);
         for (int t = 0; t < 2; ++t) {
           if (j >= (t == 0 ? T0 : T1)) continue;
           if (!failed) failed = !mbar_wait(&bars[B_PFULL + buf * 2 + t], (j >> 1) & 1, WAIT_LIMIT);
+          PH(3);
           fence_after_sync();
           const uint32_t d = tmem + 256 + t * 128;
           const uint32_t a = tmem + (buf * 2 + t) * 64;
@@ -255,9 +263,11 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
 #pragma unroll
           for (int ks = 0; ks < TK / 16; ++ks)
             mma_ts_lh(d, a + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          PH(4);
         }
         mma_commit(&bars[B_PVDONE + buf]);
       }
+      PH_PRINT("fwd mma [wait kfull, issue S, wait vfull, wait pfull, issue PV]", T_tiles);
     }
     __syncwarp();
   } else {
@@ -269,6 +279,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
     const int T_mine = tile == 0 ? T0 : T1;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     float m_run = -CUDART_INF_F, l_run = 0.f;
+    PH_DECL;
 
     for (int j = 0; j < T_mine; ++j) {
       const int buf = j & 1, n0 = j * TK;
@@ -285,13 +296,16 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
         vis &= lim >= 63 ? ~0ull : (lim < 0 ? 0ull : ((2ull << lim) - 1ull));
       }
       const bool all_vis = __all_sync(0xffffffffu, vis == ~0ull);
-      if (!failed) failed = !mbar_wait(&bars[B_SFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
+      PH(0);
+      if (!failed) failed = !mbar_wait(&bars[B_SFULL + buf * 2 + tile], (j >> 1) & 1, WAIT_LIMIT);
       fence_after_sync();
+      PH(1);
       const uint32_t s_addr = tmem + lane_base + (buf * 2 + tile) * 64;
       uint32_t s0[32], s1[32];
       tmem_ld32(s_addr, s0);
       tmem_ld32(s_addr + 32, s1);
       tmem_ld_wait();
+      PH(2);
       // row maximum (four independent chains)
       float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (all_vis) {
@@ -335,33 +349,42 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
         }
         tmem_st_wait();
       }
+      PH(3);
       // P = 2^(s*c - m), written over the scores (16 packed columns per 32 scores)
       const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
+      // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
+      auto exponentials = [&](auto masked) {
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const uint32_t vh = (uint32_t)(vis >> (32 * hh));
+        for (int hh = 0; hh < 2; ++hh) {
+          const uint32_t vh = (uint32_t)(vis >> (32 * hh));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint32_t x0 = hh ? s1[2 * i] : s0[2 * i], x1 = hh ? s1[2 * i + 1] : s0[2 * i + 1];
-          float p0 = ex2_approx(fmaf(__uint_as_float(x0), p.scale_log2, -m_use));
-          float p1 = ex2_approx(fmaf(__uint_as_float(x1), p.scale_log2, -m_use));
-          if (!all_vis) {
-            p0 = ((vh >> (2 * i)) & 1u) ? p0 : 0.f;
-            p1 = ((vh >> (2 * i + 1)) & 1u) ? p1 : 0.f;
+          for (int i = 0; i < 16; ++i) {
+            const uint32_t x0 = hh ? s1[2 * i] : s0[2 * i], x1 = hh ? s1[2 * i + 1] : s0[2 * i + 1];
+            float p0 = ex2_approx(fmaf(__uint_as_float(x0), p.scale_log2, -m_use));
+            float p1 = ex2_approx(fmaf(__uint_as_float(x1), p.scale_log2, -m_use));
+            if (decltype(masked)::value) {
+              p0 = ((vh >> (2 * i)) & 1u) ? p0 : 0.f;
+              p1 = ((vh >> (2 * i + 1)) & 1u) ? p1 : 0.f;
+            }
+            ls4[i & 3] += p0 + p1;
+            pk[hh * 16 + i] = pack2<T>(p0, p1);
           }
-          ls4[i & 3] += p0 + p1;
-          pk[hh * 16 + i] = pack2<T>(p0, p1);
         }
-      }
+      };
+      if (all_vis) exponentials(std::false_type());
+      else exponentials(std::true_type());
       l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       tmem_st32(s_addr, pk);
       tmem_st_wait();
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[B_PFULL + buf * 2 + tile]);
+      PH(4);
     }
+    if (tid == 128 && T_mine > 0) PH_PRINT("fwd softmax tile1 [vis, wait S, ld, max+rescale, exp+st]", T_mine);
+    PH(5);
 
     // ---- epilogue: O / l, LSE ---------------------------------------------------------------------
     if (T_mine > 0) {
@@ -391,6 +414,8 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
       if (row < p.Nq)
         p.lse[(int64_t)u * p.Nq + row] = l_run > 0.f ? m_run * LN2 + logf(l_run) : -CUDART_INF_F;
     }
+    PH(6);
+    if (tid == 128 && T_mine > 0) PH_PRINT("fwd softmax tile1 [.., 5: print, 6: epilogue total/tiles]", T_mine);
   }
   if (failed) atomicOr(&g_tc_status, 1u);
   fence_before_sync();
