@@ -45,11 +45,14 @@ constexpr int BQ = 128;  // resident rows per CTA
 constexpr int BT = 64;   // streamed rows per step (= IMAGE_ROWS)
 static_assert(BT == IMAGE_ROWS, "a streamed tile is one image tile");
 
-// Warp roles of both backward kernels (10 warps, 320 threads)
+// Warp roles of both backward kernels (11 warps, 352 threads).  Two issuing warps: a single thread spends ~55
+// clocks per MMA instruction, so the accumulation MMAs of tile j are issued by a second thread while the first
+// is still issuing the score products of tile j+1 (the tensor pipe is idle about half of that time).
 constexpr int BWD_E_WARPS = 8;     // warps 0-7 : elementwise work (P, dS) and the epilogue
 constexpr int BWD_L_WARP = 8;      // warp 8    : issues the bulk copies of the resident and the streamed tiles
-constexpr int BWD_M_WARP = 9;      // warp 9    : one lane issues every MMA; owns the TMEM allocation
-constexpr int BWD_THREADS = 32 * (BWD_M_WARP + 1);
+constexpr int BWD_M_WARP = 9;      // warp 9    : one lane issues the score products; owns the TMEM allocation
+constexpr int BWD_A_WARP = 10;     // warp 10   : one lane issues the accumulation products
+constexpr int BWD_THREADS = 32 * (BWD_A_WARP + 1);
 constexpr int BCS = BT * 16;       // bytes of one 16-byte chunk column of a streamed tile
 
 // mbarrier slots shared by both backward kernels; a streamed tile j lives in stage j % NST
@@ -142,7 +145,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     // =============================== MMA issue ===================================================
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
-      const uint32_t idesc_q = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
       const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
       const uint64_t qd = smem_desc(qs_addr, BQ * 16, 128);
       auto issue_scores = [&](int jt) {   // S = Q' K'^T (both from shared memory), dP = dO V^T (dO from TMEM)
@@ -161,34 +163,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         mma_commit(&bars[BB_SCORES]);
       };
       if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
-      if (!mbar_wait(&bars[BB_FULL], 0, WAIT_LIMIT)) failed = true;
-      fence_after_sync();
-      issue_scores(0);
-      PH_DECL;
-      for (int j = 0; j < T_tiles; ++j) {
-        const int st = j % DQ_NST;
-        if (j + 1 < T_tiles) {
-          if (!failed) failed = !mbar_wait(&bars[BB_FULL + (j + 1) % DQ_NST], ((j + 1) / DQ_NST) & 1, WAIT_LIMIT);
-          PH(0);
-          if (!failed) failed = !mbar_wait(&bars[BB_CONSUMED], j & 1, WAIT_LIMIT);
-          PH(1);
-          fence_after_sync();
-          issue_scores(j + 1);
-          PH(2);
-        }
-        if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
-        PH(3);
+      for (int j = 0; j < T_tiles && !failed; ++j) {
+        failed = !mbar_wait(&bars[BB_FULL + j % DQ_NST], (j / DQ_NST) & 1, WAIT_LIMIT);
+        // the elementwise warps have copied the previous tile's scores out of TMEM
+        if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
         fence_after_sync();
-        // dQ' += dS K'  (dS from TMEM; the K' tile re-described as an MN-major B operand)
+        issue_scores(j);
+      }
+      if (failed) atomicOr(p.status, 1u);
+    }
+    __syncwarp();
+  } else if (warp == BWD_A_WARP) {
+    // =============================== MMA issue: dQ' += dS K' ====================================
+    if (lane == 0) {
+      const uint32_t idesc_q = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
+      const uint32_t ks_addr = smem_u32(Ks);
+      for (int j = 0; j < T_tiles && !failed; ++j) {
+        const int st = j % DQ_NST;
+        failed = !mbar_wait(&bars[BB_FULL + st], (j / DQ_NST) & 1, WAIT_LIMIT);
+        if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
+        fence_after_sync();
+        // dS from TMEM; the K' tile re-described as an MN-major B operand
         const uint64_t bd = smem_desc(ks_addr + st * KBUF, 128, BCS);
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks)
           mma_ts_lh(tmem + TC_DQ, tmem + TC_DS + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_q,
                     (j > 0 || ks > 0) ? 1u : 0u);
-        mma_commit(&bars[BB_ACC + st]);
-        PH(4);
+        mma_commit(&bars[BB_ACC + st]);   // every score product of this tile finished before its dS existed
       }
-      PH_PRINT("dq mma  [wait full, wait consumed, issue scores, wait grad, issue acc]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -228,8 +230,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   const float lse2 = gi < p.Nq ? p.lse[(int64_t)u * p.Nq + gi] * LOG2E : -CUDART_INF_F;
   const float lse_use = lse2 == -CUDART_INF_F ? 0.f : lse2;
   const float dlt = gi < p.Nq ? p.delta[(int64_t)u * p.Nq + gi] : 0.f;
-
-  PH_DECL;
   for (int j = 0; j < T_tiles; ++j) {
     const int n0 = tile_start(j);
     // key visibility of this thread's 32-key half (key-padding mask, ragged end): the same for every row
@@ -246,7 +246,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     const bool all_vis = __all_sync(0xffffffffu, vis == 0xffffffffu);   // interior tile: no masking work
     if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
     fence_after_sync();
-    PH(0);
     uint32_t sv[32], dv[32];
     tmem_ld32(tmem + lane_base + TC_S + half * 32, sv);
     tmem_ld32(tmem + lane_base + TC_DP + half * 32, dv);
@@ -254,7 +253,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     // every score of this tile is in registers: the next score products may overwrite them
     fence_before_sync();
     warp_arrive(&bars[BB_CONSUMED], lane);
-    PH(1);
     uint32_t pk[16];
     // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
     auto elementwise = [&](auto masked) {
@@ -273,18 +271,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     };
     if (all_vis) elementwise(std::false_type());
     else elementwise(std::true_type());
-    PH(2);
     // the dS columns were read by the accumulation step of tile j-1
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (j - 1) % DQ_NST], ((j - 1) / DQ_NST) & 1, WAIT_LIMIT);
-    PH(3);
     tmem_st16(tmem + lane_base + TC_DS + half * 16, pk);
     tmem_st_wait();
     fence_before_sync();
     warp_arrive(&bars[BB_GRAD], lane);
-    PH(4);
   }
-  if (tid == 0) PH_PRINT("dq elem [wait scores, ld+arrive, math, wait acc, st+arrive]", T_tiles);
-  PH(5);
 
   // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
   if (!failed) failed = !mbar_wait(&bars[BB_ACC + (T_tiles - 1) % DQ_NST], ((T_tiles - 1) / DQ_NST) & 1, WAIT_LIMIT);
@@ -338,8 +331,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       }
     }
   }
-  PH(6);
-  if (tid == 0) PH_PRINT("dq elem [.. 5: print, 6: epilogue TOTAL clk / tiles]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier

@@ -19,7 +19,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.Hk, hk = u % p.Hk;
   const int j0 = blockIdx.x * BQ;
-  const int qoff = p.Nk - p.Nq;
   const int groups = p.H / p.Hk;
   const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
   const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
@@ -85,10 +84,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     // =============================== MMA issue ===================================================
     if (lane == 0 && T_tiles > 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
-      const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
-      const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
       const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
-      const uint32_t ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
       auto issue_scores = [&](int jt) {
         const int buf = jt & 1;
         const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128), qb = smem_desc(qb_addr + buf * KBUF, BCS, 128);
@@ -107,25 +103,29 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
         mma_commit(&bars[BB_SCORES]);
       };
       if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
-      if (!mbar_wait(&bars[BB_FULL], 0, WAIT_LIMIT)) failed = true;
-      fence_after_sync();
-      issue_scores(0);
-      PH_DECL;
-      for (int j = 0; j < T_tiles; ++j) {
-        const int buf = j & 1;
-        if (j + 1 < T_tiles) {
-          if (!failed) failed = !mbar_wait(&bars[BB_FULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
-          PH(0);
-          if (!failed) failed = !mbar_wait(&bars[BB_CONSUMED], j & 1, WAIT_LIMIT);
-          PH(1);
-          fence_after_sync();
-          issue_scores(j + 1);
-          PH(2);
-        }
-        if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
-        PH(3);
+      for (int j = 0; j < T_tiles && !failed; ++j) {
+        failed = !mbar_wait(&bars[BB_FULL + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
+        // the elementwise warps have copied the previous tile's scores out of TMEM
+        if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
         fence_after_sync();
-        const uint64_t pa = smem_desc(ps_addr, BQ * 16, 128), da = smem_desc(ds_addr, BQ * 16, 128);
+        issue_scores(j);
+      }
+      if (failed) atomicOr(p.status, 1u);
+    }
+    __syncwarp();
+  } else if (warp == BWD_A_WARP) {
+    // =============================== MMA issue: dK' += dS^T Q', dV += P^T dO ====================
+    if (lane == 0 && T_tiles > 0) {
+      const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
+      const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
+      const uint32_t qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb), ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
+      const uint64_t pa = smem_desc(ps_addr, BQ * 16, 128), da = smem_desc(ds_addr, BQ * 16, 128);
+      for (int j = 0; j < T_tiles && !failed; ++j) {
+        const int buf = j & 1;
+        failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);
+        if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
+        fence_after_sync();
+        // the streamed tiles re-described as MN-major B operands
         const uint64_t gd = smem_desc(gb_addr + buf * VBUF, 128, BCS), qd = smem_desc(qb_addr + buf * KBUF, 128, BCS);
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks) {
@@ -133,10 +133,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
           mma_ss_lh(tmem + 256, desc_lo(da) + astep, desc_hi(da), desc_lo(qd) + bstep, desc_hi(qd), idesc_k, acc);
           mma_ss_lh(tmem + 128, desc_lo(pa) + astep, desc_hi(pa), desc_lo(gd) + bstep, desc_hi(gd), idesc_v, acc);
         }
-        mma_commit(&bars[BB_ACC + buf]);
-        PH(4);
+        mma_commit(&bars[BB_ACC + buf]);   // every score product of this tile finished before its P^T / dS^T existed
       }
-      PH_PRINT("dkdv mma  [wait full, wait consumed, issue scores, wait grad, issue acc]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -155,14 +153,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const int gj = j0 + row;
   const bool key_ok = gj < p.Nk && (!maskb || maskb[(int64_t)gj * p.msn] != 0);
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  PH_DECL;
   for (int j = 0; j < T_tiles; ++j) {
     const int buf = j & 1;
     const int m0 = tile_start(j);
     if (!failed) failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the lse / delta read
     if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
     fence_after_sync();
-    PH(0);
     const float* st = rowstat + buf * 128 + half * 32;
     // interior tile for this warp: every key row valid and (causal) every key at or before every query column;
     // out-of-range queries and rows without any visible key carry lse = +inf, which makes P exactly 0
@@ -175,7 +171,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     // every score of this tile is in registers: the next score products may overwrite them
     fence_before_sync();
     warp_arrive(&bars[BB_CONSUMED], lane);
-    PH(1);
     uint32_t pw[16], dw[16];   // P^T and dS^T of this thread's 32 query columns, packed in pairs
     // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
     auto elementwise = [&](auto masked) {
@@ -201,10 +196,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     };
     if (interior) elementwise(std::false_type());
     else elementwise(std::true_type());
-    PH(2);
     // the P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
-    PH(3);
 #pragma unroll
     for (int c8 = 0; c8 < 4; ++c8) {
       const int chunk = half * 4 + c8;
@@ -213,10 +206,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     }
     fence_async_smem();
     warp_arrive(&bars[BB_GRAD], lane);
-    PH(4);
   }
-  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [wait scores, ld+arrive, math, wait acc, st+arrive]", T_tiles);
-  PH(5);
 
   // ---- epilogue ---------------------------------------------------------------------------------
   if (T_tiles > 0 && !failed)
@@ -311,8 +301,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     asm volatile("bar.sync 1, 256;" ::: "memory");
     for (int c = tid; c < p.r; c += 256) atomicAdd(p.dbias + hk * p.dbias_sh + c, red[c]);
   }
-  PH(6);
-  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [.. 5: print, 6: epilogue TOTAL clk / tiles]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier

@@ -120,11 +120,14 @@ constexpr int TQ = 128;   // rows per MMA tile
 constexpr int TK = 64;    // keys per step (= IMAGE_ROWS)
 static_assert(TK == IMAGE_ROWS, "a streamed K' tile is one image tile");
 
-// Warp roles of the forward kernel (10 warps, 320 threads)
+// Warp roles of the forward kernel (11 warps, 352 threads).  Two issuing warps: a single thread spends ~55 clocks
+// per MMA instruction, so O += P V of tile j is issued by a second thread while the first is still issuing the
+// score products of tile j+1.
 constexpr int FWD_SOFTMAX_WARPS = 8;               // warps 0-7 : one query row per thread (two 128-row tiles)
 constexpr int FWD_LOAD_WARP = FWD_SOFTMAX_WARPS;   // warp 8    : one lane issues every bulk / tensor copy
-constexpr int FWD_MMA_WARP = FWD_LOAD_WARP + 1;    // warp 9    : one lane issues every MMA; owns the TMEM allocation
-constexpr int FWD_THREADS = 32 * (FWD_MMA_WARP + 1);
+constexpr int FWD_MMA_WARP = FWD_LOAD_WARP + 1;    // warp 9    : one lane issues S = Q' K'^T; owns the TMEM allocation
+constexpr int FWD_PV_WARP = FWD_MMA_WARP + 1;      // warp 10   : one lane issues O += P V
+constexpr int FWD_THREADS = 32 * (FWD_PV_WARP + 1);
 
 // mbarrier slots
 enum {
@@ -214,8 +217,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
     // =============================== MMA issue ================================================
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, TQ, TK, false, false);
-      const uint32_t idesc_o = instr_desc(TcFmt<T>::fmt, TQ, D, false, true);
-      const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+      const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks);
       auto issue_s = [&](int jt) {   // S(jt) = Q'_t K'(jt)^T into score buffer jt & 1
         const int buf = jt & 1;
         for (int t = 0; t < 2; ++t) {
@@ -235,27 +237,26 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
         mma_commit(&bars[B_KFREE + buf]);
       };
       if (!mbar_wait(&bars[B_QFULL], 0, WAIT_LIMIT)) failed = true;
-      if (!mbar_wait(&bars[B_KFULL], 0, WAIT_LIMIT)) failed = true;
-      fence_after_sync();
-      issue_s(0);
-      PH_DECL;
-      for (int j = 0; j < T_tiles; ++j) {
+      for (int j = 0; j < T_tiles && !failed; ++j) {
+        failed = !mbar_wait(&bars[B_KFULL + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
+        // score buffer j & 1 still holds P(j-2) until PV(j-2) has read it
+        if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + (j & 1)], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        fence_after_sync();
+        issue_s(j);
+      }
+    }
+    __syncwarp();
+  } else if (warp == FWD_PV_WARP) {
+    // =============================== MMA issue: O += P V =======================================
+    if (lane == 0) {
+      const uint32_t idesc_o = instr_desc(TcFmt<T>::fmt, TQ, D, false, true);
+      const uint32_t vs_addr = smem_u32(Vs);
+      for (int j = 0; j < T_tiles && !failed; ++j) {
         const int buf = j & 1;
-        if (j + 1 < T_tiles) {
-          if (!failed) failed = !mbar_wait(&bars[B_KFULL + (1 - buf)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
-          PH(0);
-          // Score buffer 1-buf still holds P(j-1), which PV(j-1) reads.  No wait is needed for that: the MMAs of
-          // one thread execute in issue order, and PV(j-1) was issued before these score products.
-          fence_after_sync();
-          issue_s(j + 1);
-          PH(1);
-        }
-        if (!failed) failed = !mbar_wait(&bars[B_VFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
-        PH(2);
+        failed = !mbar_wait(&bars[B_VFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
         for (int t = 0; t < 2; ++t) {
           if (j >= (t == 0 ? T0 : T1)) continue;
           if (!failed) failed = !mbar_wait(&bars[B_PFULL + buf * 2 + t], (j >> 1) & 1, WAIT_LIMIT);
-          PH(3);
           fence_after_sync();
           const uint32_t d = tmem + 256 + t * 128;
           const uint32_t a = tmem + (buf * 2 + t) * 64;
@@ -263,11 +264,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
 #pragma unroll
           for (int ks = 0; ks < TK / 16; ++ks)
             mma_ts_lh(d, a + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-          PH(4);
         }
         mma_commit(&bars[B_PVDONE + buf]);
       }
-      PH_PRINT("fwd mma [wait kfull, issue S, wait vfull, wait pfull, issue PV]", T_tiles);
     }
     __syncwarp();
   } else {
@@ -279,7 +278,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
     const int T_mine = tile == 0 ? T0 : T1;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     float m_run = -CUDART_INF_F, l_run = 0.f;
-    PH_DECL;
 
     for (int j = 0; j < T_mine; ++j) {
       const int buf = j & 1, n0 = j * TK;
@@ -296,16 +294,13 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
         vis &= lim >= 63 ? ~0ull : (lim < 0 ? 0ull : ((2ull << lim) - 1ull));
       }
       const bool all_vis = __all_sync(0xffffffffu, vis == ~0ull);
-      PH(0);
       if (!failed) failed = !mbar_wait(&bars[B_SFULL + buf * 2 + tile], (j >> 1) & 1, WAIT_LIMIT);
       fence_after_sync();
-      PH(1);
       const uint32_t s_addr = tmem + lane_base + (buf * 2 + tile) * 64;
       uint32_t s0[32], s1[32];
       tmem_ld32(s_addr, s0);
       tmem_ld32(s_addr + 32, s1);
       tmem_ld_wait();
-      PH(2);
       // row maximum (four independent chains)
       float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (all_vis) {
@@ -349,7 +344,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
         }
         tmem_st_wait();
       }
-      PH(3);
       // P = 2^(s*c - m), written over the scores (16 packed columns per 32 scores)
       const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -381,10 +375,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars[B_PFULL + buf * 2 + tile]);
-      PH(4);
     }
-    if (tid == 128 && T_mine > 0) PH_PRINT("fwd softmax tile1 [vis, wait S, ld, max+rescale, exp+st]", T_mine);
-    PH(5);
 
     // ---- epilogue: O / l, LSE ---------------------------------------------------------------------
     if (T_mine > 0) {
@@ -414,8 +405,6 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
       if (row < p.Nq)
         p.lse[(int64_t)u * p.Nq + row] = l_run > 0.f ? m_run * LN2 + logf(l_run) : -CUDART_INF_F;
     }
-    PH(6);
-    if (tid == 128 && T_mine > 0) PH_PRINT("fwd softmax tile1 [.., 5: print, 6: epilogue total/tiles]", T_mine);
   }
   if (failed) atomicOr(&g_tc_status, 1u);
   fence_before_sync();
