@@ -243,8 +243,8 @@ def main():
     flops_rank = algorithmic_flops(B, H, N, d, r, True)
     value = flops_rank * world / (ms_per_step * 1e-3) / 1e12
     # kernels of this library per step -- exact-arithmetic path: fwd, delta, dq, dkdv; tensor-core path:
-    # phase table + fwd, then delta + phase table + dq + dkdv
-    launches_per_step = 4 if path == "simt" else 6
+    # phase table + operand images + fwd, then phase table + operand images + row statistics + dq + dkdv
+    launches_per_step = 4 if path == "simt" else 8
 
     # ---- end to end: pinned host buffers -> public API -> results back on the host -------------
     hq, hk, hv, hdo = make_inputs(3000 + rank, w, pin=True)

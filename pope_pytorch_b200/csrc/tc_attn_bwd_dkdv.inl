@@ -318,31 +318,56 @@ bool attn_bwd_tc_supported(const PopeAttnBwdArgs& a) {
   if (s.Nq < 64) return false;
   if (s.r > 0 && (a.embed.sf.b != 0 || a.embed.sf.h != 0)) return false;
   if (a.dfreqs && (a.sdf.b != 0 || a.sdf.h != 0)) return false;
-  const void* ptrs[] = {a.q, a.k, a.v, a.dout, a.dq, a.dk, a.dv};
+  const void* ptrs[] = {a.q, a.k, a.v, a.out, a.dout, a.dq, a.dk, a.dv};
   for (const void* ptr : ptrs)
     if (!bwd_aligned16(ptr)) return false;
-  const PopeStride3 strides[] = {a.sq, a.sk, a.sv, a.sdo, a.sdq, a.sdk, a.sdv};
+  const PopeStride3 strides[] = {a.sq, a.sk, a.sv, a.so, a.sdo, a.sdq, a.sdk, a.sdv};
   for (const PopeStride3& st : strides)
     if (!bwd_stride_ok(st)) return false;
   return true;
 }
 
-// lse and delta of every 64-query tile in the order the dk/dv kernel consumes them, padded to whole tiles so
-// that one aligned 512-byte bulk copy brings a tile's rows: [unit][tile][64 x lse * log2(e) | 64 x delta].
-// Empty rows (lse = -inf) and rows past Nq carry +inf, which makes their probabilities exactly 0.
-__global__ void bwd_rowstat_kernel(const float* __restrict__ lse, const float* __restrict__ delta, int Nq, float* __restrict__ out) {
-  const int t = threadIdx.x, tile = blockIdx.x, u = blockIdx.y, i = tile * BT + t;
-  const float l = i < Nq ? lse[(int64_t)u * Nq + i] : -CUDART_INF_F;
-  float* o = out + ((int64_t)u * gridDim.x + tile) * (2 * BT);
-  o[t] = l == -CUDART_INF_F ? CUDART_INF_F : l * LOG2E;
-  o[BT + t] = i < Nq ? delta[(int64_t)u * Nq + i] : 0.f;
+// Row statistics of the backward in one pass over out and dout: delta[u, i] = <out_i, dout_i>
+// (PoPE_pytorch/triton_pope_flash_attn.py:119-130) as a plain (B*H, Nq) array for the dq kernel, and, in the order
+// the dk/dv kernel consumes them, [unit][64-query tile][64 x lse * log2(e) | 64 x delta], padded to whole tiles so
+// that one aligned 512-byte bulk copy brings a tile's rows.  Empty rows (lse = -inf) and rows past Nq carry +inf,
+// which makes their probabilities exactly 0.  grid (tiles, units), 256 threads: four threads per row.
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_rowstat_kernel(const T* __restrict__ out, Strides so, const T* __restrict__ dout,
+                                                           Strides sdo, const float* __restrict__ lse, int H, int Nq, int d,
+                                                           float* __restrict__ delta, float* __restrict__ rowstat) {
+  const int tile = blockIdx.x, u = blockIdx.y, b = u / H, h = u % H;
+  const int t = threadIdx.x >> 2, part = threadIdx.x & 3, i = tile * BT + t;
+  float acc = 0.f;
+  if (i < Nq) {
+    const T* o = out + b * so.b + h * so.h + (int64_t)i * so.n;
+    const T* g = dout + b * sdo.b + h * sdo.h + (int64_t)i * sdo.n;
+    for (int c = part * 8; c < d; c += 32) {
+      const uint4 ov = __ldg(reinterpret_cast<const uint4*>(o + c)), gv = __ldg(reinterpret_cast<const uint4*>(g + c));
+      const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 x = unpack2<T>(ow[e]), y = unpack2<T>(gw[e]);
+        acc = fmaf(x.x, y.x, fmaf(x.y, y.y, acc));
+      }
+    }
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  if (part == 0) {
+    const float l = i < Nq ? lse[(int64_t)u * Nq + i] : -CUDART_INF_F;
+    float* rs = rowstat + ((int64_t)u * gridDim.x + tile) * (2 * BT);
+    rs[t] = l == -CUDART_INF_F ? CUDART_INF_F : l * LOG2E;
+    rs[BT + t] = i < Nq ? acc : 0.f;
+    if (i < Nq) delta[(int64_t)u * Nq + i] = acc;
+  }
 }
 
-// workspace: [delta][fp32 cos / sin table][K' images][Q' images][V images][dO images][row statistics], each
+// workspace: [delta][fp32 and fp16 cos / sin tables][K' images][Q' images][V images][dO images][row statistics], each
 // rounded up to 256 bytes
 static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 static size_t delta_bytes(const PopeShape& s) { return up256((size_t)s.B * s.H * s.Nq * sizeof(float)); }
-static size_t bwd_table_bytes(const PopeShape& s) { return trig_table_f32_bytes(s.Nk, s.r); }
+static size_t bwd_table_bytes(const PopeShape& s) { return trig_tables_bytes(s.Nk, s.r); }
 static size_t rowstat_bytes(const PopeShape& s) { return up256((size_t)s.B * s.H * image_tiles(s.Nq) * 2 * BT * sizeof(float)); }
 
 size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
@@ -359,24 +384,24 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const bool bf16 = s.dtype == POPE_BF16;
   uint8_t* ws = reinterpret_cast<uint8_t*>(a.workspace);
   float* delta = reinterpret_cast<float*>(ws);
-  float* ctab = reinterpret_cast<float*>(ws + delta_bytes(s));
-  float* stab = ctab + (size_t)s.Nk * s.r;
+  const TrigTables tt = trig_tables_at(ws + delta_bytes(s), s.Nk, s.r);
   uint8_t* kimg = ws + delta_bytes(s) + bwd_table_bytes(s);
   uint8_t* qimg = kimg + up256(image_bytes(s.B * s.Hk, s.Nk, KD));
   uint8_t* vimg = qimg + up256(image_bytes(s.B * s.H, s.Nq, KD));
   uint8_t* gimg = vimg + up256(image_bytes(s.B * s.Hk, s.Nk, s.d));
   float* rowstat = reinterpret_cast<float*>(gimg + up256(image_bytes(s.B * s.H, s.Nq, s.d)));
-  cudaError_t e = attn_bwd_delta(a, delta, st);
-  if (e != cudaSuccess) return e;
-  if (s.r > 0 && (e = launch_trig_table_f32(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, ctab, stab, st)) != cudaSuccess) return e;
+  cudaError_t e;
+  if (s.r > 0 && (e = launch_trig_tables(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, tt.ctab, tt.stab, tt.ch, tt.sh, st)) != cudaSuccess) return e;
   // K' (phase bias folded in), Q', and V / dO as the same tiles without rotated features (a pure re-layout)
   ExpandJobs jobs;
   jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg);
   jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg);
   jobs.job[2] = expand_job(a.v, a.sv, s.B, s.Hk, s.Nk, 0, 0, nullptr, 0, vimg);
   jobs.job[3] = expand_job(a.dout, a.sdo, s.B, s.H, s.Nq, 0, 0, nullptr, 0, gimg);
-  if ((e = launch_expand_images(jobs, 4, s.d, bf16, ctab, stab, st)) != cudaSuccess) return e;
-  bwd_rowstat_kernel<<<dim3((unsigned)image_tiles(s.Nq), s.B * s.H), BT, 0, st>>>(a.lse, delta, s.Nq, rowstat);
+  if ((e = launch_expand_images(jobs, 4, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+  bwd_rowstat_kernel<T><<<dim3((unsigned)image_tiles(s.Nq), s.B * s.H), 256, 0, st>>>(
+      static_cast<const T*>(a.out), Strides(a.so), static_cast<const T*>(a.dout), Strides(a.sdo), a.lse, s.H, s.Nq, s.d, delta,
+      rowstat);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   TcBwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
@@ -385,7 +410,7 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.sdo = a.sdo, p.sdq = a.sdq, p.sdk = a.sdk, p.sdv = a.sdv, p.sdf = a.sdf;
   p.freqs = a.embed.freqs, p.bias = a.embed.bias, p.lse = a.lse, p.delta = delta;
   p.sfn = a.embed.sf.n, p.bias_sh = a.embed.bias_stride_h, p.dbias_sh = a.dbias_stride_h;
-  p.ctab = ctab, p.stab = stab, p.kimg = kimg, p.qimg = qimg, p.vimg = vimg, p.gimg = gimg, p.rowstat = rowstat;
+  p.ctab = tt.ctab, p.stab = tt.stab, p.kimg = kimg, p.qimg = qimg, p.vimg = vimg, p.gimg = gimg, p.rowstat = rowstat;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   p.dfreqs = s.r > 0 ? a.dfreqs : nullptr, p.dbias = s.r > 0 ? a.dbias : nullptr;
   p.status = tc_status_ptr();

@@ -428,12 +428,12 @@ bool attn_fwd_tc_supported(const PopeAttnArgs& a) {
   return true;
 }
 
-// workspace: [fp32 cos / sin table][K' image tiles of all (batch, key head) units][Q' image tiles of all (batch, head) units]
+// workspace: [fp32 and fp16 cos / sin tables][K' image tiles of all (batch, key head) units][Q' image tiles of all (batch, head) units]
 static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 size_t attn_fwd_tc_workspace(const PopeAttnArgs& a) {
   const PopeShape& s = a.shape;
-  return trig_table_f32_bytes(s.Nk, s.r) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) + image_bytes(s.B * s.H, s.Nq, s.d + s.r);
+  return trig_tables_bytes(s.Nk, s.r) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) + image_bytes(s.B * s.H, s.Nq, s.d + s.r);
 }
 
 template <int D, typename T>
@@ -442,9 +442,8 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   const int KD = s.d + s.r;
   const bool bf16 = s.dtype == POPE_BF16;
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
-  float* ctab = reinterpret_cast<float*>(ws);
-  float* stab = ctab + (size_t)s.Nk * s.r;
-  uint8_t* kimg = ws + trig_table_f32_bytes(s.Nk, s.r);
+  const TrigTables tt = trig_tables_at(ws, s.Nk, s.r);
+  uint8_t* kimg = ws + trig_tables_bytes(s.Nk, s.r);
   uint8_t* qimg = kimg + up256(image_bytes(s.B * s.Hk, s.Nk, KD));
   TcFwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
@@ -455,11 +454,11 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   p.qimg = qimg, p.kimg = kimg;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   cudaError_t e;
-  if (s.r > 0 && (e = launch_trig_table_f32(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, ctab, stab, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_tables(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, tt.ctab, tt.stab, tt.ch, tt.sh, st)) != cudaSuccess) return e;
   ExpandJobs jobs;
   jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg);
   jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg);
-  if ((e = launch_expand_images(jobs, 2, s.d, bf16, ctab, stab, st)) != cudaSuccess) return e;
+  if ((e = launch_expand_images(jobs, 2, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
   CUtensorMap tmap_v;
   if (!make_chunk_tmap(&tmap_v, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, TK)) return cudaErrorNotSupported;
   size_t smem = (size_t)2 * TQ * KD * 2 + 2 * (size_t)TK * KD * 2 + 2 * (size_t)TK * D * 2 + (B_COUNT + 1) * 8 + 16;

@@ -103,12 +103,25 @@ inline ExpandJob expand_job(const void* x, const PopeStride3& sx, int batch, int
   j.bias = r > 0 ? bias : nullptr, j.bias_sh = bias_sh, j.img = img;
   return j;
 }
-// ctab / stab = fp32 cos / sin of the phase table, [positions][r].  All jobs share d and the dtype; one launch.
-cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const float* ctab, const float* stab,
+// ch / sh = fp16 cos / sin of the phase table, [positions][r].  All jobs share d and the dtype; one launch.
+cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const void* ch, const void* sh,
                                  cudaStream_t st);
-// fp32 cos / sin of freqs[pos][c] into ctab / stab ([n][r] each)
+// fp32 cos / sin of freqs[pos][c] into ctab / stab ([n][r] each); launch_trig_tables also writes fp16 copies (ch, sh).
 cudaError_t launch_trig_table_f32(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, cudaStream_t st);
-inline size_t trig_table_f32_bytes(int n, int r) { return ((size_t)n * r * 2 * sizeof(float) + 255) & ~(size_t)255; }
+cudaError_t launch_trig_tables(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, void* ch, void* sh,
+                               cudaStream_t st);
+// Table block of the attention workspace: [cos fp32][sin fp32][cos fp16][sin fp16], n*r entries each.
+struct TrigTables {
+  float *ctab, *stab;
+  void *ch, *sh;
+};
+inline size_t trig_tables_bytes(int n, int r) { return ((size_t)n * r * 12 + 255) & ~(size_t)255; }
+inline TrigTables trig_tables_at(void* base, int n, int r) {
+  TrigTables t;
+  t.ctab = static_cast<float*>(base), t.stab = t.ctab + (size_t)n * r;
+  t.ch = t.stab + (size_t)n * r, t.sh = static_cast<uint8_t*>(t.ch) + (size_t)n * r * 2;
+  return t;
+}
 
 // A resident 128-row operand [chunk][128 rows][16 B] out of two consecutive image tiles: 2 x `chunks` bulk copies
 // of 1 KB, issued by the lanes of one warp after one of them has posted 2 * chunks * 1024 transaction bytes on `bar`.

@@ -22,8 +22,8 @@ namespace pope {
 // grid (tiles, units, jobs), 256 threads; dynamic shared memory (d+r)/8 * CS64 bytes + 2 r floats.  One launch
 // builds the images of up to four operands (blockIdx.z picks the job); CTAs outside a job's tile / unit range leave.
 template <typename T, int D>
-__global__ void __launch_bounds__(256) expand_image_kernel(ExpandJobs jobs, const float* __restrict__ ctab,
-                                                            const float* __restrict__ stab) {
+__global__ void __launch_bounds__(256) expand_image_kernel(ExpandJobs jobs, const __half* __restrict__ ctab,
+                                                            const __half* __restrict__ stab) {
   extern __shared__ __align__(16) uint8_t stage[];
   const ExpandJob& jb = jobs.job[blockIdx.z];
   const int tid = threadIdx.x, tile = blockIdx.x, u = blockIdx.y;
@@ -58,11 +58,15 @@ __global__ void __launch_bounds__(256) expand_image_kernel(ExpandJobs jobs, cons
     if (c < RC) {
       uint4 oc = make_uint4(0, 0, 0, 0), os = oc;
       if (j < rows) {
-        const float4* cp = reinterpret_cast<const float4*>(ctab + (int64_t)(jb.pos0 + j) * r + c * 8);
-        const float4* sp = reinterpret_cast<const float4*>(stab + (int64_t)(jb.pos0 + j) * r + c * 8);
-        const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
-        float co[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        float si[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const uint4 cq = __ldg(reinterpret_cast<const uint4*>(ctab + (int64_t)(jb.pos0 + j) * r + c * 8));
+        const uint4 sq = __ldg(reinterpret_cast<const uint4*>(stab + (int64_t)(jb.pos0 + j) * r + c * 8));
+        const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w}, sw[4] = {sq.x, sq.y, sq.z, sq.w};
+        float co[8], si[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 cv = unpack2<__half>(cw[e]), sv = unpack2<__half>(sw[e]);
+          co[2 * e] = cv.x, co[2 * e + 1] = cv.y, si[2 * e] = sv.x, si[2 * e + 1] = sv.y;
+        }
         if (bias) {   // cos(f + b), sin(f + b)
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
@@ -98,7 +102,7 @@ __global__ void __launch_bounds__(256) expand_image_kernel(ExpandJobs jobs, cons
 }
 
 template <typename T>
-static cudaError_t launch_expand_t(const ExpandJobs& jobs, int njobs, int d, const float* ctab, const float* stab,
+static cudaError_t launch_expand_t(const ExpandJobs& jobs, int njobs, int d, const __half* ctab, const __half* stab,
                                    cudaStream_t st) {
   int tiles = 0, units = 0, rmax = 0;
   for (int i = 0; i < njobs; ++i) {
@@ -117,9 +121,11 @@ static cudaError_t launch_expand_t(const ExpandJobs& jobs, int njobs, int d, con
   return cudaGetLastError();
 }
 
-cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const float* ctab, const float* stab,
+cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const void* ch, const void* sh,
                                  cudaStream_t st) {
   if (njobs < 1 || njobs > 4) return cudaErrorInvalidValue;
+  const __half* ctab = static_cast<const __half*>(ch);
+  const __half* stab = static_cast<const __half*>(sh);
   return is_bf16 ? launch_expand_t<__nv_bfloat16>(jobs, njobs, d, ctab, stab, st)
                  : launch_expand_t<__half>(jobs, njobs, d, ctab, stab, st);
 }

@@ -38,17 +38,28 @@ constexpr int SIM_THREADS = 288;
 constexpr int SIM_STG_ROW = 256 + 16;             // staging row: 64 fp32 columns + padding (conflict-free 16-byte stores)
 constexpr int SIM_STG = SIM_M * SIM_STG_ROW;      // bytes of the output staging tile
 
-__global__ void pope_trig_table_f32_kernel(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab) {
+// ch / sh (may be null): the same tables rounded to fp16 (cos and sin lie in [-1, 1]: 2^-12 absolute error), read by
+// the operand-image pre-pass, whose result is rounded to 8 or 11 bits anyway.
+__global__ void pope_trig_table_f32_kernel(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab,
+                                           __half* ch, __half* sh) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)n * r) return;
   const int pos = idx / r, c = idx % r;
-  sincosf(freqs[pos * sfn + c], &stab[idx], &ctab[idx]);
+  float sn, cs;
+  sincosf(freqs[pos * sfn + c], &sn, &cs);
+  stab[idx] = sn, ctab[idx] = cs;
+  if (ch) ch[idx] = __float2half_rn(cs), sh[idx] = __float2half_rn(sn);
 }
 
-cudaError_t launch_trig_table_f32(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, cudaStream_t st) {
+cudaError_t launch_trig_tables(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, void* ch, void* sh,
+                               cudaStream_t st) {
   const int64_t total = (int64_t)n * r;
-  pope_trig_table_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(freqs, sfn, n, r, ctab, stab);
+  pope_trig_table_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(freqs, sfn, n, r, ctab, stab,
+                                                                               static_cast<__half*>(ch), static_cast<__half*>(sh));
   return cudaGetLastError();
+}
+cudaError_t launch_trig_table_f32(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, cudaStream_t st) {
+  return launch_trig_tables(freqs, sfn, n, r, ctab, stab, nullptr, nullptr, st);
 }
 
 template <typename T> struct Load8;
@@ -342,7 +353,7 @@ static cudaError_t launch_sim_tc(const PopeSimArgs& a, cudaStream_t st) {
   if (!p.status) return cudaErrorInvalidSymbol;
   if (s.r > 0) {
     const int64_t n = (int64_t)s.Nk * s.r;
-    pope_trig_table_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, ctab, stab);
+    pope_trig_table_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, ctab, stab, nullptr, nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
