@@ -103,13 +103,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
         mma_commit(&bars[BB_SCORES]);
       };
       if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
+      PH_DECL;
       for (int j = 0; j < T_tiles && !failed; ++j) {
         failed = !mbar_wait(&bars[BB_FULL + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
+        PH(0);
         // the elementwise warps have copied the previous tile's scores out of TMEM
         if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
+        PH(1);
         fence_after_sync();
         issue_scores(j);
+        PH(2);
       }
+      PH_PRINT("dkdv scores warp [wait full, wait consumed, issue]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -120,10 +125,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
       const uint32_t qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb), ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
       const uint64_t pa = smem_desc(ps_addr, BQ * 16, 128), da = smem_desc(ds_addr, BQ * 16, 128);
+      PH_DECL;
       for (int j = 0; j < T_tiles && !failed; ++j) {
         const int buf = j & 1;
         failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);
         if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
+        PH(0);
         fence_after_sync();
         // the streamed tiles re-described as MN-major B operands
         const uint64_t gd = smem_desc(gb_addr + buf * VBUF, 128, BCS), qd = smem_desc(qb_addr + buf * KBUF, 128, BCS);
@@ -134,7 +141,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
           mma_ss_lh(tmem + 128, desc_lo(pa) + astep, desc_hi(pa), desc_lo(gd) + bstep, desc_hi(gd), idesc_v, acc);
         }
         mma_commit(&bars[BB_ACC + buf]);   // every score product of this tile finished before its P^T / dS^T existed
+        PH(1);
       }
+      PH_PRINT("dkdv acc warp [wait grad, issue]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -153,12 +162,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const int gj = j0 + row;
   const bool key_ok = gj < p.Nk && (!maskb || maskb[(int64_t)gj * p.msn] != 0);
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  PH_DECL;
   for (int j = 0; j < T_tiles; ++j) {
     const int buf = j & 1;
     const int m0 = tile_start(j);
     if (!failed) failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the lse / delta read
     if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
     fence_after_sync();
+    PH(0);
     const float* st = rowstat + buf * 128 + half * 32;
     // interior tile for this warp: every key row valid and (causal) every key at or before every query column;
     // out-of-range queries and rows without any visible key carry lse = +inf, which makes P exactly 0
@@ -171,6 +182,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     // every score of this tile is in registers: the next score products may overwrite them
     fence_before_sync();
     warp_arrive(&bars[BB_CONSUMED], lane);
+    PH(1);
     uint32_t pw[16], dw[16];   // P^T and dS^T of this thread's 32 query columns, packed in pairs
     // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
     auto elementwise = [&](auto masked) {
@@ -196,8 +208,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     };
     if (interior) elementwise(std::false_type());
     else elementwise(std::true_type());
+    PH(2);
     // the P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+    PH(3);
 #pragma unroll
     for (int c8 = 0; c8 < 4; ++c8) {
       const int chunk = half * 4 + c8;
@@ -206,7 +220,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     }
     fence_async_smem();
     warp_arrive(&bars[BB_GRAD], lane);
+    PH(4);
   }
+  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [wait scores, ld+arrive, math, wait acc, st+arrive]", T_tiles);
 
   // ---- epilogue ---------------------------------------------------------------------------------
   if (T_tiles > 0 && !failed)
