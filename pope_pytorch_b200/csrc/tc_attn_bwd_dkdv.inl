@@ -223,26 +223,29 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     PH(4);
   }
   if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [wait scores, ld+arrive, math, wait acc, st+arrive]", T_tiles);
+  PH(5);
 
   // ---- epilogue ---------------------------------------------------------------------------------
   if (T_tiles > 0 && !failed)
     failed = !mbar_wait(&bars[BB_ACC + ((T_tiles - 1) & 1)], ((T_tiles - 1) >> 1) & 1, WAIT_LIMIT);
   fence_after_sync();
   asm volatile("bar.sync 1, 256;" ::: "memory");   // every MMA is done: the streamed buffers can be reused
-  float* red = reinterpret_cast<float*>(Qb);   // [r] per-CTA sum of the key-phase gradient
+  // Everything below reuses dead shared memory: the streamed buffers hold the bias trig and the per-row key-phase
+  // gradients (feature-major, [r][128 rows] fp32); the resident K' / V tiles become row-major staging tiles of dk
+  // and dv, so that both leave in fully coalesced 16-byte pieces.
+  constexpr int OSTR = D * 2 + 16;             // bytes of a staged output row (16 bytes of padding: conflict-free)
+  uint8_t* dk_stage = Ks;                      // (the two tiles may run a few KB past K' and V into the streamed
+  uint8_t* dv_stage = Ks + BQ * OSTR;          //  buffers, which only happens when r = 0 and nothing else lives there)
+  float* red = reinterpret_cast<float*>(Qb);   // (unused tail of the first 2 KB: bias trig below)
+  float* dmat = reinterpret_cast<float*>(Qb + 2048);   // [r][128]
   float* bias_cb = red + 128;                  // cos / sin of the head's phase bias
   float* bias_sb = red + 256;
-  for (int c = tid; c < p.r; c += 256) {
-    red[c] = 0.f;
-    sincosf(biasr[c], &bias_sb[c], &bias_cb[c]);
-  }
+  for (int c = tid; c < p.r; c += 256) sincosf(biasr[c], &bias_sb[c], &bias_cb[c]);
   asm volatile("bar.sync 1, 256;" ::: "memory");
   {
     constexpr int HW = D / 2;
     const uint32_t accv = tmem + lane_base + 128, acck = tmem + lane_base + 256;
     const T* krow = kbase + (int64_t)gj * p.sk.n;
-    T* dkrow = (T*)p.dk + b * p.sdk.b + hk * p.sdk.h + (int64_t)gj * p.sdk.n;
-    T* dvrow = (T*)p.dv + b * p.sdv.b + hk * p.sdv.h + (int64_t)gj * p.sdv.n;
     const int64_t trow = (int64_t)gj * p.r;   // row of the fp32 cos / sin tables
     float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + hk * p.sdf.h + (int64_t)gj * p.sdf.n : nullptr;
     const bool live = gj < p.Nk;
@@ -295,28 +298,44 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
             g0 = (g0 * cf[e] + h0 * sf[e]) * sigmoid_fast(x.x);
             g1 = (g1 * cf[e + 1] + h1 * sf[e + 1]) * sigmoid_fast(x.y);
           }
-          if (p.dbias) {   // warp-uniform branch: sum over the 32 key rows of this warp
-            d0 = warp_sum(d0), d1 = warp_sum(d1);
-            if ((tid & 31) == 0) atomicAdd(&red[cbase + e], d0), atomicAdd(&red[cbase + e + 1], d1);
-          }
+          if (p.dbias) dmat[(cbase + e) * BQ + row] = d0, dmat[(cbase + e + 1) * BQ + row] = d1;
           wk[e >> 1] = pack2<T>(g0, g1);
         }
       } else {
 #pragma unroll
         for (int e = 0; e < 16; e += 2) wk[e >> 1] = pack2<T>(__uint_as_float(gc[e]), __uint_as_float(gc[e + 1]));
       }
-      if (live) {
-        *reinterpret_cast<uint4*>(dvrow + cbase) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-        *reinterpret_cast<uint4*>(dvrow + cbase + 8) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
-        *reinterpret_cast<uint4*>(dkrow + cbase) = make_uint4(wk[0], wk[1], wk[2], wk[3]);
-        *reinterpret_cast<uint4*>(dkrow + cbase + 8) = make_uint4(wk[4], wk[5], wk[6], wk[7]);
+      *reinterpret_cast<uint4*>(dv_stage + row * OSTR + cbase * 2) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+      *reinterpret_cast<uint4*>(dv_stage + row * OSTR + cbase * 2 + 16) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
+      *reinterpret_cast<uint4*>(dk_stage + row * OSTR + cbase * 2) = make_uint4(wk[0], wk[1], wk[2], wk[3]);
+      *reinterpret_cast<uint4*>(dk_stage + row * OSTR + cbase * 2 + 16) = make_uint4(wk[4], wk[5], wk[6], wk[7]);
+    }
+  }
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  {
+    // dk / dv rows leave 16 bytes per thread: consecutive threads cover one 2 D-byte row after the other
+    constexpr int GPR = D / 8;   // 16-byte groups per row
+    T* dkbase = (T*)p.dk + b * p.sdk.b + hk * p.sdk.h;
+    T* dvbase = (T*)p.dv + b * p.sdv.b + hk * p.sdv.h;
+    for (int idx = tid; idx < BQ * GPR; idx += 256) {
+      const int rr = idx / GPR, g = idx - rr * GPR;
+      if (j0 + rr < p.Nk) {
+        *reinterpret_cast<uint4*>(dkbase + (int64_t)(j0 + rr) * p.sdk.n + g * 8) = *reinterpret_cast<const uint4*>(dk_stage + rr * OSTR + g * 16);
+        *reinterpret_cast<uint4*>(dvbase + (int64_t)(j0 + rr) * p.sdv.n + g * 8) = *reinterpret_cast<const uint4*>(dv_stage + rr * OSTR + g * 16);
+      }
+    }
+    if (p.dbias) {
+      // column sums of the key-phase gradient: one warp per feature, lanes stride over the 128 rows
+      for (int c = warp; c < p.r; c += BWD_E_WARPS) {
+        const float* col = dmat + c * BQ;
+        float sum = (col[lane] + col[lane + 32]) + (col[lane + 64] + col[lane + 96]);
+        sum = warp_sum(sum);
+        if (lane == 0) atomicAdd(p.dbias + hk * p.dbias_sh + c, sum);
       }
     }
   }
-  if (p.dbias && p.r > 0) {
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    for (int c = tid; c < p.r; c += 256) atomicAdd(p.dbias + hk * p.dbias_sh + c, red[c]);
-  }
+  PH(6);
+  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [..., 5: print, 6: epilogue total / tiles]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier
