@@ -72,7 +72,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu_index), "-lms", "50"],
+                                          "-i", str(self.gpu_index), "-lms", "20"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -161,7 +161,7 @@ def run_reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -285,6 +285,7 @@ def main():
     achieved = flops_rank / (ms_per_step * 1e-3) / 1e12
     pairs = N * N / 2
     bwd_flops = 2.0 * B * H * pairs * (5 * d + 3 * r)
+    fwd_flops = 2.0 * B * H * pairs * (2 * d + r)
     bwd_achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
     peak_sus = pk["bf16_tflops_sustained"] or pk["bf16_tflops"]
 
@@ -329,18 +330,21 @@ def main():
         data="synthetic",
         config=dict(workload=w["name"], per_gpu_batch=B, global_batch=B * world, heads=H, seq_len=N, head_dim=d,
                     rotate_dim=r, causal=True, sharding=f"batch x heads units, {world} rank(s), no collective",
-                    l2="per-step working set 340 MB exceeds the 126 MB L2; no explicit flush", kernel_path=path),
+                    l2="per-step working set (inputs, outputs and operand images: 0.9 GB) exceeds the 126 MB L2; no explicit flush", kernel_path=path),
         tokens_per_s=B * N * world / (ms_per_step * 1e-3),
         fwd_ms=fwd_ms, bwd_ms=bwd_ms,
         pct_of_nominal_bf16_peak=100.0 * achieved / 2250.0,
         roofline=dict(bound="tensor", achieved=bwd_achieved, peak=peak_sus, unit="TFLOP/s", frac=bwd_achieved / peak_sus,
-                      traffic=322.0e6 + 308.0e6,
-                      kernel="backward pass = attn_bwd_dkdv_tc_kernel + attn_bwd_dq_tc_kernel (99 % of its time; one "
-                             "C-ABI call launches both, timed together with CUDA events on the launch stream)",
+                      traffic=4 * (122.5e6 + 9.6e6 + 122.9e6 + 17.9e6),
+                      kernel="backward pass = attn_bwd_dkdv_tc_kernel + attn_bwd_dq_tc_kernel (92 % of its time; the rest "
+                             "is its pre-pass: operand images, row statistics, phase tables; one C-ABI call launches all "
+                             "of it, timed together with CUDA events on the launch stream)",
                       peak_source=f"{pk['source']} sustained bf16 GEMM (kernels timed inside a long step)",
                       algorithmic_flops_per_launch=bwd_flops,
-                      traffic_note="dram read+write bytes of one ncu capture at B=1 (80.5 MB dkdv, 77.0 MB dq), "
-                                   "scaled by 4: traffic is proportional to the number of (b,h) units",
+                      traffic_note="dram read+write bytes of the dq and dkdv launches of one ncu capture at B=1 (132.1 MB dq, "
+                                   "140.8 MB dkdv), scaled by 4: traffic is proportional to the number of (b,h) units",
+                      forward=dict(achieved=fwd_flops / (fwd_ms * 1e-3) / 1e12, frac=fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak_sus,
+                                   what="forward call (tables + images + attn_fwd_tc_kernel), algorithmic flops 2*U*pairs*(2d+r)"),
                       step=dict(achieved=achieved, frac=achieved / peak_sus, frac_of_burst_peak=achieved / pk["bf16_tflops"],
                                 what="forward + backward of one step, algorithmic flops 2*U*pairs*(7d+4r)")),
         secondary=secondary,

@@ -1,6 +1,21 @@
 // dk / dv kernel and the host-side launch of the tensor-core backward (included by tc_attn_bwd.cu).
 namespace pope {
 
+// mbarrier slots of the dk/dv kernel.  Q' tiles have three stages and dO tiles two: that is what fits beside the
+// resident K' and V once P^T and dS^T live in TMEM, and the Q' tile is the one whose copy is needed first.
+enum { KB_QFULL = 0,     // [3] Q' tile j (and its lse / delta rows) has landed in stage j % 3
+       KB_GFULL = 3,     // [2] dO tile j has landed in stage j % 2
+       KB_ACCQ = 5,      // [3] tcgen05.commit: accumulation of tile j finished (slot j % 3): its Q' stage is free
+       KB_ACCG = 8,      // [2] the same event in slot j % 2: the dO stage and the P^T / dS^T columns are free
+       KB_SDONE = 10,    // tcgen05.commit: S^T of the current tile is in TMEM
+       KB_DPDONE = 11,   // tcgen05.commit: dP^T of the current tile is in TMEM (same columns as S^T)
+       KB_CONS_S = 12,   // 8 warps: S^T copied to registers, dP^T may overwrite it
+       KB_CONS_DP = 13,  // 8 warps: dP^T copied to registers, the next S^T may overwrite it
+       KB_GRAD = 14,     // 8 warps: P^T and dS^T of the current tile are written to TMEM
+       KB_RESIDENT = 15, // the resident K' and V tiles have landed
+       KB_COUNT = 16 };
+constexpr int KQ_NST = 3, KG_NST = 2;
+
 template <int D, typename T>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -8,13 +23,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   uint8_t* Ks = smem;                          // [KD/8][128][16 B]  resident K' (phase fk + bias)
   uint8_t* Vs = Ks + BQ * KD * 2;              // [D/8][128][16 B]   resident V
   const int KBUF = (KD / 8) * BCS, VBUF = (D / 8) * BCS;  // one streamed buffer
-  uint8_t* Qb = Vs + BQ * D * 2;               // 2 x [KD/8][64][16 B] streamed Q'
-  uint8_t* Gb = Qb + 2 * KBUF;                 // 2 x [D/8][64][16 B]  streamed dO
-  uint8_t* Ps = Gb + 2 * VBUF;                 // [8 chunks][128][16 B] P^T  (A operand, K = 64 queries)
-  uint8_t* Ds = Ps + BQ * BT * 2;              // [8 chunks][128][16 B] dS^T
-  float* rowstat = reinterpret_cast<float*>(Ds + BQ * BT * 2);  // 2 bufs x (64 lse*log2e, 64 delta)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(rowstat + 2 * 128);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BB_COUNT + 1);
+  uint8_t* Qb = Vs + BQ * D * 2;               // 3 x [KD/8][64][16 B] streamed Q'
+  uint8_t* Gb = Qb + KQ_NST * KBUF;            // 2 x [D/8][64][16 B]  streamed dO
+  float* rowstat = reinterpret_cast<float*>(Gb + KG_NST * VBUF);  // 3 x (64 lse*log2e, 64 delta), with the Q' stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rowstat + KQ_NST * 128);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + KB_COUNT + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.Hk, hk = u % p.Hk;
@@ -28,10 +41,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     tmem_relinquish();
   }
   if (tid == 0) {
-    mbar_init(&bars[BB_FULL], 1), mbar_init(&bars[BB_FULL + 1], 1);
-    mbar_init(&bars[BB_SCORES], 1), mbar_init(&bars[BB_ACC], 1), mbar_init(&bars[BB_ACC + 1], 1);
-    mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
-    mbar_init(&bars[BB_RESIDENT], 1);
+    for (int i = 0; i < KQ_NST; ++i) mbar_init(&bars[KB_QFULL + i], 1), mbar_init(&bars[KB_ACCQ + i], 1);
+    for (int i = 0; i < KG_NST; ++i) mbar_init(&bars[KB_GFULL + i], 1), mbar_init(&bars[KB_ACCG + i], 1);
+    mbar_init(&bars[KB_SDONE], 1), mbar_init(&bars[KB_DPDONE], 1);
+    mbar_init(&bars[KB_CONS_S], BWD_E_WARPS), mbar_init(&bars[KB_CONS_DP], BWD_E_WARPS), mbar_init(&bars[KB_GRAD], BWD_E_WARPS);
+    mbar_init(&bars[KB_RESIDENT], 1);
     mbar_init_fence();
   }
   // query tiles: under the causal mask rows i < j0 see none of this CTA's keys
@@ -51,70 +65,85 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  // TMEM columns: S^T [0,64), dP^T [64,128), dV [128, 128+D), dK' [256, 256+KD)
+  // TMEM columns: S^T, then dP^T [0,64); P^T (16-bit pairs) [64,96); dS^T (16-bit pairs) [96,128); dV [128,128+D);
+  // dK' [256,256+KD).  S^T and dP^T share their columns: dP^T is issued once the elementwise warps hold S^T in
+  // registers, which frees 64 columns for P^T / dS^T as TMEM-resident A operands of the accumulation products.
+  constexpr uint32_t TK_SD = 0, TK_P = 64, TK_DS = 96, TK_DV = 128, TK_DK = 256;
 
   if (warp == BWD_L_WARP) {
-    // =============================== copies: Q' and dO image tiles, lse / delta rows =============
+    // =============================== copies: resident K' / V, then Q' and dO image tiles ==========
     {   // resident K' (phase bias folded in) and V: two image tiles each, one 1 KB copy per chunk column and 64 rows
       const int64_t t0 = (int64_t)u * (int64_t)image_tiles(p.Nk) + j0 / BT;
       if (T_tiles > 0) {   // (a CTA without any visible query row would leave with these copies in flight)
-        if (lane == 0) mbar_expect_tx(&bars[BB_RESIDENT], BQ * KD * 2 + BQ * D * 2);
+        if (lane == 0) mbar_expect_tx(&bars[KB_RESIDENT], BQ * KD * 2 + BQ * D * 2);
         __syncwarp();
-        copy_resident_tiles(Ks, p.kimg + t0 * KBUF, KD / 8, &bars[BB_RESIDENT], lane);
-        copy_resident_tiles(Vs, p.vimg + t0 * VBUF, D / 8, &bars[BB_RESIDENT], lane);
+        copy_resident_tiles(Ks, p.kimg + t0 * KBUF, KD / 8, &bars[KB_RESIDENT], lane);
+        copy_resident_tiles(Vs, p.vimg + t0 * VBUF, D / 8, &bars[KB_RESIDENT], lane);
       }
     }
     if (lane == 0) {
       const int64_t qtiles = (int64_t)image_tiles(p.Nq);
       for (int j = 0; j < T_tiles; ++j) {
-        const int buf = j & 1, m0 = tile_start(j), h = tile_head(j);
+        const int sq = j % KQ_NST, sg = j % KG_NST, m0 = tile_start(j), h = tile_head(j);
         const int64_t t = (int64_t)(b * p.H + h) * qtiles + m0 / BT;
-        // buffer j & 1 was last read by the accumulation step of tile j-2
-        if (j >= 2 && !failed) failed = !mbar_wait(&bars[BB_ACC + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        if (j >= KQ_NST && !failed) failed = !mbar_wait(&bars[KB_ACCQ + sq], ((j - KQ_NST) / KQ_NST) & 1, WAIT_LIMIT);
         if (failed) break;
-        mbar_expect_tx(&bars[BB_FULL + buf], KBUF + VBUF + 2 * BT * 4);
-        bulk_load(Qb + buf * KBUF, p.qimg + t * KBUF, KBUF, &bars[BB_FULL + buf]);
-        bulk_load(rowstat + buf * 128, p.rowstat + t * 128, 2 * BT * 4, &bars[BB_FULL + buf]);
-        bulk_load(Gb + buf * VBUF, p.gimg + t * VBUF, VBUF, &bars[BB_FULL + buf]);
+        mbar_expect_tx(&bars[KB_QFULL + sq], KBUF + 2 * BT * 4);
+        bulk_load(Qb + sq * KBUF, p.qimg + t * KBUF, KBUF, &bars[KB_QFULL + sq]);
+        bulk_load(rowstat + sq * 128, p.rowstat + t * 128, 2 * BT * 4, &bars[KB_QFULL + sq]);
+        if (j >= KG_NST && !failed) failed = !mbar_wait(&bars[KB_ACCG + sg], ((j - KG_NST) / KG_NST) & 1, WAIT_LIMIT);
+        if (failed) break;
+        mbar_expect_tx(&bars[KB_GFULL + sg], VBUF);
+        bulk_load(Gb + sg * VBUF, p.gimg + t * VBUF, VBUF, &bars[KB_GFULL + sg]);
       }
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
   } else if (warp == BWD_M_WARP) {
-    // =============================== MMA issue ===================================================
+    // =============================== MMA issue: S^T = K' Q'^T, then dP^T = V dO^T =================
     if (lane == 0 && T_tiles > 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
       const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
-      auto issue_scores = [&](int jt) {
-        const int buf = jt & 1;
-        const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128), qb = smem_desc(qb_addr + buf * KBUF, BCS, 128);
-        const uint64_t va = smem_desc(vs_addr, BQ * 16, 128), gb = smem_desc(gb_addr + buf * VBUF, BCS, 128);
-        uint32_t alo = desc_lo(ka), blo = desc_lo(qb);
-        mma_ss_lh(tmem, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 0u);
-#pragma unroll 4
-        for (int ks = 1; ks < KSTEPS; ++ks) {
-          alo += (2 * BQ * 16) >> 4, blo += (2 * BCS) >> 4;
-          mma_ss_lh(tmem, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 1u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          mma_ss_lh(tmem + 64, desc_lo(va) + ks * ((2 * BQ * 16) >> 4), desc_hi(va), desc_lo(gb) + ks * ((2 * BCS) >> 4),
-                    desc_hi(gb), idesc_s, ks > 0);
-        mma_commit(&bars[BB_SCORES]);
-      };
-      if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
+      const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128), va = smem_desc(vs_addr, BQ * 16, 128);
+      if (!mbar_wait(&bars[KB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
       PH_DECL;
       for (int j = 0; j < T_tiles && !failed; ++j) {
-        failed = !mbar_wait(&bars[BB_FULL + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
+        const int sq = j % KQ_NST, sg = j % KG_NST;
+        failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);
         PH(0);
-        // the elementwise warps have copied the previous tile's scores out of TMEM
-        if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
+        // the elementwise warps hold dP^T of the previous tile in registers
+        if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_CONS_DP], (j - 1) & 1, WAIT_LIMIT);
         PH(1);
         fence_after_sync();
-        issue_scores(j);
+        {
+          const uint64_t qb = smem_desc(qb_addr + sq * KBUF, BCS, 128);
+          uint32_t alo = desc_lo(ka), blo = desc_lo(qb);
+          mma_ss_lh(tmem + TK_SD, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 0u);
+#pragma unroll 4
+          for (int ks = 1; ks < KSTEPS; ++ks) {
+            alo += (2 * BQ * 16) >> 4, blo += (2 * BCS) >> 4;
+            mma_ss_lh(tmem + TK_SD, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 1u);
+          }
+          mma_commit(&bars[KB_SDONE]);
+        }
         PH(2);
+        if (!failed) failed = !mbar_wait(&bars[KB_GFULL + sg], (j / KG_NST) & 1, WAIT_LIMIT);
+        PH(3);
+        // ... and S^T of this tile
+        if (!failed) failed = !mbar_wait(&bars[KB_CONS_S], j & 1, WAIT_LIMIT);
+        PH(4);
+        fence_after_sync();
+        {
+          const uint64_t gb = smem_desc(gb_addr + sg * VBUF, BCS, 128);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks)
+            mma_ss_lh(tmem + TK_SD, desc_lo(va) + ks * ((2 * BQ * 16) >> 4), desc_hi(va), desc_lo(gb) + ks * ((2 * BCS) >> 4),
+                      desc_hi(gb), idesc_s, ks > 0);
+          mma_commit(&bars[KB_DPDONE]);
+        }
+        PH(5);
       }
-      PH_PRINT("dkdv scores warp [wait full, wait consumed, issue]", T_tiles);
+      PH_PRINT("dkdv scores [wait q, wait cons_dp, issue S, wait g, wait cons_s, issue dP]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -123,27 +152,25 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     if (lane == 0 && T_tiles > 0) {
       const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
       const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
-      const uint32_t qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb), ps_addr = smem_u32(Ps), ds_addr = smem_u32(Ds);
-      const uint64_t pa = smem_desc(ps_addr, BQ * 16, 128), da = smem_desc(ds_addr, BQ * 16, 128);
-      PH_DECL;
+      const uint32_t qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
       for (int j = 0; j < T_tiles && !failed; ++j) {
-        const int buf = j & 1;
-        failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);
-        if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
-        PH(0);
+        const int sq = j % KQ_NST, sg = j % KG_NST;
+        failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);
+        if (!failed) failed = !mbar_wait(&bars[KB_GFULL + sg], (j / KG_NST) & 1, WAIT_LIMIT);
+        if (!failed) failed = !mbar_wait(&bars[KB_GRAD], j & 1, WAIT_LIMIT);
         fence_after_sync();
-        // the streamed tiles re-described as MN-major B operands
-        const uint64_t gd = smem_desc(gb_addr + buf * VBUF, 128, BCS), qd = smem_desc(qb_addr + buf * KBUF, 128, BCS);
+        // P^T / dS^T from TMEM; the streamed tiles re-described as MN-major B operands
+        const uint64_t gd = smem_desc(gb_addr + sg * VBUF, 128, BCS), qd = smem_desc(qb_addr + sq * KBUF, 128, BCS);
 #pragma unroll
         for (int ks = 0; ks < BT / 16; ++ks) {
-          const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u, astep = ks * ((2 * BQ * 16) >> 4), bstep = ks * ((2 * 128) >> 4);
-          mma_ss_lh(tmem + 256, desc_lo(da) + astep, desc_hi(da), desc_lo(qd) + bstep, desc_hi(qd), idesc_k, acc);
-          mma_ss_lh(tmem + 128, desc_lo(pa) + astep, desc_hi(pa), desc_lo(gd) + bstep, desc_hi(gd), idesc_v, acc);
+          const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u, bstep = ks * ((2 * 128) >> 4);
+          mma_ts_lh(tmem + TK_DK, tmem + TK_DS + ks * 8, desc_lo(qd) + bstep, desc_hi(qd), idesc_k, acc);
+          mma_ts_lh(tmem + TK_DV, tmem + TK_P + ks * 8, desc_lo(gd) + bstep, desc_hi(gd), idesc_v, acc);
         }
-        mma_commit(&bars[BB_ACC + buf]);   // every score product of this tile finished before its P^T / dS^T existed
-        PH(1);
+        // every score product of this tile finished before its P^T / dS^T existed
+        mma_commit(&bars[KB_ACCQ + sq]);
+        mma_commit(&bars[KB_ACCG + sg]);
       }
-      PH_PRINT("dkdv acc warp [wait grad, issue]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -164,70 +191,81 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   PH_DECL;
   for (int j = 0; j < T_tiles; ++j) {
-    const int buf = j & 1;
+    const int sq = j % KQ_NST;
     const int m0 = tile_start(j);
-    if (!failed) failed = !mbar_wait(&bars[BB_FULL + buf], (j >> 1) & 1, WAIT_LIMIT);   // orders the lse / delta read
-    if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
+    if (!failed) failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);   // orders the lse / delta read
+    if (!failed) failed = !mbar_wait(&bars[KB_SDONE], j & 1, WAIT_LIMIT);
     fence_after_sync();
     PH(0);
-    const float* st = rowstat + buf * 128 + half * 32;
+    const float* st = rowstat + sq * 128 + half * 32;
     // interior tile for this warp: every key row valid and (causal) every key at or before every query column;
     // out-of-range queries and rows without any visible key carry lse = +inf, which makes P exactly 0
     const int gj_hi = j0 + (warp & 3) * 32 + 31, gi_lo = m0 + half * 32;
     const bool interior = __all_sync(0xffffffffu, key_ok) && (!p.causal || gj_hi <= gi_lo);
-    uint32_t sv[32], dv[32];
-    tmem_ld32(tmem + lane_base + half * 32, sv);
-    tmem_ld32(tmem + lane_base + 64 + half * 32, dv);
+    uint32_t sv[32];
+    tmem_ld32(tmem + lane_base + TK_SD + half * 32, sv);
     tmem_ld_wait();
-    // every score of this tile is in registers: the next score products may overwrite them
+    // S^T of this tile is in registers: dP^T may overwrite it
     fence_before_sync();
-    warp_arrive(&bars[BB_CONSUMED], lane);
-    PH(1);
-    uint32_t pw[16], dw[16];   // P^T and dS^T of this thread's 32 query columns, packed in pairs
+    warp_arrive(&bars[KB_CONS_S], lane);
+    uint32_t pw[16];   // P^T of this thread's 32 query columns, packed in pairs; the fp32 values stay in sv
     // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
-    auto elementwise = [&](auto masked) {
+    auto probabilities = [&](auto masked) {
 #pragma unroll
       for (int c4 = 0; c4 < 8; ++c4) {
-        const float4 l4 = *reinterpret_cast<const float4*>(st + c4 * 4), d4 = *reinterpret_cast<const float4*>(st + 64 + c4 * 4);
-        const float l2v[4] = {l4.x, l4.y, l4.z, l4.w}, dlv[4] = {d4.x, d4.y, d4.z, d4.w};
+        const float4 l4 = *reinterpret_cast<const float4*>(st + c4 * 4);
+        const float l2v[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const int cl = c4 * 4 + e * 2 + t;   // query column within the thread's half
-            float pr = ex2_approx(fmaf(__uint_as_float(sv[cl]), p.scale_log2, -l2v[e * 2 + t]));
-            if (decltype(masked)::value) pr = (key_ok && (!p.causal || gj <= gi_lo + cl)) ? pr : 0.f;
-            pv[t] = pr;
-            dsv[t] = pr * (__uint_as_float(dv[cl]) - dlv[e * 2 + t]) * p.scale;
-          }
-          pw[c4 * 2 + e] = pack2<T>(pv[0], pv[1]);
-          dw[c4 * 2 + e] = pack2<T>(dsv[0], dsv[1]);
+        for (int t = 0; t < 4; ++t) {
+          const int cl = c4 * 4 + t;   // query column within the thread's half
+          float pr = ex2_approx(fmaf(__uint_as_float(sv[cl]), p.scale_log2, -l2v[t]));
+          if (decltype(masked)::value) pr = (key_ok && (!p.causal || gj <= gi_lo + cl)) ? pr : 0.f;
+          sv[cl] = __float_as_uint(pr);
         }
+        pw[c4 * 2] = pack2<T>(__uint_as_float(sv[c4 * 4]), __uint_as_float(sv[c4 * 4 + 1]));
+        pw[c4 * 2 + 1] = pack2<T>(__uint_as_float(sv[c4 * 4 + 2]), __uint_as_float(sv[c4 * 4 + 3]));
       }
     };
-    if (interior) elementwise(std::false_type());
-    else elementwise(std::true_type());
+    if (interior) probabilities(std::false_type());
+    else probabilities(std::true_type());
+    // the P^T / dS^T columns were read by the accumulation step of tile j-1
+    PH(1);
+    if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_ACCG + (j - 1) % KG_NST], ((j - 1) / KG_NST) & 1, WAIT_LIMIT);
     PH(2);
-    // the P^T / dS^T tiles in shared memory were read by the accumulation step of tile j-1
-    if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_ACC + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+    tmem_st16(tmem + lane_base + TK_P + half * 16, pw);
+    if (!failed) failed = !mbar_wait(&bars[KB_DPDONE], j & 1, WAIT_LIMIT);
+    fence_after_sync();
     PH(3);
+    uint32_t dv[32];
+    tmem_ld32(tmem + lane_base + TK_SD + half * 32, dv);
+    tmem_ld_wait();
+    // dP^T of this tile is in registers: the next S^T may overwrite it
+    fence_before_sync();
+    warp_arrive(&bars[KB_CONS_DP], lane);
+    uint32_t dw[16];
 #pragma unroll
-    for (int c8 = 0; c8 < 4; ++c8) {
-      const int chunk = half * 4 + c8;
-      *reinterpret_cast<uint4*>(Ps + chunk * (BQ * 16) + row * 16) = make_uint4(pw[c8 * 4], pw[c8 * 4 + 1], pw[c8 * 4 + 2], pw[c8 * 4 + 3]);
-      *reinterpret_cast<uint4*>(Ds + chunk * (BQ * 16) + row * 16) = make_uint4(dw[c8 * 4], dw[c8 * 4 + 1], dw[c8 * 4 + 2], dw[c8 * 4 + 3]);
+    for (int c4 = 0; c4 < 8; ++c4) {
+      const float4 d4 = *reinterpret_cast<const float4*>(st + 64 + c4 * 4);
+      const float dlv[4] = {d4.x, d4.y, d4.z, d4.w};
+      float ds[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        ds[t] = __uint_as_float(sv[c4 * 4 + t]) * (__uint_as_float(dv[c4 * 4 + t]) - dlv[t]) * p.scale;
+      dw[c4 * 2] = pack2<T>(ds[0], ds[1]);
+      dw[c4 * 2 + 1] = pack2<T>(ds[2], ds[3]);
     }
-    fence_async_smem();
-    warp_arrive(&bars[BB_GRAD], lane);
+    tmem_st16(tmem + lane_base + TK_DS + half * 16, dw);
+    tmem_st_wait();
+    fence_before_sync();
+    warp_arrive(&bars[KB_GRAD], lane);
     PH(4);
   }
-  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [wait scores, ld+arrive, math, wait acc, st+arrive]", T_tiles);
+  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [wait S, ld+P math, wait acc, st P + wait dP, ld + dS + st]", T_tiles);
   PH(5);
 
   // ---- epilogue ---------------------------------------------------------------------------------
   if (T_tiles > 0 && !failed)
-    failed = !mbar_wait(&bars[BB_ACC + ((T_tiles - 1) & 1)], ((T_tiles - 1) >> 1) & 1, WAIT_LIMIT);
+    failed = !mbar_wait(&bars[KB_ACCG + (T_tiles - 1) % KG_NST], ((T_tiles - 1) / KG_NST) & 1, WAIT_LIMIT);
   fence_after_sync();
   asm volatile("bar.sync 1, 256;" ::: "memory");   // every MMA is done: the streamed buffers can be reused
   // Everything below reuses dead shared memory: the streamed buffers hold the bias trig and the per-row key-phase
@@ -244,7 +282,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   asm volatile("bar.sync 1, 256;" ::: "memory");
   {
     constexpr int HW = D / 2;
-    const uint32_t accv = tmem + lane_base + 128, acck = tmem + lane_base + 256;
+    const uint32_t accv = tmem + lane_base + TK_DV, acck = tmem + lane_base + TK_DK;
     const T* krow = kbase + (int64_t)gj * p.sk.n;
     const int64_t trow = (int64_t)gj * p.r;   // row of the fp32 cos / sin tables
     float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + hk * p.sdf.h + (int64_t)gj * p.sdf.n : nullptr;
@@ -335,7 +373,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     }
   }
   PH(6);
-  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [..., 5: print, 6: epilogue total / tiles]", T_tiles);
+  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [..., 6: epilogue total / tiles]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier
@@ -452,7 +490,8 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   if (!p.status) return cudaErrorInvalidSymbol;
   const size_t stage = (size_t)BT * KD * 2 + (size_t)BT * D * 2;
   size_t smem_q = (size_t)BQ * KD * 2 + DQ_NST * stage + (BB_COUNT + 1) * 8 + 16;
-  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + 2 * stage + 2 * BQ * BT * 2 + 256 * 4 + (BB_COUNT + 1) * 8 + 16 + 16;
+  size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + KQ_NST * (size_t)BT * KD * 2 + KG_NST * (size_t)BT * D * 2 + KQ_NST * 512 +
+                  (KB_COUNT + 1) * 8 + 16;
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;
