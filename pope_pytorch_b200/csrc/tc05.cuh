@@ -69,6 +69,13 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
                : "memory");
 }
 
+// Ask L2 to fetch the 128-byte lines covering [p, p + bytes) (no register, no completion to wait for).
+__device__ __forceinline__ void prefetch_l2(const void* p, int bytes) {
+  const char* c = static_cast<const char*>(p);
+  for (int o = 0; o < bytes; o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(c + o));
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(c + bytes - 1));
+}
+
 // ---- fences ----------------------------------------------------------------------------------
 // generic-proxy shared-memory writes -> visible to the async proxy (tensor core / TMA reads)
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

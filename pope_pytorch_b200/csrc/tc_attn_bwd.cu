@@ -234,6 +234,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   PH(0);
   for (int j = 0; j < T_tiles; ++j) {
     const int n0 = tile_start(j);
+    if (j == max(T_tiles - 3, 0) && gi < p.Nq) {
+      // The epilogue reads this thread's half of the q row and of its cos / sin table rows, which have long left
+      // L2 by then (a DRAM round trip per 16 features was 4.7 K clk of the epilogue's 19 K): fetch them now.
+      prefetch_l2((const T*)p.q + b * p.sq.b + h * p.sq.h + (int64_t)gi * p.sq.n + half * (D / 2), D);
+      if (half * (D / 2) < p.r) {
+        const int nf = min(D / 2, p.r - half * (D / 2)) * 4;
+        prefetch_l2(p.ctab + (int64_t)(qoff + gi) * p.r + half * (D / 2), nf);
+        prefetch_l2(p.stab + (int64_t)(qoff + gi) * p.r + half * (D / 2), nf);
+      }
+    }
     // key visibility of this thread's 32-key half (key-padding mask, ragged end): the same for every row
     uint32_t vis = 0xffffffffu;
     if (maskb || n0 + BT > p.Nk) {
@@ -285,6 +295,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
   if (!failed) failed = !mbar_wait(&bars[BB_ACC + (T_tiles - 1) % DQ_NST], ((T_tiles - 1) / DQ_NST) & 1, WAIT_LIMIT);
   fence_after_sync();
+  PH(2);
   {
     constexpr int HW = D / 2;  // features handled by this thread: [half*HW, half*HW + HW)
     const uint32_t acc = tmem + lane_base + TC_DQ;
@@ -300,6 +311,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       const bool rot = cbase < p.r;  // r is a multiple of 16: the 16-wide group is rotated as a whole
       if (rot) tmem_ld16(acc + D + cbase, gs);
       tmem_ld_wait();
+      PH(3);
       if (gi < p.Nq) {
         uint32_t outw[8];
         if (rot) {
@@ -331,12 +343,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         }
         // (staging the rows through shared memory for coalesced stores was measured slower here: 839 against 809 us)
         *reinterpret_cast<uint4*>(dqrow + cbase) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+        PH(4);
         *reinterpret_cast<uint4*>(dqrow + cbase + 8) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
       }
+      PH(5);
     }
   }
-  PH(2);
-  if (tid == 0) PH_PRINT("dq cta totals / tiles [prologue, loop, epilogue]", T_tiles);
+  PH(6);
+  if (tid == 0) PH_PRINT("dq cta totals / tiles [prologue, loop, wait last acc, tmem ld, loads+math, stores, tail]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier

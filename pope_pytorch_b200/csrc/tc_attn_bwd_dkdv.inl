@@ -193,6 +193,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   for (int j = 0; j < T_tiles; ++j) {
     const int sq = j % KQ_NST;
     const int m0 = tile_start(j);
+    if (j == max(T_tiles - 3, 0) && gj < p.Nk) {
+      // the epilogue reads this thread's half of the k row and of its cos / sin table rows: have L2 fetch them now
+      prefetch_l2(kbase + (int64_t)gj * p.sk.n + half * (D / 2), D);
+      if (half * (D / 2) < p.r) {
+        const int nf = min(D / 2, p.r - half * (D / 2)) * 4;
+        prefetch_l2(p.ctab + (int64_t)gj * p.r + half * (D / 2), nf);
+        prefetch_l2(p.stab + (int64_t)gj * p.r + half * (D / 2), nf);
+      }
+    }
     if (!failed) failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);   // orders the lse / delta read
     if (!failed) failed = !mbar_wait(&bars[KB_SDONE], j & 1, WAIT_LIMIT);
     fence_after_sync();
