@@ -203,7 +203,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   }
 
   // =============================== elementwise warps ================================================
-  PH_DECL;
   const int row = tid & 127, half = tid >> 7;           // thread = (query row, 32-key half)
   const int gi = i0 + row;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -231,19 +230,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   const float lse2 = gi < p.Nq ? p.lse[(int64_t)u * p.Nq + gi] * LOG2E : -CUDART_INF_F;
   const float lse_use = lse2 == -CUDART_INF_F ? 0.f : lse2;
   const float dlt = gi < p.Nq ? p.delta[(int64_t)u * p.Nq + gi] : 0.f;
-  PH(0);
   for (int j = 0; j < T_tiles; ++j) {
     const int n0 = tile_start(j);
-    if (j == max(T_tiles - 3, 0) && gi < p.Nq) {
-      // The epilogue reads this thread's half of the q row and of its cos / sin table rows, which have long left
-      // L2 by then (a DRAM round trip per 16 features was 4.7 K clk of the epilogue's 19 K): fetch them now.
-      prefetch_l2((const T*)p.q + b * p.sq.b + h * p.sq.h + (int64_t)gi * p.sq.n + half * (D / 2), D);
-      if (half * (D / 2) < p.r) {
-        const int nf = min(D / 2, p.r - half * (D / 2)) * 4;
-        prefetch_l2(p.ctab + (int64_t)(qoff + gi) * p.r + half * (D / 2), nf);
-        prefetch_l2(p.stab + (int64_t)(qoff + gi) * p.r + half * (D / 2), nf);
-      }
-    }
     // key visibility of this thread's 32-key half (key-padding mask, ragged end): the same for every row
     uint32_t vis = 0xffffffffu;
     if (maskb || n0 + BT > p.Nk) {
@@ -290,19 +278,18 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     fence_before_sync();
     warp_arrive(&bars[BB_GRAD], lane);
   }
-
-  PH(1);
   // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
+  // TMEM hands every thread one ROW of dQ', but q, the phase tables and dq are row-major in global memory: read by
+  // rows, a warp-wide 16-byte access touches 32 different lines.  So the accumulator is transposed through the (now
+  // dead) shared memory first, and the chain rule runs with consecutive threads on consecutive 8-feature groups of
+  // one row: every global access is a contiguous 256 or 512 bytes per warp.
   if (!failed) failed = !mbar_wait(&bars[BB_ACC + (T_tiles - 1) % DQ_NST], ((T_tiles - 1) / DQ_NST) & 1, WAIT_LIMIT);
   fence_after_sync();
-  PH(2);
   {
-    constexpr int HW = D / 2;  // features handled by this thread: [half*HW, half*HW + HW)
+    const int ASTR = KD * 4 + 16;            // bytes of one staged fp32 row (16 bytes of padding: conflict-free)
+    uint8_t* accs = smem;                    // [128 rows][KD fp32]: 133 KB at KD = 256, over Q' and the stages
+    constexpr int HW = D / 2;                // columns of each part copied by this thread: [half*HW, half*HW + HW)
     const uint32_t acc = tmem + lane_base + TC_DQ;
-    const T* qrow = (const T*)p.q + b * p.sq.b + h * p.sq.h + (int64_t)gi * p.sq.n;
-    T* dqrow = (T*)p.dq + b * p.sdq.b + h * p.sdq.h + (int64_t)gi * p.sdq.n;
-    const int64_t trow = (int64_t)(qoff + gi) * p.r;   // row of the fp32 cos / sin tables
-    float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + h * p.sdf.h + (int64_t)(qoff + gi) * p.sdf.n : nullptr;
 #pragma unroll
     for (int c0 = 0; c0 < HW; c0 += 16) {
       const int cbase = half * HW + c0;
@@ -311,46 +298,73 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       const bool rot = cbase < p.r;  // r is a multiple of 16: the 16-wide group is rotated as a whole
       if (rot) tmem_ld16(acc + D + cbase, gs);
       tmem_ld_wait();
-      PH(3);
-      if (gi < p.Nq) {
-        uint32_t outw[8];
-        if (rot) {
-          const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(qrow + cbase)), q1 = __ldg(reinterpret_cast<const uint4*>(qrow + cbase + 8));
-          const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-          float cf[16], sf[16];
+      uint4* dc = reinterpret_cast<uint4*>(accs + row * ASTR + cbase * 4);
 #pragma unroll
-          for (int e4 = 0; e4 < 4; ++e4) {
-            const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.ctab + trow + cbase) + e4);
-            const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.stab + trow + cbase) + e4);
-            cf[e4 * 4] = c4.x, cf[e4 * 4 + 1] = c4.y, cf[e4 * 4 + 2] = c4.z, cf[e4 * 4 + 3] = c4.w;
-            sf[e4 * 4] = s4.x, sf[e4 * 4 + 1] = s4.y, sf[e4 * 4 + 2] = s4.z, sf[e4 * 4 + 3] = s4.w;
-          }
+      for (int e = 0; e < 4; ++e) dc[e] = make_uint4(gc[4 * e], gc[4 * e + 1], gc[4 * e + 2], gc[4 * e + 3]);
+      if (rot) {
+        uint4* dsn = reinterpret_cast<uint4*>(accs + row * ASTR + (D + cbase) * 4);
 #pragma unroll
-          for (int e = 0; e < 16; e += 2) {
+        for (int e = 0; e < 4; ++e) dsn[e] = make_uint4(gs[4 * e], gs[4 * e + 1], gs[4 * e + 2], gs[4 * e + 3]);
+      }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    constexpr int GPR = D / 8;               // 8-feature groups per row
+    const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
+    T* dqbase = (T*)p.dq + b * p.sdq.b + h * p.sdq.h;
+    // Items (row, 8-feature group) in batches of EB per thread: all global loads of a batch are issued before its
+    // arithmetic.  (They remain the bulk of the epilogue: ~11 K of its ~15 K clk with them, 3 K without.)
+    constexpr int NITEM = BQ * GPR / 256, EB = NITEM % 4 == 0 ? 4 : (NITEM % 3 == 0 ? 3 : 2);
+    static_assert(NITEM % EB == 0, "items per thread must split into whole batches");
+#pragma unroll 1
+    for (int i0b = 0; i0b < NITEM; i0b += EB) {
+      uint4 qv[EB];
+      float4 tc0[EB], tc1[EB], ts0[EB], ts1[EB];
+#pragma unroll
+      for (int k = 0; k < EB; ++k) {
+        const int idx = tid + (i0b + k) * 256, rr = idx / GPR, cb = (idx - rr * GPR) * 8, gr = i0 + rr;
+        qv[k] = make_uint4(0, 0, 0, 0);
+        tc0[k] = tc1[k] = ts0[k] = ts1[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gr < p.Nq && cb < p.r) {   // r is a multiple of 16: an 8-wide group is rotated as a whole
+          qv[k] = __ldg(reinterpret_cast<const uint4*>(qbase + (int64_t)gr * p.sq.n + cb));
+          const int64_t trow = (int64_t)(qoff + gr) * p.r + cb;   // fp32 cos / sin tables
+          tc0[k] = __ldg(reinterpret_cast<const float4*>(p.ctab + trow)), tc1[k] = __ldg(reinterpret_cast<const float4*>(p.ctab + trow) + 1);
+          ts0[k] = __ldg(reinterpret_cast<const float4*>(p.stab + trow)), ts1[k] = __ldg(reinterpret_cast<const float4*>(p.stab + trow) + 1);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < EB; ++k) {
+        const int idx = tid + (i0b + k) * 256, rr = idx / GPR, cb = (idx - rr * GPR) * 8, gr = i0 + rr;
+        if (gr >= p.Nq) continue;
+        const float4 a0 = *reinterpret_cast<const float4*>(accs + rr * ASTR + cb * 4);
+        const float4 a1 = *reinterpret_cast<const float4*>(accs + rr * ASTR + cb * 4 + 16);
+        const float gcv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        uint32_t outw[4];
+        if (cb < p.r) {
+          const float4 b0 = *reinterpret_cast<const float4*>(accs + rr * ASTR + (D + cb) * 4);
+          const float4 b1 = *reinterpret_cast<const float4*>(accs + rr * ASTR + (D + cb) * 4 + 16);
+          const float gsv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+          const uint32_t qw[4] = {qv[k].x, qv[k].y, qv[k].z, qv[k].w};
+          const float cf[8] = {tc0[k].x, tc0[k].y, tc0[k].z, tc0[k].w, tc1[k].x, tc1[k].y, tc1[k].z, tc1[k].w};
+          const float sf[8] = {ts0[k].x, ts0[k].y, ts0[k].z, ts0[k].w, ts1[k].x, ts1[k].y, ts1[k].z, ts1[k].w};
+          float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + h * p.sdf.h + (int64_t)(qoff + gr) * p.sdf.n + cb : nullptr;
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
             const float2 x = unpack2<T>(qw[e >> 1]);
-            const float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
-            const float h0 = __uint_as_float(gs[e]), h1 = __uint_as_float(gs[e + 1]);
             if (dfrow) {
-              atomicAdd(dfrow + cbase + e, softplus_fast(x.x) * (h0 * cf[e] - g0 * sf[e]));
-              atomicAdd(dfrow + cbase + e + 1, softplus_fast(x.y) * (h1 * cf[e + 1] - g1 * sf[e + 1]));
+              atomicAdd(dfrow + e, softplus_fast(x.x) * (gsv[e] * cf[e] - gcv[e] * sf[e]));
+              atomicAdd(dfrow + e + 1, softplus_fast(x.y) * (gsv[e + 1] * cf[e + 1] - gcv[e + 1] * sf[e + 1]));
             }
-            outw[e >> 1] = pack2<T>((g0 * cf[e] + h0 * sf[e]) * sigmoid_fast(x.x),
-                                    (g1 * cf[e + 1] + h1 * sf[e + 1]) * sigmoid_fast(x.y));
+            outw[e >> 1] = pack2<T>((gcv[e] * cf[e] + gsv[e] * sf[e]) * sigmoid_fast(x.x),
+                                    (gcv[e + 1] * cf[e + 1] + gsv[e + 1] * sf[e + 1]) * sigmoid_fast(x.y));
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 16; e += 2) outw[e >> 1] = pack2<T>(__uint_as_float(gc[e]), __uint_as_float(gc[e + 1]));
+          for (int e = 0; e < 8; e += 2) outw[e >> 1] = pack2<T>(gcv[e], gcv[e + 1]);
         }
-        // (staging the rows through shared memory for coalesced stores was measured slower here: 839 against 809 us)
-        *reinterpret_cast<uint4*>(dqrow + cbase) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
-        PH(4);
-        *reinterpret_cast<uint4*>(dqrow + cbase + 8) = make_uint4(outw[4], outw[5], outw[6], outw[7]);
+        *reinterpret_cast<uint4*>(dqbase + (int64_t)gr * p.sdq.n + cb) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
       }
-      PH(5);
     }
   }
-  PH(6);
-  if (tid == 0) PH_PRINT("dq cta totals / tiles [prologue, loop, wait last acc, tmem ld, loads+math, stores, tail]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier

@@ -106,14 +106,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
       const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128), va = smem_desc(vs_addr, BQ * 16, 128);
       if (!mbar_wait(&bars[KB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
-      PH_DECL;
       for (int j = 0; j < T_tiles && !failed; ++j) {
         const int sq = j % KQ_NST, sg = j % KG_NST;
         failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);
-        PH(0);
         // the elementwise warps hold dP^T of the previous tile in registers
         if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_CONS_DP], (j - 1) & 1, WAIT_LIMIT);
-        PH(1);
         fence_after_sync();
         {
           const uint64_t qb = smem_desc(qb_addr + sq * KBUF, BCS, 128);
@@ -126,12 +123,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
           }
           mma_commit(&bars[KB_SDONE]);
         }
-        PH(2);
         if (!failed) failed = !mbar_wait(&bars[KB_GFULL + sg], (j / KG_NST) & 1, WAIT_LIMIT);
-        PH(3);
         // ... and S^T of this tile
         if (!failed) failed = !mbar_wait(&bars[KB_CONS_S], j & 1, WAIT_LIMIT);
-        PH(4);
         fence_after_sync();
         {
           const uint64_t gb = smem_desc(gb_addr + sg * VBUF, BCS, 128);
@@ -141,9 +135,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
                       desc_hi(gb), idesc_s, ks > 0);
           mma_commit(&bars[KB_DPDONE]);
         }
-        PH(5);
       }
-      PH_PRINT("dkdv scores [wait q, wait cons_dp, issue S, wait g, wait cons_s, issue dP]", T_tiles);
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
@@ -189,7 +181,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const int gj = j0 + row;
   const bool key_ok = gj < p.Nk && (!maskb || maskb[(int64_t)gj * p.msn] != 0);
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  PH_DECL;
   for (int j = 0; j < T_tiles; ++j) {
     const int sq = j % KQ_NST;
     const int m0 = tile_start(j);
@@ -205,7 +196,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     if (!failed) failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);   // orders the lse / delta read
     if (!failed) failed = !mbar_wait(&bars[KB_SDONE], j & 1, WAIT_LIMIT);
     fence_after_sync();
-    PH(0);
     const float* st = rowstat + sq * 128 + half * 32;
     // interior tile for this warp: every key row valid and (causal) every key at or before every query column;
     // out-of-range queries and rows without any visible key carry lse = +inf, which makes P exactly 0
@@ -238,13 +228,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     if (interior) probabilities(std::false_type());
     else probabilities(std::true_type());
     // the P^T / dS^T columns were read by the accumulation step of tile j-1
-    PH(1);
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_ACCG + (j - 1) % KG_NST], ((j - 1) / KG_NST) & 1, WAIT_LIMIT);
-    PH(2);
     tmem_st16(tmem + lane_base + TK_P + half * 16, pw);
     if (!failed) failed = !mbar_wait(&bars[KB_DPDONE], j & 1, WAIT_LIMIT);
     fence_after_sync();
-    PH(3);
     uint32_t dv[32];
     tmem_ld32(tmem + lane_base + TK_SD + half * 32, dv);
     tmem_ld_wait();
@@ -267,10 +254,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     tmem_st_wait();
     fence_before_sync();
     warp_arrive(&bars[KB_GRAD], lane);
-    PH(4);
   }
-  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [wait S, ld+P math, wait acc, st P + wait dP, ld + dS + st]", T_tiles);
-  PH(5);
 
   // ---- epilogue ---------------------------------------------------------------------------------
   if (T_tiles > 0 && !failed)
@@ -381,8 +365,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       }
     }
   }
-  PH(6);
-  if (tid == 0 && T_tiles > 0) PH_PRINT("dkdv elem [..., 6: epilogue total / tiles]", T_tiles);
   if (failed) atomicOr(p.status, 1u);
   fence_before_sync();
   __syncthreads();   // the issuing warp frees the tensor memory after this barrier
