@@ -1,18 +1,17 @@
 // PoPE flash-attention backward on the Blackwell tensor cores (tcgen05 + TMEM), sm_100a only.
 //
 // Two kernels, no atomics on dq / dk / dv (deterministic):
-//   dq kernel   : a CTA keeps 128 query rows resident (Q' expanded exactly once, dO) and
-//                 streams 64-key tiles:   S = Q' K'^T, dP = dO V^T  ->  dS  ->  dQ' += dS K'
-//   dkdv kernel : a CTA keeps 128 key rows resident (K' expanded exactly once, V) and streams
-//                 64-query tiles: S^T = K' Q'^T, dP^T = V dO^T -> P^T, dS^T ->
-//                 dV += P^T dO,  dK' += dS^T Q'
+//   dq kernel   : a CTA keeps 128 query rows resident (Q' in shared memory, dO in TMEM) and streams 64-key
+//                 tiles through three stages:   S = Q' K'^T, dP = dO V^T  ->  dS  ->  dQ' += dS K'
+//   dkdv kernel : a CTA keeps 128 key rows resident (K', V) and streams 64-query tiles:
+//                 S^T = K' Q'^T -> P^T, then dP^T = V dO^T (same TMEM columns) -> dS^T;
+//                 dV += P^T dO,  dK' += dS^T Q'  with P^T / dS^T read from TMEM
 // with P = exp(S*scale - lse), dS = P (dP - delta) scale
 // (PoPE_pytorch/triton_pope_flash_attn.py:190-199) and the chain rule through the transform in
-// the epilogue (:202-210).  Accumulators live in TMEM (dq: 64+64+32+KD columns; dkdv:
-// 64+64+D+KD = 512 columns at d = r = 128); the streamed operand is expanded in registers from
-// the raw rows and a (cos, sin) phase table, the per-head phase bias being folded into whichever
-// operand is resident.  A streamed tile in shared memory serves two MMAs: as the K-major B
-// operand of the score product and, re-described as MN-major, as the B operand of the gradient
+// the epilogue (:202-210).  Every operand tile -- expanded Q' and K', re-laid V and dO -- comes from the images
+// that a pre-pass builds once per call (tc_expand.cu) and reaches shared memory by cp.async.bulk; the per-head
+// phase bias of the keys is part of the K' images.  A streamed tile in shared memory serves two MMAs: as the
+// K-major B operand of the score product and, re-described as MN-major, as the B operand of the gradient
 // product -- the 8x16-byte core-matrix layout is symmetric under that exchange.
 #include <type_traits>
 

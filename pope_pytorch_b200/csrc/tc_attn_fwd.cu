@@ -1,21 +1,18 @@
 // PoPE flash-attention forward on the Blackwell tensor cores (tcgen05 + TMEM), sm_100a only.
 //
-// One CTA owns 256 query rows (two 128-row MMA tiles) of one (batch, head) unit and sweeps
-// the keys 64 at a time.  Per key tile:
-//   1. all 256 threads turn the raw K rows into the expanded operand K' = [a cos | pass | a sin]
-//      in registers and write it to shared memory in the tensor core's K-major layout
-//      (double buffered); V is staged MN-major; nothing expanded ever goes to global memory
-//   2. one thread issues tcgen05.mma  S_t = Q'_t K'^T  into TMEM (t = 0,1)
-//   3. every thread owns one query row: it pulls its 64 scores out of TMEM, applies the
-//      causal / key-padding masks, keeps the running max and sum, and writes P (bf16) back
-//      into TMEM over the scores
-//   4. one thread issues  O_t += P_t V  with P read straight from TMEM
-// The MMAs of step 2 run while the threads do step 3 of the previous tile, those of step 4
-// while they do step 1 of the next.
+// One CTA owns 256 query rows (two 128-row MMA tiles) of one (batch, head) unit and sweeps the keys 64 at a
+// time.  The expanded operands Q' and K' = [a cos | pass | a sin] come from the operand images that a pre-pass
+// builds once per call (tc_expand.cu), so the main loop contains no transform work:
+//   loader warp   : Q' (resident, 2 x 2 image tiles) and one K' image tile per step by cp.async.bulk; the V tile
+//                   of the step by cp.async.bulk.tensor boxes straight from the caller's strided V
+//   score warp    : one lane issues tcgen05.mma  S_t = Q'_t K'^T  into TMEM (t = 0, 1)
+//   softmax warps : every thread owns one query row: it pulls its 64 scores out of TMEM, applies the causal /
+//                   key-padding masks, keeps the running max and sum, and writes P (16-bit) back into TMEM over
+//                   the scores
+//   PV warp       : one lane issues  O_t += P_t V  with P read straight from TMEM
+// All hand-offs are mbarriers (copy completion by transaction bytes, MMA completion by tcgen05.commit).
 //
-// The per-head phase bias is folded into the QUERY phase (cos(fq - fk - b) is symmetric in
-// where b is applied), so the key-side transform needs only a per-position table of
-// (cos f, sin f) that a small pre-pass builds once per call in the caller's workspace.
+// The per-head phase bias of the keys is part of the K' images.
 //
 // Semantics follow PoPE_pytorch/triton_pope_flash_attn.py:23-117 (top-left causal mask,
 // bottom-right positions, mask True = keep, zero output and -inf LSE for empty rows).
@@ -30,36 +27,9 @@ namespace pope {
 
 __device__ unsigned int g_tc_status = 0;  // sticky: bit 0 = a bounded wait gave up
 
-// Optional phase timers (compile with -DPOPE_TC_PROFILE): clock64 deltas of warp 0 / lane 0 of every
-// CTA summed per phase.  [0] prologue [1] wait PV [2] stage [3] sync A [4] wait S [5] softmax [6] sync B
-// [7] epilogue [8] CTA count [9] tiles
-#ifdef POPE_TC_PROFILE
-__device__ unsigned long long g_tc_prof[16];
-#define PROF_DECL long long _t0 = clock64(), _t1; unsigned long long _acc[16] = {}
-#define PROF(i) do { _t1 = clock64(); _acc[i] += (unsigned long long)(_t1 - _t0); _t0 = _t1; } while (0)
-#define PROF_FLUSH(lo, hi) do { for (int _i = lo; _i < hi; ++_i) atomicAdd(&g_tc_prof[_i], _acc[_i]); } while (0)
-#define PROF_COUNT(i, n) atomicAdd(&g_tc_prof[i], (unsigned long long)(n))
-#else
-#define PROF_DECL
-#define PROF(i)
-#define PROF_FLUSH(lo, hi)
-#define PROF_COUNT(i, n)
-#endif
-
 unsigned int* tc_status_ptr() {
   void* p = nullptr;
   return cudaGetSymbolAddress(&p, g_tc_status) == cudaSuccess ? static_cast<unsigned int*>(p) : nullptr;
-}
-
-// copies the phase timers (zeros unless built with POPE_TC_PROFILE) and clears them
-void tc_read_profile(unsigned long long* out16) {
-#ifdef POPE_TC_PROFILE
-  cudaMemcpyFromSymbol(out16, g_tc_prof, 16 * sizeof(unsigned long long));
-  unsigned long long z[16] = {};
-  cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z));
-#else
-  for (int i = 0; i < 16; ++i) out16[i] = 0;
-#endif
 }
 
 unsigned int tc_read_status() {
@@ -517,10 +487,6 @@ static cudaError_t static_scratch_address(void** out) {
 }
 
 }  // namespace pope
-
-extern "C" __attribute__((visibility("default"))) void pope_b200_debug_profile(unsigned long long* out16) {
-  pope::tc_read_profile(out16);
-}
 
 extern "C" int pope_b200_attn_fwd_noalloc(const PopeAttnArgs* args, void* stream) {
   using namespace pope;
