@@ -5,8 +5,10 @@ namespace pope {
 // resident K' and V once P^T and dS^T live in TMEM, and the Q' tile is the one whose copy is needed first.
 enum { KB_QFULL = 0,     // [3] Q' tile j (and its lse / delta rows) has landed in stage j % 3
        KB_GFULL = 3,     // [2] dO tile j has landed in stage j % 2
-       KB_ACCQ = 5,      // [3] tcgen05.commit: accumulation of tile j finished (slot j % 3): its Q' stage is free
-       KB_ACCG = 8,      // [2] the same event in slot j % 2: the dO stage and the P^T / dS^T columns are free
+       KB_ACCQ = 5,      // [3] tcgen05.commit: dK' += dS^T Q' of tile j finished (slot j % 3): its Q' stage and the dS^T
+                         //     columns are free
+       KB_ACCG = 8,      // [2] tcgen05.commit: dV += P^T dO of tile j finished (slot j % 2): its dO stage and the P^T
+                         //     columns are free
        KB_SDONE = 10,    // tcgen05.commit: S^T of the current tile is in TMEM
        KB_DPDONE = 11,   // tcgen05.commit: dP^T of the current tile is in TMEM (same columns as S^T)
        KB_CONS_S = 12,   // 8 warps: S^T copied to registers, dP^T may overwrite it
@@ -100,19 +102,26 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     }
     __syncwarp();
   } else if (warp == BWD_M_WARP) {
-    // =============================== MMA issue: S^T = K' Q'^T, then dP^T = V dO^T =================
+    // =============================== MMA issue ===================================================
+    // One thread issues everything, in the order the tensor pipe should execute it: the accumulation products of
+    // tile j-1 fill the two gaps in which the elementwise warps copy S^T(j), resp. dP^T(j), out of TMEM.
+    //   S^T(j) | dV(j-1) | dP^T(j) | dK'(j-1)
+    // (The second issuing warp of this CTA shape stays idle in this kernel: issued from it, the accumulation
+    // products ran ahead of S^T(j) in the pipe and delayed the critical score -> elementwise -> score chain.)
     if (lane == 0 && T_tiles > 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
+      const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
+      const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
       const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
       const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128), va = smem_desc(vs_addr, BQ * 16, 128);
       if (!mbar_wait(&bars[KB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
-      for (int j = 0; j < T_tiles && !failed; ++j) {
-        const int sq = j % KQ_NST, sg = j % KG_NST;
-        failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);
-        // the elementwise warps hold dP^T of the previous tile in registers
-        if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_CONS_DP], (j - 1) & 1, WAIT_LIMIT);
-        fence_after_sync();
-        {
+      for (int j = 0; j <= T_tiles && !failed; ++j) {
+        const int sq = j % KQ_NST, sg = j % KG_NST, pq = (j + KQ_NST - 1) % KQ_NST, pg = (j + KG_NST - 1) % KG_NST;
+        if (j < T_tiles) {
+          failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);
+          // the elementwise warps hold dP^T of the previous tile in registers
+          if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_CONS_DP], (j - 1) & 1, WAIT_LIMIT);
+          fence_after_sync();
           const uint64_t qb = smem_desc(qb_addr + sq * KBUF, BCS, 128);
           uint32_t alo = desc_lo(ka), blo = desc_lo(qb);
           mma_ss_lh(tmem + TK_SD, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 0u);
@@ -123,11 +132,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
           }
           mma_commit(&bars[KB_SDONE]);
         }
-        if (!failed) failed = !mbar_wait(&bars[KB_GFULL + sg], (j / KG_NST) & 1, WAIT_LIMIT);
-        // ... and S^T of this tile
-        if (!failed) failed = !mbar_wait(&bars[KB_CONS_S], j & 1, WAIT_LIMIT);
-        fence_after_sync();
-        {
+        if (j >= 1) {   // dV += P^T dO of tile j-1 (P^T from TMEM; the dO tile re-described as an MN-major B operand)
+          if (!failed) failed = !mbar_wait(&bars[KB_GRAD], (j - 1) & 1, WAIT_LIMIT);
+          fence_after_sync();
+          const uint64_t gd = smem_desc(gb_addr + pg * VBUF, 128, BCS);
+#pragma unroll
+          for (int ks = 0; ks < BT / 16; ++ks)
+            mma_ts_lh(tmem + TK_DV, tmem + TK_P + ks * 8, desc_lo(gd) + ks * ((2 * 128) >> 4), desc_hi(gd), idesc_v,
+                      (j > 1 || ks > 0) ? 1u : 0u);
+          mma_commit(&bars[KB_ACCG + pg]);
+        }
+        if (j < T_tiles) {
+          if (!failed) failed = !mbar_wait(&bars[KB_GFULL + sg], (j / KG_NST) & 1, WAIT_LIMIT);
+          // ... and S^T of this tile
+          if (!failed) failed = !mbar_wait(&bars[KB_CONS_S], j & 1, WAIT_LIMIT);
+          fence_after_sync();
           const uint64_t gb = smem_desc(gb_addr + sg * VBUF, BCS, 128);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks)
@@ -135,33 +154,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
                       desc_hi(gb), idesc_s, ks > 0);
           mma_commit(&bars[KB_DPDONE]);
         }
-      }
-      if (failed) atomicOr(p.status, 1u);
-    }
-    __syncwarp();
-  } else if (warp == BWD_A_WARP) {
-    // =============================== MMA issue: dK' += dS^T Q', dV += P^T dO ====================
-    if (lane == 0 && T_tiles > 0) {
-      const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
-      const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
-      const uint32_t qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
-      for (int j = 0; j < T_tiles && !failed; ++j) {
-        const int sq = j % KQ_NST, sg = j % KG_NST;
-        failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);
-        if (!failed) failed = !mbar_wait(&bars[KB_GFULL + sg], (j / KG_NST) & 1, WAIT_LIMIT);
-        if (!failed) failed = !mbar_wait(&bars[KB_GRAD], j & 1, WAIT_LIMIT);
-        fence_after_sync();
-        // P^T / dS^T from TMEM; the streamed tiles re-described as MN-major B operands
-        const uint64_t gd = smem_desc(gb_addr + sg * VBUF, 128, BCS), qd = smem_desc(qb_addr + sq * KBUF, 128, BCS);
+        if (j >= 1) {   // dK' += dS^T Q' of tile j-1
+          const uint64_t qd = smem_desc(qb_addr + pq * KBUF, 128, BCS);
 #pragma unroll
-        for (int ks = 0; ks < BT / 16; ++ks) {
-          const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u, bstep = ks * ((2 * 128) >> 4);
-          mma_ts_lh(tmem + TK_DK, tmem + TK_DS + ks * 8, desc_lo(qd) + bstep, desc_hi(qd), idesc_k, acc);
-          mma_ts_lh(tmem + TK_DV, tmem + TK_P + ks * 8, desc_lo(gd) + bstep, desc_hi(gd), idesc_v, acc);
+          for (int ks = 0; ks < BT / 16; ++ks)
+            mma_ts_lh(tmem + TK_DK, tmem + TK_DS + ks * 8, desc_lo(qd) + ks * ((2 * 128) >> 4), desc_hi(qd), idesc_k,
+                      (j > 1 || ks > 0) ? 1u : 0u);
+          mma_commit(&bars[KB_ACCQ + pq]);
         }
-        // every score product of this tile finished before its P^T / dS^T existed
-        mma_commit(&bars[KB_ACCQ + sq]);
-        mma_commit(&bars[KB_ACCG + sg]);
       }
       if (failed) atomicOr(p.status, 1u);
     }
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     };
     if (interior) probabilities(std::false_type());
     else probabilities(std::true_type());
-    // the P^T / dS^T columns were read by the accumulation step of tile j-1
+    // the P^T columns were read by dV += P^T dO of tile j-1
     if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_ACCG + (j - 1) % KG_NST], ((j - 1) / KG_NST) & 1, WAIT_LIMIT);
     tmem_st16(tmem + lane_base + TK_P + half * 16, pw);
     if (!failed) failed = !mbar_wait(&bars[KB_DPDONE], j & 1, WAIT_LIMIT);
@@ -250,6 +250,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       dw[c4 * 2] = pack2<T>(ds[0], ds[1]);
       dw[c4 * 2 + 1] = pack2<T>(ds[2], ds[3]);
     }
+    // the dS^T columns were read by dK' += dS^T Q' of tile j-1
+    if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_ACCQ + (j - 1) % KQ_NST], ((j - 1) / KQ_NST) & 1, WAIT_LIMIT);
     tmem_st16(tmem + lane_base + TK_DS + half * 16, dw);
     tmem_st_wait();
     fence_before_sync();
@@ -258,7 +260,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
 
   // ---- epilogue ---------------------------------------------------------------------------------
   if (T_tiles > 0 && !failed)
-    failed = !mbar_wait(&bars[KB_ACCG + (T_tiles - 1) % KG_NST], ((T_tiles - 1) / KG_NST) & 1, WAIT_LIMIT);
+    failed = !mbar_wait(&bars[KB_ACCG + (T_tiles - 1) % KG_NST], ((T_tiles - 1) / KG_NST) & 1, WAIT_LIMIT) ||
+             !mbar_wait(&bars[KB_ACCQ + (T_tiles - 1) % KQ_NST], ((T_tiles - 1) / KQ_NST) & 1, WAIT_LIMIT);
   fence_after_sync();
   asm volatile("bar.sync 1, 256;" ::: "memory");   // every MMA is done: the streamed buffers can be reused
   // Everything below reuses dead shared memory: the streamed buffers hold the bias trig and the per-row key-phase
