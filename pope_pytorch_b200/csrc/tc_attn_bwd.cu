@@ -61,7 +61,9 @@ enum { BB_FULL = 0,      // [3] streamed tile j has landed in its stage (transac
        BB_CONSUMED = 7,  // 8 warps: scores copied to registers, the score columns may be overwritten
        BB_GRAD = 8,      // 8 warps: dS (and P) of the current tile are written
        BB_RESIDENT = 9,  // the resident operands are in place (copies' transaction bytes, plus the warps that wrote TMEM)
-       BB_COUNT = 10 };
+       BB_ISSUED = 10,   // [2] the score products of tile j have been ISSUED (slot j & 1): what is issued after this
+                         //     executes behind them in the tensor pipe
+       BB_COUNT = 12 };
 
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -99,6 +101,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     mbar_init(&bars[BB_SCORES], 1);
     mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
     mbar_init(&bars[BB_RESIDENT], 1 + BWD_E_WARPS);
+    mbar_init(&bars[BB_ISSUED], 1), mbar_init(&bars[BB_ISSUED + 1], 1);
     mbar_init_fence();
   }
   int n_end = p.Nk;
@@ -168,6 +171,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
         fence_after_sync();
         issue_scores(j);
+        mbar_arrive(&bars[BB_ISSUED + (j & 1)]);
       }
       if (failed) atomicOr(p.status, 1u);
     }
@@ -181,6 +185,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         const int st = j % DQ_NST;
         failed = !mbar_wait(&bars[BB_FULL + st], (j / DQ_NST) & 1, WAIT_LIMIT);
         if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
+        // Let the score products of the next tile enter the pipe first: they head the critical score -> elementwise
+        // -> score chain, and this accumulation then runs in the gap while their results are copied out of TMEM.
+        if (j + 1 < T_tiles && !failed) failed = !mbar_wait(&bars[BB_ISSUED + ((j + 1) & 1)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
         fence_after_sync();
         // dS from TMEM; the K' tile re-described as an MN-major B operand
         const uint64_t bd = smem_desc(ks_addr + st * KBUF, 128, BCS);
