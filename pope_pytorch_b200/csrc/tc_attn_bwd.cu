@@ -63,7 +63,8 @@ enum { BB_FULL = 0,      // [3] streamed tile j has landed in its stage (transac
        BB_RESIDENT = 9,  // the resident operands are in place (copies' transaction bytes, plus the warps that wrote TMEM)
        BB_ISSUED = 10,   // [2] the score products of tile j have been ISSUED (slot j & 1): what is issued after this
                          //     executes behind them in the tensor pipe
-       BB_COUNT = 12 };
+       BB_DPDONE = 12,   // tcgen05.commit: dP of the current tile is in TMEM (dq kernel: issued by the second warp)
+       BB_COUNT = 13 };
 
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
     mbar_init(&bars[BB_RESIDENT], 1 + BWD_E_WARPS);
     mbar_init(&bars[BB_ISSUED], 1), mbar_init(&bars[BB_ISSUED + 1], 1);
+    mbar_init(&bars[BB_DPDONE], 1);
     mbar_init_fence();
   }
   int n_end = p.Nk;
@@ -144,14 +146,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     }
     __syncwarp();
   } else if (warp == BWD_M_WARP) {
-    // =============================== MMA issue ===================================================
+    // =============================== MMA issue: S = Q' K'^T ======================================
+    // The two score products of a tile are issued by the two issuing warps at the same time (16 + 8 instructions at
+    // ~55 clk each from one thread were the longest link of the score -> elementwise -> score chain).
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
-      const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+      const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks);
       const uint64_t qd = smem_desc(qs_addr, BQ * 16, 128);
-      auto issue_scores = [&](int jt) {   // S = Q' K'^T (both from shared memory), dP = dO V^T (dO from TMEM)
-        const int st = jt % DQ_NST;
-        const uint64_t kd = smem_desc(ks_addr + st * KBUF, BCS, 128), vd = smem_desc(vs_addr + st * VBUF, BCS, 128);
+      if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
+      for (int j = 0; j < T_tiles && !failed; ++j) {
+        const int st = j % DQ_NST;
+        failed = !mbar_wait(&bars[BB_FULL + st], (j / DQ_NST) & 1, WAIT_LIMIT);
+        // the elementwise warps have copied the previous tile's scores out of TMEM
+        if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
+        fence_after_sync();
+        const uint64_t kd = smem_desc(ks_addr + st * KBUF, BCS, 128);
         uint32_t alo = desc_lo(qd), blo = desc_lo(kd);
         mma_ss_lh(tmem + TC_S, alo, desc_hi(qd), blo, desc_hi(kd), idesc_s, 0u);
 #pragma unroll 4
@@ -159,43 +168,45 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
           alo += (2 * BQ * 16) >> 4, blo += (2 * BCS) >> 4;
           mma_ss_lh(tmem + TC_S, alo, desc_hi(qd), blo, desc_hi(kd), idesc_s, 1u);
         }
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          mma_ts_lh(tmem + TC_DP, tmem + TC_DO + ks * 8, desc_lo(vd) + ks * ((2 * BCS) >> 4), desc_hi(vd), idesc_s, ks > 0);
         mma_commit(&bars[BB_SCORES]);
-      };
-      if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
-      for (int j = 0; j < T_tiles && !failed; ++j) {
-        failed = !mbar_wait(&bars[BB_FULL + j % DQ_NST], (j / DQ_NST) & 1, WAIT_LIMIT);
-        // the elementwise warps have copied the previous tile's scores out of TMEM
-        if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
-        fence_after_sync();
-        issue_scores(j);
         mbar_arrive(&bars[BB_ISSUED + (j & 1)]);
       }
       if (failed) atomicOr(p.status, 1u);
     }
     __syncwarp();
   } else if (warp == BWD_A_WARP) {
-    // =============================== MMA issue: dQ' += dS K' ====================================
+    // =============================== MMA issue: dP = dO V^T, dQ' += dS K' ========================
     if (lane == 0) {
+      const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
       const uint32_t idesc_q = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
-      const uint32_t ks_addr = smem_u32(Ks);
-      for (int j = 0; j < T_tiles && !failed; ++j) {
-        const int st = j % DQ_NST;
-        failed = !mbar_wait(&bars[BB_FULL + st], (j / DQ_NST) & 1, WAIT_LIMIT);
-        if (!failed) failed = !mbar_wait(&bars[BB_GRAD], j & 1, WAIT_LIMIT);
-        // Let the score products of the next tile enter the pipe first: they head the critical score -> elementwise
-        // -> score chain, and this accumulation then runs in the gap while their results are copied out of TMEM.
-        if (j + 1 < T_tiles && !failed) failed = !mbar_wait(&bars[BB_ISSUED + ((j + 1) & 1)], ((j + 1) >> 1) & 1, WAIT_LIMIT);
-        fence_after_sync();
-        // dS from TMEM; the K' tile re-described as an MN-major B operand
-        const uint64_t bd = smem_desc(ks_addr + st * KBUF, 128, BCS);
+      const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs);
+      if (!mbar_wait(&bars[BB_RESIDENT], 0, WAIT_LIMIT)) failed = true;   // dO is in TMEM
+      for (int j = 0; j <= T_tiles && !failed; ++j) {
+        if (j < T_tiles) {   // dP(j): dO from TMEM, the V tile from shared memory
+          const int st = j % DQ_NST;
+          failed = !mbar_wait(&bars[BB_FULL + st], (j / DQ_NST) & 1, WAIT_LIMIT);
+          if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
+          fence_after_sync();
+          const uint64_t vd = smem_desc(vs_addr + st * VBUF, BCS, 128);
 #pragma unroll
-        for (int ks = 0; ks < BT / 16; ++ks)
-          mma_ts_lh(tmem + TC_DQ, tmem + TC_DS + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_q,
-                    (j > 0 || ks > 0) ? 1u : 0u);
-        mma_commit(&bars[BB_ACC + st]);   // every score product of this tile finished before its dS existed
+          for (int ks = 0; ks < D / 16; ++ks)
+            mma_ts_lh(tmem + TC_DP, tmem + TC_DO + ks * 8, desc_lo(vd) + ks * ((2 * BCS) >> 4), desc_hi(vd), idesc_s, ks > 0);
+          mma_commit(&bars[BB_DPDONE]);
+        }
+        if (j >= 1) {   // dQ' += dS K'(j-1): dS from TMEM; the K' tile re-described as an MN-major B operand
+          const int jp = j - 1, st = jp % DQ_NST;
+          if (!failed) failed = !mbar_wait(&bars[BB_GRAD], jp & 1, WAIT_LIMIT);
+          // Let the score product of tile j enter the pipe first: it heads the critical score -> elementwise -> score
+          // chain, and this accumulation then runs in the gap while its results are copied out of TMEM.
+          if (j < T_tiles && !failed) failed = !mbar_wait(&bars[BB_ISSUED + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
+          fence_after_sync();
+          const uint64_t bd = smem_desc(ks_addr + st * KBUF, 128, BCS);
+#pragma unroll
+          for (int ks = 0; ks < BT / 16; ++ks)
+            mma_ts_lh(tmem + TC_DQ, tmem + TC_DS + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_q,
+                      (jp > 0 || ks > 0) ? 1u : 0u);
+          mma_commit(&bars[BB_ACC + st]);   // every score product of this tile finished before its dS existed
+        }
       }
       if (failed) atomicOr(p.status, 1u);
     }
@@ -251,6 +262,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     if (lse2 == -CUDART_INF_F) vis = 0u;
     const bool all_vis = __all_sync(0xffffffffu, vis == 0xffffffffu);   // interior tile: no masking work
     if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
+    if (!failed) failed = !mbar_wait(&bars[BB_DPDONE], j & 1, WAIT_LIMIT);
     fence_after_sync();
     uint32_t sv[32], dv[32];
     tmem_ld32(tmem + lane_base + TC_S + half * 32, sv);
