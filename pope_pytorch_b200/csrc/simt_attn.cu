@@ -274,6 +274,7 @@ cudaError_t attn_bwd_delta(const PopeAttnBwdArgs& a, float* delta, cudaStream_t 
 // once per call and shared by all units, rotated by the head's bias held in registers.  Each (unit, key
 // range) CTA writes a partial (o, m, l) that attn_fwd_combine_kernel merges.
 constexpr int DEC_WARPS = 8;
+constexpr int DEC_KU = 4;   // keys per warp and loop iteration
 
 struct DecodeP {
   int H, Hk, Nk, d, r, nsplit, split_len;
@@ -349,43 +350,65 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(DecodeP p) 
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[m][e] = 0.f;
 
-  for (int j = kb + w; j < ke; j += DEC_WARPS) {
-    float part = 0.f, vv[DM][4];
+  // DEC_KU keys per warp and iteration: their loads are issued together, their warp reductions interleave, and
+  // the running maximum / rescale of the accumulator is paid once per group instead of once per key.
+  for (int j0 = kb + w; j0 < ke; j0 += DEC_WARPS * DEC_KU) {
+    float part[DEC_KU], vv[DEC_KU][DM][4];
+    bool ok[DEC_KU];
 #pragma unroll
-    for (int m = 0; m < DM; ++m) {
-      const int c0 = m * 128 + lane * 4;
+    for (int u = 0; u < DEC_KU; ++u) {
+      const int j = j0 + u * DEC_WARPS;
+      const bool in = j < ke;
+      ok[u] = in && (!mask || mask[(int64_t)j * p.msn] != 0);   // warp-uniform
+      part[u] = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) vv[m][e] = 0.f;
-      if (!live[m]) continue;
-      float x[4];
-      load4<T>(kbase + (int64_t)j * p.sk.n + c0, x);
-      load4<T>(vbase + (int64_t)j * p.sv.n + c0, vv[m]);
-      if (rot[m]) {
-        float ct[4], stt[4];
-        load4<float>(p.ctab + (int64_t)j * p.r + c0, ct);
-        load4<float>(p.stab + (int64_t)j * p.r + c0, stt);
+      for (int m = 0; m < DM; ++m) {
+        const int c0 = m * 128 + lane * 4;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a = softplus_fast(x[e]);   // ex2.approx / lg2.approx: 2^-22, a sixth of the instructions
-          const float kc = a * (ct[e] * cb[m][e] - stt[e] * sb[m][e]);
-          const float ks = a * (stt[e] * cb[m][e] + ct[e] * sb[m][e]);
-          part = fmaf(qc[m][e], kc, fmaf(qs[m][e], ks, part));
+        for (int e = 0; e < 4; ++e) vv[u][m][e] = 0.f;
+        if (!live[m] || !in) continue;
+        float x[4];
+        load4<T>(kbase + (int64_t)j * p.sk.n + c0, x);
+        load4<T>(vbase + (int64_t)j * p.sv.n + c0, vv[u][m]);
+        if (rot[m]) {
+          float ct[4], stt[4];
+          load4<float>(p.ctab + (int64_t)j * p.r + c0, ct);
+          load4<float>(p.stab + (int64_t)j * p.r + c0, stt);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float a = softplus_fast(x[e]);   // ex2.approx / lg2.approx: 2^-22, a sixth of the instructions
+            const float kc = a * (ct[e] * cb[m][e] - stt[e] * sb[m][e]);
+            const float ks = a * (stt[e] * cb[m][e] + ct[e] * sb[m][e]);
+            part[u] = fmaf(qc[m][e], kc, fmaf(qs[m][e], ks, part[u]));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) part[u] = fmaf(qc[m][e], x[e], part[u]);
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) part = fmaf(qc[m][e], x[e], part);
       }
     }
-    const float sc = warp_sum(part) * p.scale;
-    if (mask && !mask[(int64_t)j * p.msn]) continue;   // warp-uniform
-    const float mnew = fmaxf(mrun, sc);
-    const float alpha = expf(mrun - mnew), pj = expf(sc - mnew);
-    lrun = lrun * alpha + pj;
+    float sc[DEC_KU], mnew = mrun;
+#pragma unroll
+    for (int u = 0; u < DEC_KU; ++u) {
+      sc[u] = ok[u] ? warp_sum(part[u]) * p.scale : -CUDART_INF_F;
+      mnew = fmaxf(mnew, sc[u]);
+    }
+    if (mnew == -CUDART_INF_F) continue;   // nothing visible so far (warp-uniform)
+    const float alpha = expf(mrun - mnew);   // exp(-inf) = 0 on the first visible group
+    float pj[DEC_KU], psum = 0.f;
+#pragma unroll
+    for (int u = 0; u < DEC_KU; ++u) pj[u] = expf(sc[u] - mnew), psum += pj[u];
+    lrun = lrun * alpha + psum;
     mrun = mnew;
 #pragma unroll
     for (int m = 0; m < DM; ++m)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[m][e] = fmaf(pj, vv[m][e], o[m][e] * alpha);
+      for (int e = 0; e < 4; ++e) {
+        float acc = o[m][e] * alpha;
+#pragma unroll
+        for (int u = 0; u < DEC_KU; ++u) acc = fmaf(pj[u], vv[u][m][e], acc);
+        o[m][e] = acc;
+      }
   }
 
   // merge the 8 warps of the CTA, then hand the partial to the cross-split combine
