@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   fence_after_sync();
   {
     const int ASTR = KD * 4 + 16;            // bytes of one staged fp32 row (16 bytes of padding: conflict-free)
-    uint8_t* accs = smem;                    // [128 rows][KD fp32]: 133 KB at KD = 256, over Q' and the stages
+    uint8_t* accs = Ks;                      // [128 rows][KD fp32]: 133 KB at KD = 256, over the (dead) stages; Q' stays
     constexpr int HW = D / 2;                // columns of each part copied by this thread: [half*HW, half*HW + HW)
     const uint32_t acc = tmem + lane_base + TC_DQ;
 #pragma unroll
@@ -327,60 +327,44 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     }
     asm volatile("bar.sync 1, 256;" ::: "memory");
     constexpr int GPR = D / 8;               // 8-feature groups per row
-    const T* qbase = (const T*)p.q + b * p.sq.b + h * p.sq.h;
     T* dqbase = (T*)p.dq + b * p.sdq.b + h * p.sdq.h;
-    // Items (row, 8-feature group) in batches of EB per thread: all global loads of a batch are issued before its
-    // arithmetic.  (They remain the bulk of the epilogue: ~11 K of its ~15 K clk with them, 3 K without.)
-    constexpr int NITEM = BQ * GPR / 256, EB = NITEM % 4 == 0 ? 4 : (NITEM % 3 == 0 ? 3 : 2);
-    static_assert(NITEM % EB == 0, "items per thread must split into whole batches");
-#pragma unroll 1
-    for (int i0b = 0; i0b < NITEM; i0b += EB) {
-      uint4 qv[EB];
-      float4 tc0[EB], tc1[EB], ts0[EB], ts1[EB];
+    // Everything the chain rule needs is in the resident Q' tile: with qc = a cos f, qs = a sin f (a = softplus(q)),
+    //   a = sqrt(qc^2 + qs^2),  sigmoid(q) = 1 - exp(-a),  dq = (dQc qc + dQs qs) / a * sigmoid(q),
+    //   dphase = a (dQs cos f - dQc sin f) = dQs qc - dQc qs,
+    // so the epilogue reads neither q nor the phase tables from global memory (those loads took 11 K of its 15 K
+    // clocks).  The 16-bit rounding of Q' costs cos f a relative 2^-8 sin^2 f at most.
+    for (int idx = tid; idx < BQ * GPR; idx += 256) {
+      const int rr = idx / GPR, g = idx - rr * GPR, cb = g * 8, gr = i0 + rr;
+      if (gr >= p.Nq) continue;
+      const float4 a0 = *reinterpret_cast<const float4*>(accs + rr * ASTR + cb * 4);
+      const float4 a1 = *reinterpret_cast<const float4*>(accs + rr * ASTR + cb * 4 + 16);
+      const float gcv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      uint32_t outw[4];
+      if (cb < p.r) {   // r is a multiple of 16: an 8-wide group is rotated as a whole
+        const float4 b0 = *reinterpret_cast<const float4*>(accs + rr * ASTR + (D + cb) * 4);
+        const float4 b1 = *reinterpret_cast<const float4*>(accs + rr * ASTR + (D + cb) * 4 + 16);
+        const float gsv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const uint4 qcw = *reinterpret_cast<const uint4*>(Qs + g * (BQ * 16) + rr * 16);
+        const uint4 qsw = *reinterpret_cast<const uint4*>(Qs + (D / 8 + g) * (BQ * 16) + rr * 16);
+        const uint32_t cw[4] = {qcw.x, qcw.y, qcw.z, qcw.w}, sw[4] = {qsw.x, qsw.y, qsw.z, qsw.w};
+        float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + h * p.sdf.h + (int64_t)(qoff + gr) * p.sdf.n + cb : nullptr;
 #pragma unroll
-      for (int k = 0; k < EB; ++k) {
-        const int idx = tid + (i0b + k) * 256, rr = idx / GPR, cb = (idx - rr * GPR) * 8, gr = i0 + rr;
-        qv[k] = make_uint4(0, 0, 0, 0);
-        tc0[k] = tc1[k] = ts0[k] = ts1[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (gr < p.Nq && cb < p.r) {   // r is a multiple of 16: an 8-wide group is rotated as a whole
-          qv[k] = __ldg(reinterpret_cast<const uint4*>(qbase + (int64_t)gr * p.sq.n + cb));
-          const int64_t trow = (int64_t)(qoff + gr) * p.r + cb;   // fp32 cos / sin tables
-          tc0[k] = __ldg(reinterpret_cast<const float4*>(p.ctab + trow)), tc1[k] = __ldg(reinterpret_cast<const float4*>(p.ctab + trow) + 1);
-          ts0[k] = __ldg(reinterpret_cast<const float4*>(p.stab + trow)), ts1[k] = __ldg(reinterpret_cast<const float4*>(p.stab + trow) + 1);
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < EB; ++k) {
-        const int idx = tid + (i0b + k) * 256, rr = idx / GPR, cb = (idx - rr * GPR) * 8, gr = i0 + rr;
-        if (gr >= p.Nq) continue;
-        const float4 a0 = *reinterpret_cast<const float4*>(accs + rr * ASTR + cb * 4);
-        const float4 a1 = *reinterpret_cast<const float4*>(accs + rr * ASTR + cb * 4 + 16);
-        const float gcv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-        uint32_t outw[4];
-        if (cb < p.r) {
-          const float4 b0 = *reinterpret_cast<const float4*>(accs + rr * ASTR + (D + cb) * 4);
-          const float4 b1 = *reinterpret_cast<const float4*>(accs + rr * ASTR + (D + cb) * 4 + 16);
-          const float gsv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-          const uint32_t qw[4] = {qv[k].x, qv[k].y, qv[k].z, qv[k].w};
-          const float cf[8] = {tc0[k].x, tc0[k].y, tc0[k].z, tc0[k].w, tc1[k].x, tc1[k].y, tc1[k].z, tc1[k].w};
-          const float sf[8] = {ts0[k].x, ts0[k].y, ts0[k].z, ts0[k].w, ts1[k].x, ts1[k].y, ts1[k].z, ts1[k].w};
-          float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + h * p.sdf.h + (int64_t)(qoff + gr) * p.sdf.n + cb : nullptr;
-#pragma unroll
-          for (int e = 0; e < 8; e += 2) {
-            const float2 x = unpack2<T>(qw[e >> 1]);
-            if (dfrow) {
-              atomicAdd(dfrow + e, softplus_fast(x.x) * (gsv[e] * cf[e] - gcv[e] * sf[e]));
-              atomicAdd(dfrow + e + 1, softplus_fast(x.y) * (gsv[e + 1] * cf[e + 1] - gcv[e + 1] * sf[e + 1]));
-            }
-            outw[e >> 1] = pack2<T>((gcv[e] * cf[e] + gsv[e] * sf[e]) * sigmoid_fast(x.x),
-                                    (gcv[e + 1] * cf[e + 1] + gsv[e + 1] * sf[e + 1]) * sigmoid_fast(x.y));
+        for (int e = 0; e < 8; e += 2) {
+          const float2 qc = unpack2<T>(cw[e >> 1]), qs = unpack2<T>(sw[e >> 1]);
+          const float m0 = qc.x * qc.x + qs.x * qs.x, m1 = qc.y * qc.y + qs.y * qs.y;   // a^2
+          const float r0 = m0 > 0.f ? rsqrtf(m0) : 0.f, r1 = m1 > 0.f ? rsqrtf(m1) : 0.f;
+          const float sg0 = 1.f - ex2_approx(-m0 * r0 * LOG2E), sg1 = 1.f - ex2_approx(-m1 * r1 * LOG2E);
+          if (dfrow) {
+            atomicAdd(dfrow + e, gsv[e] * qc.x - gcv[e] * qs.x);
+            atomicAdd(dfrow + e + 1, gsv[e + 1] * qc.y - gcv[e + 1] * qs.y);
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; e += 2) outw[e >> 1] = pack2<T>(gcv[e], gcv[e + 1]);
+          outw[e >> 1] = pack2<T>((gcv[e] * qc.x + gsv[e] * qs.x) * r0 * sg0, (gcv[e + 1] * qc.y + gsv[e + 1] * qs.y) * r1 * sg1);
         }
-        *reinterpret_cast<uint4*>(dqbase + (int64_t)gr * p.sdq.n + cb) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) outw[e >> 1] = pack2<T>(gcv[e], gcv[e + 1]);
       }
+      *reinterpret_cast<uint4*>(dqbase + (int64_t)gr * p.sdq.n + cb) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
     }
   }
   if (failed) atomicOr(p.status, 1u);
