@@ -184,15 +184,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   for (int j = 0; j < T_tiles; ++j) {
     const int sq = j % KQ_NST;
     const int m0 = tile_start(j);
-    if (j == max(T_tiles - 3, 0) && gj < p.Nk) {
-      // the epilogue reads this thread's half of the k row and of its cos / sin table rows: have L2 fetch them now
-      prefetch_l2(kbase + (int64_t)gj * p.sk.n + half * (D / 2), D);
-      if (half * (D / 2) < p.r) {
-        const int nf = min(D / 2, p.r - half * (D / 2)) * 4;
-        prefetch_l2(p.ctab + (int64_t)gj * p.r + half * (D / 2), nf);
-        prefetch_l2(p.stab + (int64_t)gj * p.r + half * (D / 2), nf);
-      }
-    }
     if (!failed) failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);   // orders the lse / delta read
     if (!failed) failed = !mbar_wait(&bars[KB_SDONE], j & 1, WAIT_LIMIT);
     fence_after_sync();
@@ -264,36 +255,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
              !mbar_wait(&bars[KB_ACCQ + (T_tiles - 1) % KQ_NST], ((T_tiles - 1) / KQ_NST) & 1, WAIT_LIMIT);
   fence_after_sync();
   asm volatile("bar.sync 1, 256;" ::: "memory");   // every MMA is done: the streamed buffers can be reused
-  // Everything below reuses dead shared memory: the streamed buffers hold the bias trig and the per-row key-phase
-  // gradients (feature-major, [r][128 rows] fp32); the resident K' / V tiles become row-major staging tiles of dk
-  // and dv, so that both leave in fully coalesced 16-byte pieces.
+  // Everything below reuses dead shared memory behind the resident K' tile (V and the streamed buffers): row-major
+  // staging tiles of dk and dv, so that both leave in fully coalesced 16-byte pieces, and the per-row key-phase
+  // gradients (feature-major, [r][128 rows] fp32) for the bias gradient.
+  // Everything the chain rule needs is in the resident K' tile: with kc = a cos(f + b), ks = a sin(f + b)
+  // (a = softplus(k)),   a = sqrt(kc^2 + ks^2),  sigmoid(k) = 1 - exp(-a),
+  //   dk = (dKc kc + dKs ks) / a * sigmoid(k),   dphase = a (dKs cos - dKc sin) = dKs kc - dKc ks,
+  // so the epilogue reads neither k nor the phase tables from global memory.  The 16-bit rounding of K' costs the
+  // cosine a relative 2^-8 sin^2 at most.  Rows past Nk are zero in the image and produce zeros.
   constexpr int OSTR = D * 2 + 16;             // bytes of a staged output row (16 bytes of padding: conflict-free)
-  uint8_t* dk_stage = Ks;                      // (the two tiles may run a few KB past K' and V into the streamed
-  uint8_t* dv_stage = Ks + BQ * OSTR;          //  buffers, which only happens when r = 0 and nothing else lives there)
-  float* red = reinterpret_cast<float*>(Qb);   // (unused tail of the first 2 KB: bias trig below)
-  float* dmat = reinterpret_cast<float*>(Qb + 2048);   // [r][128]
-  float* bias_cb = red + 128;                  // cos / sin of the head's phase bias
-  float* bias_sb = red + 256;
-  for (int c = tid; c < p.r; c += 256) sincosf(biasr[c], &bias_sb[c], &bias_cb[c]);
-  asm volatile("bar.sync 1, 256;" ::: "memory");
+  uint8_t* dk_stage = Vs;
+  uint8_t* dv_stage = Vs + BQ * OSTR;
+  float* dmat = reinterpret_cast<float*>(Vs + 2 * BQ * OSTR);   // [r][128]
   {
     constexpr int HW = D / 2;
     const uint32_t accv = tmem + lane_base + TK_DV, acck = tmem + lane_base + TK_DK;
-    const T* krow = kbase + (int64_t)gj * p.sk.n;
-    const int64_t trow = (int64_t)gj * p.r;   // row of the fp32 cos / sin tables
     float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + hk * p.sdf.h + (int64_t)gj * p.sdf.n : nullptr;
     const bool live = gj < p.Nk;
 #pragma unroll
     for (int c0 = 0; c0 < HW; c0 += 16) {
       const int cbase = half * HW + c0;
       uint32_t gv[16], gc[16], gs[16];
-      const bool rot = cbase < p.r;
+      const bool rot = cbase < p.r && T_tiles > 0;
       if (T_tiles > 0) {
         tmem_ld16(accv + cbase, gv);
         tmem_ld16(acck + cbase, gc);
         if (rot) tmem_ld16(acck + D + cbase, gs);
         tmem_ld_wait();
-      } else {
+      } else {   // no visible query row: zero gradients (the resident tiles were never loaded)
 #pragma unroll
         for (int e = 0; e < 16; ++e) gv[e] = gc[e] = gs[e] = 0u;
       }
@@ -301,41 +290,32 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
 #pragma unroll
       for (int e = 0; e < 16; e += 2) wv[e >> 1] = pack2<T>(__uint_as_float(gv[e]), __uint_as_float(gv[e + 1]));
       if (rot) {
-        uint32_t kw[8] = {};
-        float cf[16], sf[16];
-        if (live) {
-          const uint4 k0 = __ldg(reinterpret_cast<const uint4*>(krow + cbase)), k1 = __ldg(reinterpret_cast<const uint4*>(krow + cbase + 8));
-          kw[0] = k0.x, kw[1] = k0.y, kw[2] = k0.z, kw[3] = k0.w, kw[4] = k1.x, kw[5] = k1.y, kw[6] = k1.z, kw[7] = k1.w;
+        uint32_t cw[8], sw[8];
 #pragma unroll
-          for (int e4 = 0; e4 < 4; ++e4) {
-            const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.ctab + trow + cbase) + e4);
-            const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.stab + trow + cbase) + e4);
-            const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {   // cos(f + b), sin(f + b)
-              const float cb = bias_cb[cbase + e4 * 4 + t], sb = bias_sb[cbase + e4 * 4 + t];
-              cf[e4 * 4 + t] = cc[t] * cb - ss[t] * sb;
-              sf[e4 * 4 + t] = ss[t] * cb + cc[t] * sb;
-            }
-          }
+        for (int i = 0; i < 2; ++i) {
+          const uint4 kcw = *reinterpret_cast<const uint4*>(Ks + (cbase / 8 + i) * (BQ * 16) + row * 16);
+          const uint4 ksw = *reinterpret_cast<const uint4*>(Ks + (D / 8 + cbase / 8 + i) * (BQ * 16) + row * 16);
+          cw[4 * i] = kcw.x, cw[4 * i + 1] = kcw.y, cw[4 * i + 2] = kcw.z, cw[4 * i + 3] = kcw.w;
+          sw[4 * i] = ksw.x, sw[4 * i + 1] = ksw.y, sw[4 * i + 2] = ksw.z, sw[4 * i + 3] = ksw.w;
         }
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
-          float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
-          float d0 = 0.f, d1 = 0.f;
-          if (live) {
-            const float2 x = unpack2<T>(kw[e >> 1]);
-            const float h0 = __uint_as_float(gs[e]), h1 = __uint_as_float(gs[e + 1]);
-            d0 = softplus_fast(x.x) * (h0 * cf[e] - g0 * sf[e]);
-            d1 = softplus_fast(x.y) * (h1 * cf[e + 1] - g1 * sf[e + 1]);
-            if (dfrow) atomicAdd(dfrow + cbase + e, d0), atomicAdd(dfrow + cbase + e + 1, d1);
-            g0 = (g0 * cf[e] + h0 * sf[e]) * sigmoid_fast(x.x);
-            g1 = (g1 * cf[e + 1] + h1 * sf[e + 1]) * sigmoid_fast(x.y);
-          }
+          const float2 kc = unpack2<T>(cw[e >> 1]), ks = unpack2<T>(sw[e >> 1]);
+          const float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
+          const float h0 = __uint_as_float(gs[e]), h1 = __uint_as_float(gs[e + 1]);
+          const float m0 = kc.x * kc.x + ks.x * ks.x, m1 = kc.y * kc.y + ks.y * ks.y;   // a^2
+          const float r0 = m0 > 0.f ? rsqrtf(m0) : 0.f, r1 = m1 > 0.f ? rsqrtf(m1) : 0.f;
+          const float sg0 = 1.f - ex2_approx(-m0 * r0 * LOG2E), sg1 = 1.f - ex2_approx(-m1 * r1 * LOG2E);
+          const float d0 = h0 * kc.x - g0 * ks.x, d1 = h1 * kc.y - g1 * ks.y;
+          if (dfrow && live) atomicAdd(dfrow + cbase + e, d0), atomicAdd(dfrow + cbase + e + 1, d1);
           if (p.dbias) dmat[(cbase + e) * BQ + row] = d0, dmat[(cbase + e + 1) * BQ + row] = d1;
-          wk[e >> 1] = pack2<T>(g0, g1);
+          wk[e >> 1] = pack2<T>((g0 * kc.x + h0 * ks.x) * r0 * sg0, (g1 * kc.y + h1 * ks.y) * r1 * sg1);
         }
       } else {
+        if (p.dbias && cbase < p.r) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) dmat[(cbase + e) * BQ + row] = 0.f;
+        }
 #pragma unroll
         for (int e = 0; e < 16; e += 2) wk[e >> 1] = pack2<T>(__uint_as_float(gc[e]), __uint_as_float(gc[e + 1]));
       }
