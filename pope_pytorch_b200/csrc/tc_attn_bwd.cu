@@ -226,16 +226,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
   const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
   {
     // dO rows into TMEM, the A operand of dP = dO V^T: 16 columns (32 features) per step, the two threads
-    // of a row take alternate steps
-    const T* grow = (const T*)p.dout + b * p.sdo.b + h * p.sdo.h + (int64_t)gi * p.sdo.n;
+    // of a row take alternate steps.  Read from the dO IMAGE ([chunk][row][16 B] per 64-row tile; rows past Nq are
+    // zero there): for a fixed chunk the 32 lanes of a warp (32 consecutive rows) read 512 contiguous bytes, where
+    // the row-major dO itself would be touched in 32 different lines per load.
+    const uint8_t* gtile = p.gimg + ((int64_t)u * (int64_t)image_tiles(p.Nq) + i0 / BT + (row >> 6)) * VBUF + (row & 63) * 16;
 #pragma unroll
     for (int g = 0; g < D / 32; ++g) {
       if ((g & 1) != half) continue;
       uint32_t w[16];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        uint4 v4 = make_uint4(0, 0, 0, 0);
-        if (gi < p.Nq) v4 = __ldg(reinterpret_cast<const uint4*>(grow + g * 32 + q4 * 8));
+        const uint4 v4 = __ldg(reinterpret_cast<const uint4*>(gtile + (g * 4 + q4) * BCS));
         w[q4 * 4] = v4.x, w[q4 * 4 + 1] = v4.y, w[q4 * 4 + 2] = v4.z, w[q4 * 4 + 3] = v4.w;
       }
       tmem_st16(tmem + lane_base + TC_DO + g * 16, w);

@@ -35,8 +35,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   const int u = blockIdx.y, b = u / p.Hk, hk = u % p.Hk;
   const int j0 = blockIdx.x * BQ;
   const int groups = p.H / p.Hk;
-  const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
-  const float* biasr = p.r > 0 ? p.bias + hk * p.bias_sh : nullptr;
 
   if (warp == BWD_M_WARP) {
     tmem_alloc(tmem_slot, 512);
