@@ -335,14 +335,14 @@ def main():
         fwd_ms=fwd_ms, bwd_ms=bwd_ms,
         pct_of_nominal_bf16_peak=100.0 * achieved / 2250.0,
         roofline=dict(bound="tensor", achieved=bwd_achieved, peak=peak_sus, unit="TFLOP/s", frac=bwd_achieved / peak_sus,
-                      traffic=4 * (122.5e6 + 10.3e6 + 122.8e6 + 18.5e6),
-                      kernel="backward pass = attn_bwd_dkdv_tc_kernel + attn_bwd_dq_tc_kernel (92 % of its time; the rest "
+                      traffic=4 * (101.2e6 + 8.6e6 + 101.3e6 + 16.1e6),
+                      kernel="backward pass = attn_bwd_dkdv_tc_kernel + attn_bwd_dq_tc_kernel (90 % of its time; the rest "
                              "is its pre-pass: operand images, row statistics, phase tables; one C-ABI call launches all "
                              "of it, timed together with CUDA events on the launch stream)",
                       peak_source=f"{pk['source']} sustained bf16 GEMM (kernels timed inside a long step)",
                       algorithmic_flops_per_launch=bwd_flops,
-                      traffic_note="dram read+write bytes of the dq and dkdv launches of one ncu capture at B=1 (132.8 MB dq, "
-                                   "141.3 MB dkdv), scaled by 4: traffic is proportional to the number of (b,h) units",
+                      traffic_note="dram read+write bytes of the dq and dkdv launches of one ncu capture at B=1 (109.8 MB dq, "
+                                   "117.4 MB dkdv), scaled by 4: traffic is proportional to the number of (b,h) units",
                       forward=dict(achieved=fwd_flops / (fwd_ms * 1e-3) / 1e12, frac=fwd_flops / (fwd_ms * 1e-3) / 1e12 / peak_sus,
                                    what="forward call (tables + images + attn_fwd_tc_kernel), algorithmic flops 2*U*pairs*(2d+r)"),
                       step=dict(achieved=achieved, frac=achieved / peak_sus, frac_of_burst_peak=achieved / pk["bf16_tflops"],
