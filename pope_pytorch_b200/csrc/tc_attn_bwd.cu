@@ -13,6 +13,7 @@
 // phase bias of the keys is part of the K' images.  A streamed tile in shared memory serves two MMAs: as the
 // K-major B operand of the score product and, re-described as MN-major, as the B operand of the gradient
 // product -- the 8x16-byte core-matrix layout is symmetric under that exchange.
+#include <mutex>
 #include <type_traits>
 
 #include "kernels.h"

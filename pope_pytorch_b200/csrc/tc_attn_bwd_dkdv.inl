@@ -422,6 +422,31 @@ size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
          up256(image_bytes(s.B * s.H, s.Nq, s.d)) + rowstat_bytes(s);
 }
 
+// Side stream and fork / join events of the backward, one set per device, created on first use and kept for the
+// life of the process.  Without them (creation failed) both kernels run on the caller's stream.
+struct BwdFork {
+  cudaStream_t side;
+  cudaEvent_t ready, done;
+  std::mutex launch;   // the events are shared by all calls on the device: one fork / join sequence at a time
+};
+static BwdFork* bwd_fork() {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static BwdFork forks[kMaxDevices];
+  static int state[kMaxDevices] = {};   // 0 = not tried, 1 = usable, -1 = unavailable
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (state[dev] == 0) {
+    BwdFork& f = forks[dev];
+    const bool ok = cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) == cudaSuccess &&
+                    cudaEventCreateWithFlags(&f.ready, cudaEventDisableTiming) == cudaSuccess &&
+                    cudaEventCreateWithFlags(&f.done, cudaEventDisableTiming) == cudaSuccess;
+    state[dev] = ok ? 1 : -1;
+  }
+  return state[dev] == 1 ? &forks[dev] : nullptr;
+}
+
 template <int D, typename T>
 static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
@@ -469,10 +494,22 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;
   if ((e = cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(attn_bwd_dkdv_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k)) != cudaSuccess) return e;
+  // The two kernels are independent of each other: the dk/dv kernel goes to a side stream that forks from and joins
+  // the caller's stream, so that its CTAs fill the SMs which the last (partial) wave of the dq kernel leaves idle.
+  BwdFork* fk = bwd_fork();
+  std::unique_lock<std::mutex> fork_lock;
+  if (fk) fork_lock = std::unique_lock<std::mutex>(fk->launch);
+  const bool fork = fk && cudaEventRecord(fk->ready, st) == cudaSuccess && cudaStreamWaitEvent(fk->side, fk->ready, 0) == cudaSuccess;
   attn_bwd_dq_tc_kernel<D, T><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), BWD_THREADS, smem_q, st>>>(p);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, st>>>(p);
-  return cudaGetLastError();
+  cudaStream_t sk = fork ? fk->side : st;
+  attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, sk>>>(p);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  if (fork) {
+    if ((e = cudaEventRecord(fk->done, fk->side)) != cudaSuccess) return e;
+    if ((e = cudaStreamWaitEvent(st, fk->done, 0)) != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 template <typename T>
