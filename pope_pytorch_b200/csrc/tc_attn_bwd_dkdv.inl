@@ -426,7 +426,7 @@ size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
 // life of the process.  Without them (creation failed) both kernels run on the caller's stream.
 struct BwdFork {
   cudaStream_t side;
-  cudaEvent_t ready, done;
+  cudaEvent_t begin, stats, ready, done;
   std::mutex launch;   // the events are shared by all calls on the device: one fork / join sequence at a time
 };
 static BwdFork* bwd_fork() {
@@ -440,6 +440,8 @@ static BwdFork* bwd_fork() {
   if (state[dev] == 0) {
     BwdFork& f = forks[dev];
     const bool ok = cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) == cudaSuccess &&
+                    cudaEventCreateWithFlags(&f.begin, cudaEventDisableTiming) == cudaSuccess &&
+                    cudaEventCreateWithFlags(&f.stats, cudaEventDisableTiming) == cudaSuccess &&
                     cudaEventCreateWithFlags(&f.ready, cudaEventDisableTiming) == cudaSuccess &&
                     cudaEventCreateWithFlags(&f.done, cudaEventDisableTiming) == cudaSuccess;
     state[dev] = ok ? 1 : -1;
@@ -461,6 +463,20 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   uint8_t* gimg = vimg + up256(image_bytes(s.B * s.Hk, s.Nk, s.d));
   float* rowstat = reinterpret_cast<float*>(gimg + up256(image_bytes(s.B * s.H, s.Nq, s.d)));
   cudaError_t e;
+  // Two independent strands run on two streams: a library-owned side stream forks from the caller's stream, takes the
+  // row statistics while the caller's stream builds tables and images, and later the dk/dv kernel while the caller's
+  // stream runs the dq kernel (its CTAs fill the SMs which the dq kernel's last partial wave leaves idle); the
+  // caller's stream waits for it at the end.  All events are shared per device, hence the lock.
+  BwdFork* fk = bwd_fork();
+  std::unique_lock<std::mutex> fork_lock;
+  if (fk) fork_lock = std::unique_lock<std::mutex>(fk->launch);
+  const bool fork = fk && cudaEventRecord(fk->begin, st) == cudaSuccess && cudaStreamWaitEvent(fk->side, fk->begin, 0) == cudaSuccess;
+  cudaStream_t sk = fork ? fk->side : st;
+  bwd_rowstat_kernel<T><<<dim3((unsigned)image_tiles(s.Nq), s.B * s.H), 256, 0, sk>>>(
+      static_cast<const T*>(a.out), Strides(a.so), static_cast<const T*>(a.dout), Strides(a.sdo), a.lse, s.H, s.Nq, s.d, delta,
+      rowstat);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  if (fork && (e = cudaEventRecord(fk->stats, sk)) != cudaSuccess) return e;
   if (s.r > 0 && (e = launch_trig_tables(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, tt.ctab, tt.stab, tt.ch, tt.sh, st)) != cudaSuccess) return e;
   // K' (phase bias folded in), Q', and V / dO as the same tiles without rotated features (a pure re-layout)
   ExpandJobs jobs;
@@ -469,10 +485,6 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   jobs.job[2] = expand_job(a.v, a.sv, s.B, s.Hk, s.Nk, 0, 0, nullptr, 0, vimg);
   jobs.job[3] = expand_job(a.dout, a.sdo, s.B, s.H, s.Nq, 0, 0, nullptr, 0, gimg);
   if ((e = launch_expand_images(jobs, 4, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
-  bwd_rowstat_kernel<T><<<dim3((unsigned)image_tiles(s.Nq), s.B * s.H), 256, 0, st>>>(
-      static_cast<const T*>(a.out), Strides(a.so), static_cast<const T*>(a.dout), Strides(a.sdo), a.lse, s.H, s.Nq, s.d, delta,
-      rowstat);
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
   TcBwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
   p.scale = a.softmax_scale, p.scale_log2 = a.softmax_scale * LOG2E;
@@ -494,15 +506,13 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;
   if ((e = cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(attn_bwd_dkdv_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k)) != cudaSuccess) return e;
-  // The two kernels are independent of each other: the dk/dv kernel goes to a side stream that forks from and joins
-  // the caller's stream, so that its CTAs fill the SMs which the last (partial) wave of the dq kernel leaves idle.
-  BwdFork* fk = bwd_fork();
-  std::unique_lock<std::mutex> fork_lock;
-  if (fk) fork_lock = std::unique_lock<std::mutex>(fk->launch);
-  const bool fork = fk && cudaEventRecord(fk->ready, st) == cudaSuccess && cudaStreamWaitEvent(fk->side, fk->ready, 0) == cudaSuccess;
+  if (fork) {   // images -> side stream (dk/dv); row statistics -> caller's stream (dq reads delta)
+    if ((e = cudaEventRecord(fk->ready, st)) != cudaSuccess) return e;
+    if ((e = cudaStreamWaitEvent(fk->side, fk->ready, 0)) != cudaSuccess) return e;
+    if ((e = cudaStreamWaitEvent(st, fk->stats, 0)) != cudaSuccess) return e;
+  }
   attn_bwd_dq_tc_kernel<D, T><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), BWD_THREADS, smem_q, st>>>(p);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  cudaStream_t sk = fork ? fk->side : st;
   attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, sk>>>(p);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   if (fork) {
