@@ -8,8 +8,8 @@
  *
  * Conventions shared by every entry point
  *   - All tensor pointers are DEVICE pointers on the current CUDA device.  The caller owns
- *     and allocates every input, output and workspace; the library never allocates or frees
- *     device memory and never synchronises the device.
+ *     and allocates every input, output and workspace; the operator entry points never allocate
+ *     or free device memory and never synchronise the device.
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
  *   - Tensors are addressed as base + b*stride.b + h*stride.h + n*stride.n + feature, strides
  *     in ELEMENTS, innermost (feature / key) dimension contiguous.  Both the (b,h,n,d) and
@@ -21,9 +21,21 @@
  *   - `bias` is fp32 (Hk, r): the per-key-head phase added to the key side only
  *     (PoPE_pytorch/pope.py:56).  Query head h reads key/value/bias head h % Hk
  *     (PoPE_pytorch/attention.py:44-45,118-120).
- *   - Return value: POPE_OK or a negative PopeStatus.  Nothing is launched on error.
- *   - Thread-safe and re-entrant; calls on different streams may overlap, except where an
- *     entry point documents shared state.
+ *   - Return value: POPE_OK or a negative PopeStatus.  Argument errors are detected before
+ *     anything is launched.
+ *   - Thread-safe: any number of host threads may call concurrently, on the same or on different
+ *     streams and devices.  State the library keeps per device for the life of the process:
+ *       * one 4-byte sticky status word (see pope_b200_device_status), written only when a
+ *         kernel's bounded wait gives up;
+ *       * for pope_b200_attn_bwd on the tensor-core path, up to four (side stream + four events)
+ *         sets created on first use.  A call borrows one set only while it ENQUEUES work: it
+ *         forks the side stream off `stream` with an event, runs part of its kernels there and
+ *         joins it back into `stream` before returning -- on error returns too -- so everything
+ *         the call launches is ordered inside `stream` exactly like a single launch, and the
+ *         sequence can be captured into a CUDA graph.  With all sets in use the call runs on
+ *         `stream` alone.  No lock is held while the GPU executes;
+ *       * the fixed scratch array of pope_b200_attn_fwd_noalloc (documented there).
+ *     Kernel attributes (dynamic shared-memory opt-in) are set once per kernel and device.
  */
 #ifndef POPE_B200_H_
 #define POPE_B200_H_
@@ -35,7 +47,7 @@
 extern "C" {
 #endif
 
-#define POPE_B200_ABI_VERSION 1
+#define POPE_B200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define POPE_API __attribute__((visibility("default")))
@@ -175,6 +187,16 @@ POPE_API const char* pope_b200_last_path(void);
  * this call synchronises the device. */
 POPE_API int pope_b200_device_status(void);
 
+/* Reset that word to 0 on the current device (synchronises the device).  POPE_OK or POPE_ERR_CUDA. */
+POPE_API int pope_b200_clear_device_status(void);
+
+/* Diagnostic, not an operator: launches one tiny kernel on `stream` whose only mbarrier is never
+ * completed, waited on with the same bounded wait the real kernels use but a limit of a few
+ * microseconds.  The kernel gives up, sets bit 0 of the status word, frees its tensor memory and
+ * returns; the device stays healthy.  It exists so that the give-up path can be tested without
+ * faulting or hanging a GPU.  Follow it with pope_b200_clear_device_status(). */
+POPE_API int pope_b200_selftest_bounded_wait(void* stream);
+
 /* Bytes of workspace the operator needs for these arguments (`args` points at the matching
  * Pope*Args struct; pointers inside it are not dereferenced).  0 = none. */
 POPE_API size_t pope_b200_workspace_bytes(int op, const void* args);
@@ -198,9 +220,9 @@ POPE_API int pope_b200_attn_bwd(const PopeAttnBwdArgs* args, void* stream);
  *   - Only the tensor-core shapes are served (bf16/fp16, d in {64,96,128}, r % 16 == 0, Nq >= 64,
  *     2-D freqs, 16-byte aligned rows); anything else returns POPE_ERR_UNSUPPORTED.
  *   - The scratch a call needs is what pope_b200_workspace_bytes reports for the forward
- *     (8 Nk r bytes of table plus 2 (d + r) bytes per query and key row of every head, rows
- *     padded to a multiple of 256); more than POPE_B200_NOALLOC_MAX_SCRATCH returns
- *     POPE_ERR_TOO_LARGE and launches nothing.  Every GPU that loads the library holds that many
+ *     (12 Nk r bytes of table -- fp32 and fp16 copies of cos and sin -- rounded up to 256, plus
+ *     2 (d + r) bytes per query and key row of every head, rows padded to a multiple of 256);
+ *     more than POPE_B200_NOALLOC_MAX_SCRATCH returns POPE_ERR_TOO_LARGE and launches nothing.  Every GPU that loads the library holds that many
  *     bytes until the process exits.
  *   - The first call on each device looks up the array's device address (a one-time runtime
  *     query made with that device current).  Make that first call outside any stream capture.

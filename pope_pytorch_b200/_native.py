@@ -17,8 +17,7 @@ from typing import Optional
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-# POPE_B200_LIBRARY points the loader at another build of the same ABI (e.g. one compiled with debug defines)
-LIB_PATH = os.environ.get("POPE_B200_LIBRARY") or os.path.join(_PKG_DIR, "libpope_b200.so")
+LIB_PATH = os.path.join(_PKG_DIR, "libpope_b200.so")
 
 OP_SIM_FWD, OP_SIM_BWD, OP_ATTN_FWD, OP_ATTN_BWD = 0, 1, 2, 3
 _DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -72,7 +71,9 @@ class AttnBwdArgs(C.Structure):
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
+ABI_VERSION = 2
 EXPORTS = ("pope_b200_abi_version", "pope_b200_status_str", "pope_b200_last_path", "pope_b200_device_status",
+           "pope_b200_clear_device_status", "pope_b200_selftest_bounded_wait",
            "pope_b200_workspace_bytes", "pope_b200_attn_fwd_noalloc",
            "pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd")
 
@@ -80,15 +81,7 @@ _lib = None
 _load_error: Optional[str] = None
 
 
-def load_library():
-    """dlopen the in-tree library once; raises RuntimeError when it is missing or stale."""
-    global _lib, _load_error
-    if _lib is not None:
-        return _lib
-    if not os.path.exists(LIB_PATH):
-        _load_error = f"{LIB_PATH} is missing: build it with `python -m pope_pytorch_b200.build`"
-        raise RuntimeError(_load_error)
-    lib = C.CDLL(LIB_PATH)
+def _bind(lib):
     lib.pope_b200_abi_version.restype = C.c_int
     lib.pope_b200_status_str.restype = C.c_char_p
     lib.pope_b200_status_str.argtypes = [C.c_int]
@@ -99,8 +92,29 @@ def load_library():
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.c_void_p, C.c_void_p]
-    if lib.pope_b200_abi_version() != 1:
+    lib.pope_b200_device_status.restype = C.c_int
+    lib.pope_b200_clear_device_status.restype = C.c_int
+    lib.pope_b200_selftest_bounded_wait.restype = C.c_int
+    lib.pope_b200_selftest_bounded_wait.argtypes = [C.c_void_p]
+    lib.pope_b200_attn_fwd_noalloc.restype = C.c_int
+    lib.pope_b200_attn_fwd_noalloc.argtypes = [C.c_void_p, C.c_void_p]
+    if lib.pope_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("libpope_b200.so has an unexpected ABI version; rebuild it")
+    return lib
+
+
+def load_library():
+    """dlopen the in-tree library once; raises RuntimeError when it is missing or stale."""
+    global _lib, _load_error
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        _load_error = f"{LIB_PATH} is missing: build it with `python -m pope_pytorch_b200.build`"
+        raise RuntimeError(_load_error)
+    try:
+        lib = _bind(C.CDLL(LIB_PATH))
+    except AttributeError as exc:     # a symbol of the current header is missing: the build is stale
+        raise RuntimeError(f"{LIB_PATH} is stale ({exc}); rebuild it with `python -m pope_pytorch_b200.build`") from exc
     _lib = lib
     return lib
 
@@ -119,9 +133,21 @@ def last_path() -> str:
 
 def device_status() -> int:
     """Sticky health word of the tensor-core kernels on the current device (synchronises)."""
-    lib = load_library()
-    lib.pope_b200_device_status.restype = C.c_int
-    return lib.pope_b200_device_status()
+    return load_library().pope_b200_device_status()
+
+
+def clear_device_status() -> None:
+    """Reset the sticky health word of the current device (synchronises)."""
+    _check(load_library().pope_b200_clear_device_status(), "pope_b200_clear_device_status")
+
+
+def selftest_bounded_wait(device=None) -> None:
+    """Launch the diagnostic kernel whose only barrier never completes: it gives up after a few
+    microseconds and sets bit 0 of the status word (see include/pope_b200.h)."""
+    dev = torch.device("cuda" if device is None else device)
+    with torch.cuda.device(dev):
+        _check(load_library().pope_b200_selftest_bounded_wait(torch.cuda.current_stream(dev).cuda_stream),
+               "pope_b200_selftest_bounded_wait")
 
 
 def _check(rc: int, what: str) -> None:
@@ -339,8 +365,6 @@ def attn_forward_noalloc(q, k, v, freqs, bias, mask, causal, scale, out, lse):
     Raises RuntimeError when the shape is not served or needs more than NOALLOC_MAX_SCRATCH.
     Calls that overlap on the GPU share the scratch and race; keep them on one stream."""
     lib = load_library()
-    lib.pope_b200_attn_fwd_noalloc.restype = C.c_int
-    lib.pope_b200_attn_fwd_noalloc.argtypes = [C.c_void_p, C.c_void_p]
     r = freqs.shape[-1]
     m8 = _mask_u8(mask)
     a = AttnArgs(C.sizeof(AttnArgs), int(causal), float(scale), 0, _shape(q, k, r), _embed_struct(freqs, bias, r),
@@ -373,7 +397,12 @@ class _FlashAttn(torch.autograd.Function):
         return dq, dk, dv, dfreqs, dbias, None, None, None
 
 
-def flash_attn(q, k, v, freqs, bias, mask=None, causal=False, softmax_scale=None):
-    """Differentiable fused PoPE attention on head-first (b,h,n,d) views."""
+def flash_attn(q, k, v, freqs=None, bias=None, mask=None, causal=False, softmax_scale=None):
+    """Differentiable fused PoPE attention on head-first (b,h,n,d) views.  Without ``freqs`` /
+    ``bias`` this is plain softmax attention, as the seam it replaces behaves with ``HAS_POPE``
+    off (PoPE_pytorch/triton_pope_flash_attn.py:364-373): the kernels run with zero rotated dims."""
     scale = q.shape[-1] ** -0.5 if softmax_scale is None else softmax_scale
+    if freqs is None or bias is None:
+        freqs = torch.empty(k.shape[2], 0, dtype=torch.float32, device=q.device)
+        bias = torch.empty(k.shape[1], 0, dtype=torch.float32, device=q.device)
     return _FlashAttn.apply(q, k, v, freqs, bias, mask, causal, scale)

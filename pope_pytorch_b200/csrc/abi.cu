@@ -42,6 +42,10 @@ int check_embed(const PopeShape& s, const PopeEmbed& e) {
 
 }  // namespace
 
+namespace pope {
+void note_last_path(const char* family) { g_last_path = family; }
+}  // namespace pope
+
 extern "C" {
 
 int pope_b200_abi_version(void) { return POPE_B200_ABI_VERSION; }
@@ -63,6 +67,14 @@ const char* pope_b200_status_str(int status) {
 const char* pope_b200_last_path(void) { return g_last_path; }
 
 int pope_b200_device_status(void) { return static_cast<int>(pope::tc_read_status()); }
+
+int pope_b200_clear_device_status(void) { return pope::tc_clear_status() == cudaSuccess ? POPE_OK : POPE_ERR_CUDA; }
+
+int pope_b200_selftest_bounded_wait(void* stream) {
+  int rc = check_device();
+  if (rc != POPE_OK) return rc;
+  return pope::tc_selftest_bounded_wait(static_cast<cudaStream_t>(stream)) == cudaSuccess ? POPE_OK : POPE_ERR_CUDA;
+}
 
 size_t pope_b200_workspace_bytes(int op, const void* args) {
   if (!args) return 0;

@@ -25,6 +25,11 @@ bool attn_bwd_tc_supported(const PopeAttnBwdArgs& a);
 size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a);
 cudaError_t attn_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st);
 unsigned int tc_read_status();  // sticky device-side status of the tensor-core kernels (synchronises)
+cudaError_t tc_clear_status();  // zero that word on the current device (synchronises)
+// one CTA that waits on an mbarrier nobody completes, with a tiny try limit: exercises the give-up path of the bounded
+// waits (status bit 0 set, TMEM freed, kernel returns) without faulting or hanging the device
+cudaError_t tc_selftest_bounded_wait(cudaStream_t st);
+void note_last_path(const char* family);  // what pope_b200_last_path() reports on this thread
 
 // delta[b,h,i] = sum_c out[i,c] * dout[i,c]  (fp32, (B,H,Nq) contiguous); used by every backward
 cudaError_t attn_bwd_delta(const PopeAttnBwdArgs& a, float* delta, cudaStream_t st);

@@ -422,32 +422,65 @@ size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
          up256(image_bytes(s.B * s.H, s.Nq, s.d)) + rowstat_bytes(s);
 }
 
-// Side stream and fork / join events of the backward, one set per device, created on first use and kept for the
-// life of the process.  Without them (creation failed) both kernels run on the caller's stream.
+// Side streams and fork / join events of the backward: a small pool per device, created on first use and kept for
+// the life of the process.  A call borrows one slot for the time it ENQUEUES its work (the slot's mutex is never held
+// while the GPU runs), so host threads that call the backward at the same time on one device do not wait for each
+// other; when every slot is taken, or none could be created, both kernels simply run on the caller's stream.
 struct BwdFork {
-  cudaStream_t side;
-  cudaEvent_t begin, stats, ready, done;
-  std::mutex launch;   // the events are shared by all calls on the device: one fork / join sequence at a time
+  cudaStream_t side = nullptr;
+  cudaEvent_t begin = nullptr, stats = nullptr, ready = nullptr, done = nullptr;
+  std::mutex busy;
+  int state = 0;   // 0 = not tried, 1 = usable, -1 = unavailable
 };
-static BwdFork* bwd_fork() {
+constexpr int kForkSlots = 4;
+static BwdFork* bwd_fork_pool() {
   constexpr int kMaxDevices = 64;
-  static std::mutex mu;
-  static BwdFork forks[kMaxDevices];
-  static int state[kMaxDevices] = {};   // 0 = not tried, 1 = usable, -1 = unavailable
+  static BwdFork forks[kMaxDevices][kForkSlots];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-  std::lock_guard<std::mutex> lock(mu);
-  if (state[dev] == 0) {
-    BwdFork& f = forks[dev];
-    const bool ok = cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) == cudaSuccess &&
-                    cudaEventCreateWithFlags(&f.begin, cudaEventDisableTiming) == cudaSuccess &&
-                    cudaEventCreateWithFlags(&f.stats, cudaEventDisableTiming) == cudaSuccess &&
-                    cudaEventCreateWithFlags(&f.ready, cudaEventDisableTiming) == cudaSuccess &&
-                    cudaEventCreateWithFlags(&f.done, cudaEventDisableTiming) == cudaSuccess;
-    state[dev] = ok ? 1 : -1;
-  }
-  return state[dev] == 1 ? &forks[dev] : nullptr;
+  return forks[dev];
 }
+// Borrowed slot with the fork open: the destructor joins the side stream back into the caller's stream on EVERY
+// path out of the launch function, error returns included, so the caller's stream always orders after whatever
+// was enqueued on the side stream.
+class ForkGuard {
+ public:
+  explicit ForkGuard(cudaStream_t st) : st_(st) {
+    BwdFork* pool = bwd_fork_pool();
+    for (int i = 0; pool && i < kForkSlots && !fk_; ++i) {
+      std::unique_lock<std::mutex> lk(pool[i].busy, std::try_to_lock);
+      if (!lk.owns_lock()) continue;
+      BwdFork& f = pool[i];
+      if (f.state == 0) {
+        const bool ok = cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) == cudaSuccess &&
+                        cudaEventCreateWithFlags(&f.begin, cudaEventDisableTiming) == cudaSuccess &&
+                        cudaEventCreateWithFlags(&f.stats, cudaEventDisableTiming) == cudaSuccess &&
+                        cudaEventCreateWithFlags(&f.ready, cudaEventDisableTiming) == cudaSuccess &&
+                        cudaEventCreateWithFlags(&f.done, cudaEventDisableTiming) == cudaSuccess;
+        f.state = ok ? 1 : -1;
+      }
+      if (f.state != 1) continue;
+      if (cudaEventRecord(f.begin, st) != cudaSuccess || cudaStreamWaitEvent(f.side, f.begin, 0) != cudaSuccess) continue;
+      fk_ = &f, lock_ = std::move(lk);
+    }
+  }
+  ~ForkGuard() { join(); }
+  bool forked() const { return fk_ != nullptr; }
+  BwdFork* operator->() const { return fk_; }
+  cudaStream_t side() const { return fk_ ? fk_->side : st_; }
+  cudaError_t join() {
+    if (!fk_) return cudaSuccess;
+    cudaError_t e = cudaEventRecord(fk_->done, fk_->side);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(st_, fk_->done, 0);
+    fk_ = nullptr;
+    lock_.unlock();
+    return e;
+  }
+ private:
+  cudaStream_t st_;
+  BwdFork* fk_ = nullptr;
+  std::unique_lock<std::mutex> lock_;
+};
 
 template <int D, typename T>
 static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
@@ -466,12 +499,10 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   // Two independent strands run on two streams: a library-owned side stream forks from the caller's stream, takes the
   // row statistics while the caller's stream builds tables and images, and later the dk/dv kernel while the caller's
   // stream runs the dq kernel (its CTAs fill the SMs which the dq kernel's last partial wave leaves idle); the
-  // caller's stream waits for it at the end.  All events are shared per device, hence the lock.
-  BwdFork* fk = bwd_fork();
-  std::unique_lock<std::mutex> fork_lock;
-  if (fk) fork_lock = std::unique_lock<std::mutex>(fk->launch);
-  const bool fork = fk && cudaEventRecord(fk->begin, st) == cudaSuccess && cudaStreamWaitEvent(fk->side, fk->begin, 0) == cudaSuccess;
-  cudaStream_t sk = fork ? fk->side : st;
+  // caller's stream waits for it at the end.
+  ForkGuard fk(st);
+  const bool fork = fk.forked();
+  cudaStream_t sk = fk.side();
   bwd_rowstat_kernel<T><<<dim3((unsigned)image_tiles(s.Nq), s.B * s.H), 256, 0, sk>>>(
       static_cast<const T*>(a.out), Strides(a.so), static_cast<const T*>(a.dout), Strides(a.sdo), a.lse, s.H, s.Nq, s.d, delta,
       rowstat);
@@ -504,8 +535,8 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;
-  if ((e = cudaFuncSetAttribute(attn_bwd_dq_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q)) != cudaSuccess) return e;
-  if ((e = cudaFuncSetAttribute(attn_bwd_dkdv_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_k)) != cudaSuccess) return e;
+  if ((e = ensure_max_smem<attn_bwd_dq_tc_kernel<D, T>>()) != cudaSuccess) return e;
+  if ((e = ensure_max_smem<attn_bwd_dkdv_tc_kernel<D, T>>()) != cudaSuccess) return e;
   if (fork) {   // images -> side stream (dk/dv); row statistics -> caller's stream (dq reads delta)
     if ((e = cudaEventRecord(fk->ready, st)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(fk->side, fk->ready, 0)) != cudaSuccess) return e;
@@ -515,11 +546,7 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, sk>>>(p);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  if (fork) {
-    if ((e = cudaEventRecord(fk->done, fk->side)) != cudaSuccess) return e;
-    if ((e = cudaStreamWaitEvent(st, fk->done, 0)) != cudaSuccess) return e;
-  }
-  return cudaSuccess;
+  return fk.join();
 }
 
 template <typename T>

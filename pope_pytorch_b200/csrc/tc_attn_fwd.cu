@@ -38,6 +38,11 @@ unsigned int tc_read_status() {
   return v;
 }
 
+cudaError_t tc_clear_status() {
+  const unsigned int zero = 0;
+  return cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(zero));
+}
+
 bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
                      int64_t sh, int64_t sb, int box_rows) {
   typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -53,12 +58,14 @@ bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, in
       encode = reinterpret_cast<EncodeFn>(fn);
   });
   if (!encode) return false;
-  // a size-1 axis may come with any stride: give it a valid dummy (multiple of 16 bytes, increasing)
+  // a size-1 axis may come with any stride: give it a valid dummy (multiple of 16 bytes, increasing); an axis with
+  // more entries must come with a usable stride
   cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
   int64_t st[3] = {sn, sh, sb};
-  if (rows == 1 || st[0] <= 0) st[0] = d;
-  if (heads == 1 || st[1] <= 0) st[1] = st[0] * rows;
-  if (batch == 1 || st[2] <= 0) st[2] = st[1] * heads;
+  if ((rows > 1 && st[0] < d) || (heads > 1 && st[1] <= 0) || (batch > 1 && st[2] <= 0)) return false;
+  if (rows == 1) st[0] = d;
+  if (heads == 1) st[1] = st[0] * rows;
+  if (batch == 1) st[2] = st[1] * heads;
   cuuint64_t strides[3] = {(cuuint64_t)st[0] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[2] * 2};
   for (int i = 0; i < 3; ++i)
     if (strides[i] % 16 != 0) return false;
@@ -108,7 +115,10 @@ enum {
   B_PFULL = 8,   // [buf][row tile] probabilities written to TMEM (4 softmax warps)
   B_QFULL = 12,  // the resident Q' tiles are in shared memory
   B_SFULL = 13,  // [buf][row tile] scores of one row tile written to TMEM (tcgen05.commit)
-  B_COUNT = 17
+  B_ODONE = 17,  // [row tile] the last O += P V of that row tile has completed: one phase per barrier, so the epilogue's
+                 //     wait cannot alias with a later completion (B_PVDONE of a buffer completes again two steps later
+                 //     for the other row tile when the causal mask ends tile 0 early)
+  B_COUNT = 19
 };
 
 template <int D, typename T>
@@ -147,6 +157,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
     }
     for (int i = 0; i < 4; ++i) mbar_init(&bars[B_PFULL + i], 4), mbar_init(&bars[B_SFULL + i], 1);
     mbar_init(&bars[B_QFULL], 1);
+    mbar_init(&bars[B_ODONE], 1), mbar_init(&bars[B_ODONE + 1], 1);
     mbar_init_fence();
   }
   fence_before_sync();
@@ -234,6 +245,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
 #pragma unroll
           for (int ks = 0; ks < TK / 16; ++ks)
             mma_ts_lh(d, a + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+          if (j == (t == 0 ? T0 : T1) - 1) mma_commit(&bars[B_ODONE + t]);
         }
         mma_commit(&bars[B_PVDONE + buf]);
       }
@@ -349,8 +361,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
 
     // ---- epilogue: O / l, LSE ---------------------------------------------------------------------
     if (T_mine > 0) {
-      const int jl = T_mine - 1;
-      if (!failed) failed = !mbar_wait(&bars[B_PVDONE + (jl & 1)], (jl >> 1) & 1, WAIT_LIMIT);
+      if (!failed) failed = !mbar_wait(&bars[B_ODONE + tile], 0, WAIT_LIMIT);
       fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const uint32_t o_addr = tmem + lane_base + 256 + tile * 128;
@@ -395,6 +406,9 @@ bool attn_fwd_tc_supported(const PopeAttnArgs& a) {
   if (s.r > 0 && (a.embed.sf.b != 0 || a.embed.sf.h != 0)) return false;  // one phase table for all units
   if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.out)) return false;
   if (!stride_ok(a.sq) || !stride_ok(a.sk) || !stride_ok(a.sv) || !stride_ok(a.so)) return false;
+  // V is read by TMA boxes over (feature, row, head, batch): an axis with more than one entry needs a real, positive
+  // stride (a V expanded over heads or batch, stride 0, or overlapping rows go to the exact family instead)
+  if ((s.Hk > 1 && a.sv.h <= 0) || (s.B > 1 && a.sv.b <= 0) || (s.Nk > 1 && a.sv.n < s.d)) return false;
   return true;
 }
 
@@ -435,8 +449,7 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   // every CTA allocates all 512 TMEM columns: ask for more than half of the SM's shared memory so
   // that two CTAs are never co-resident
   if (smem < 120 * 1024) smem = 120 * 1024;
-  e = cudaFuncSetAttribute(attn_fwd_tc_kernel<D, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
+  if ((e = ensure_max_smem<attn_fwd_tc_kernel<D, T>>()) != cudaSuccess) return e;
   dim3 grid((s.Nq + 2 * TQ - 1) / (2 * TQ), s.B * s.H);
   attn_fwd_tc_kernel<D, T><<<grid, FWD_THREADS, smem, st>>>(p, tmap_v);
   return cudaGetLastError();
@@ -493,7 +506,9 @@ extern "C" int pope_b200_attn_fwd_noalloc(const PopeAttnArgs* args, void* stream
   if (!args || args->struct_bytes != sizeof(PopeAttnArgs)) return POPE_ERR_BAD_ARG;
   const PopeShape& s = args->shape;
   if (s.B <= 0 || s.H <= 0 || s.Hk <= 0 || s.Nq <= 0 || s.Nk <= 0 || s.d <= 0 || s.r < 0) return POPE_ERR_BAD_ARG;
-  if (s.H % s.Hk != 0 || s.Nq > s.Nk || s.r > s.d || (int64_t)s.B * s.H > 65535) return POPE_ERR_BAD_ARG;
+  if (s.H % s.Hk != 0 || s.Nq > s.Nk || s.r > s.d) return POPE_ERR_BAD_ARG;
+  if (s.dtype != POPE_F32 && s.dtype != POPE_BF16 && s.dtype != POPE_F16) return POPE_ERR_BAD_ARG;
+  if ((int64_t)s.B * s.H > 65535) return POPE_ERR_UNSUPPORTED;
   if (!args->q || !args->k || !args->v || !args->out || !args->lse) return POPE_ERR_BAD_ARG;
   if (s.r > 0 && (!args->embed.freqs || !args->embed.bias)) return POPE_ERR_BAD_ARG;
   if (!attn_fwd_tc_supported(*args)) return POPE_ERR_UNSUPPORTED;
@@ -508,5 +523,7 @@ extern "C" int pope_b200_attn_fwd_noalloc(const PopeAttnArgs* args, void* stream
   PopeAttnArgs local = *args;
   local.workspace = scratch;              // the kernel must get the looked-up address, never the symbol
   local.workspace_bytes = kStaticScratchBytes;
-  return attn_fwd_tc(local, static_cast<cudaStream_t>(stream)) == cudaSuccess ? POPE_OK : POPE_ERR_CUDA;
+  if (attn_fwd_tc(local, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  note_last_path("tcgen05");
+  return POPE_OK;
 }

@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include <atomic>
 #include <cstdio>
 
 #include <cuda.h>   // CUtensorMap (types only; the encoder is fetched through the runtime's driver entry point)
@@ -15,6 +16,22 @@
 namespace pope {
 
 using namespace tc;
+
+// Opt a kernel into the full 227 KB of dynamic shared memory once per (kernel instantiation, device) instead of
+// on every launch.  `Kernel` is the kernel function itself (a template VALUE parameter: instantiations share one
+// function-pointer type), so every instantiation gets its own flag word, one bit per device.
+constexpr int kMaxDynamicSmem = 227 * 1024;
+template <auto Kernel>
+inline cudaError_t ensure_max_smem() {
+  static std::atomic<uint64_t> done{0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && ((done.load(std::memory_order_acquire) >> dev) & 1ull)) return cudaSuccess;
+  e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
+  if (e == cudaSuccess && dev >= 0 && dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
+  return e;
+}
 
 // device address of the sticky status word (bit 0 = a bounded wait gave up) on the current device
 unsigned int* tc_status_ptr();
@@ -48,28 +65,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
-}
-
-// softplus with ONE special-function op: t = 2^(-|x| log2 e), log1p(t) = t * q(t) with a degree-5
-// polynomial q (relative error 1.8e-5 on (0, 1]); the operand is rounded to 8 or 11 bits afterwards.
-__device__ __forceinline__ float softplus_poly(float x) {
-  const float t = ex2_approx(-fabsf(x) * LOG2E);
-  float q = fmaf(t, -0.023689253f, 0.10028721f);
-  q = fmaf(t, q, -0.20866966f);
-  q = fmaf(t, q, 0.32441181f);
-  q = fmaf(t, q, -0.49918786f);
-  q = fmaf(t, q, 0.99998188f);
-  return fmaf(t, q, fmaxf(x, 0.f));
-}
-
-template <typename T> __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b);
-template <> __device__ __forceinline__ uint32_t mul2<__nv_bfloat16>(uint32_t a, uint32_t b) {
-  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-template <> __device__ __forceinline__ uint32_t mul2<__half>(uint32_t a, uint32_t b) {
-  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
 }
 
 // Tensor map of a (batch, head, row, feature) operand for box loads of `box_rows` rows x 8 features (one
@@ -131,20 +126,6 @@ __device__ __forceinline__ void copy_resident_tiles(uint8_t* dst, const uint8_t*
     bulk_load(dst + c * 2048 + hlf * 1024, img_tile0 + ((size_t)hlf * chunks + c) * 1024, 1024, bar);
   }
 }
-
-__device__ __forceinline__ float sigmoid_fast(float x) { return __frcp_rn(1.f + ex2_approx(-x * LOG2E)); }
-
-// Optional per-phase clock counters of one CTA, printed by the thread that collected them (build with
-// -DPOPE_DBG_PHASES; never part of a normal build).
-#ifdef POPE_DBG_PHASES
-#define PH_DECL long long _t0 = clock64(), _t1; long long _acc[8] = {}
-#define PH(i) do { _t1 = clock64(); _acc[i] += _t1 - _t0; _t0 = _t1; } while (0)
-#define PH_PRINT(tag, n) do { if (blockIdx.x == 7 && blockIdx.y == 3) printf("%s tiles %d: %lld %lld %lld %lld %lld %lld %lld %lld\n", tag, n, _acc[0] / (n), _acc[1] / (n), _acc[2] / (n), _acc[3] / (n), _acc[4] / (n), _acc[5] / (n), _acc[6] / (n), _acc[7] / (n)); } while (0)
-#else
-#define PH_DECL
-#define PH(i)
-#define PH_PRINT(tag, n)
-#endif
 
 // Chunk stride used where THREADS store 16-byte groups of a 64-row tile in row-major group order (the image
 // pre-pass): 16 bytes of padding per chunk column put the lanes of a warp, which hold consecutive chunks of one

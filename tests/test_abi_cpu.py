@@ -31,7 +31,7 @@ def test_exports_match_header(lib):
     assert set(N.EXPORTS) <= set(names) and len(names) >= 8
     for name in names:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
-    assert lib.pope_b200_abi_version() == 1
+    assert lib.pope_b200_abi_version() == N.ABI_VERSION
     assert lib.pope_b200_status_str(0) == b"ok"
     assert b"workspace" in lib.pope_b200_status_str(-4)
 
