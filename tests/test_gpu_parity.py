@@ -3,10 +3,17 @@ golden vectors, on identical seeded inputs.
 
 Tolerances (written where used): fp32 similarity 1e-4 relative to max|sim|; fp32 attention and
 fp32 gradients rtol 1e-3 / atol 1e-4 (the reference's own bound, tests/test_triton.py:50-54);
-bf16 / fp16 attention outputs and gradients 2e-2 absolute (widened to 2^-8 of the tensor's
-magnitude where that is larger, i.e. one bf16 rounding of the stored result).
+bf16 / fp16 attention outputs and gradients 2e-2 absolute on the value, checked ELEMENTWISE as
+|got - ref| <= 2e-2 + ulp/2 of that element's own storage format (2^-9 |ref_ij| in bf16, 2^-12 in
+fp16: the result is stored in 16 bits, which costs half an ulp of the element before any arithmetic
+error).  On the benchmark configurations out, dq and dk additionally meet the plain 2e-2 bound.
+Phase-bias and phase-table gradients are long reductions (up to 16384 x 4096 terms of 16-bit
+products): they are bounded relative to the largest entry, 1e-2.  The largest observed error of
+every tensor of every case is written to a JSON file next to the other run outputs.
 """
+import json
 import math
+import os
 
 import pytest
 import torch
@@ -31,6 +38,45 @@ def assert_close32(a, b, what, rtol=1e-3, atol=1e-4):
 
 def gen(shape, g, dtype=torch.float32):
     return torch.randn(*shape, generator=g).to(dtype)
+
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ERRORS_PATH = os.environ.get("POPE_PARITY_ERRORS", os.path.join(_ROOT, "gpurun_out", "parity_errors.json"))
+HALF_ULP = {torch.bfloat16: 2.0 ** -9, torch.float16: 2.0 ** -12, torch.float32: 0.0}
+REL_TOL = 1e-2      # phase-bias / phase-table gradients, relative to the largest reference entry
+
+
+def record_errors(case, errs):
+    """Merge the observed maximum errors of one case into the JSON record (best effort)."""
+    try:
+        os.makedirs(os.path.dirname(ERRORS_PATH), exist_ok=True)
+        data = json.load(open(ERRORS_PATH)) if os.path.exists(ERRORS_PATH) else {}
+        data[case] = {k: float(v) for k, v in errs.items()}
+        json.dump(data, open(ERRORS_PATH, "w"), indent=1, sort_keys=True)
+    except OSError:
+        pass
+
+
+def check16(name, got, ref, dtype, tol=2e-2, strict=False, errs=None, key=None):
+    """Elementwise |got - ref| <= tol + half an ulp of the element in its storage format; with
+    ``strict`` also the plain max |got - ref| <= tol.  Returns the largest error (and keeps the
+    running maximum in ``errs[key]`` before any assertion fires)."""
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    assert got.shape == ref.shape, name
+    err = (got - ref).abs()
+    worst = float(err.max()) if err.numel() else 0.0
+    if errs is not None:
+        errs[key or name] = max(errs.get(key or name, 0.0), worst)
+    bad = err > tol + HALF_ULP[dtype] * ref.abs()
+    assert not bool(bad.any()), f"{name}: {int(bad.sum())} elements beyond {tol} + half ulp, max err {worst}"
+    if strict:
+        assert worst <= tol, f"{name}: max err {worst} > {tol}"
+    return worst
+
+
+def rel_err(got, ref):
+    got, ref = got.detach().float().cpu(), ref.detach().float().cpu()
+    return float((got - ref).abs().max() / ref.abs().max().clamp_min(1.0)) if ref.numel() else 0.0
 
 
 # ------------------------------------------------------------------------------------------
@@ -114,7 +160,7 @@ def test_attention_golden_fp32(golden, tag):
 
 
 def run_case(b, h, hk, nq, nk, d, r, dtype, causal, masked, seed, freqs=None, bias_scale=6.0, seq_first=False,
-             want_dfreqs=False, tol=2e-2):
+             want_dfreqs=False, tol=2e-2, strict=False, name=None, row_sliced_dout=False):
     g = torch.Generator().manual_seed(seed)
     q, k, v = gen((b, h, nq, d), g, dtype), gen((b, hk, nk, d), g, dtype), gen((b, hk, nk, d), g, dtype)
     dout = gen((b, h, nq, d), g, dtype)
@@ -135,21 +181,32 @@ def run_case(b, h, hk, nq, nk, d, r, dtype, causal, masked, seed, freqs=None, bi
     out = flash_attn_with_pope(qg, kg, vg, pos_emb=(fg, bg), mask=None if mask is None else mask.to(DEV),
                                causal=causal, head_dimension_at_first=not seq_first)
     dg = dout.to(DEV)
+    if row_sliced_dout:   # upstream gradient as every second row of a larger buffer (feature axis contiguous)
+        big = torch.zeros(b, h, 2 * nq, d, dtype=dtype, device=DEV)
+        big[:, :, ::2] = dg
+        dg = big[:, :, ::2]
+        assert not dg.is_contiguous()
     out.backward(dg.transpose(1, 2) if seq_first else dg)
     fix = (lambda t: t.transpose(1, 2)) if seq_first else (lambda t: t)
-    errs = dict(out=maxerr(fix(out), ref["out"]), dq=maxerr(fix(qg.grad), ref["dq"]), dk=maxerr(fix(kg.grad), ref["dk"]),
-                dv=maxerr(fix(vg.grad), ref["dv"]))
-    if r > 0:
-        errs["dbias_rel"] = maxerr(bg.grad, ref["dbias"]) / max(1.0, float(ref["dbias"].abs().max()))
-        if want_dfreqs:
-            errs["dfreqs_rel"] = maxerr(fg.grad, ref["dfreqs"]) / max(1.0, float(ref["dfreqs"].abs().max()))
     assert out.dtype == dtype and not torch.isnan(out.float()).any()
-    for name, e in errs.items():
-        # the tolerance applies to the value; storing it in a 16-bit format costs another half ulp, up to
-        # 2^-9 of its magnitude in bf16 (|dv| reaches 4-8 where grouped heads sum several query heads)
-        mag = float(ref[name].abs().max()) if (name in ref and dtype != torch.float32) else 0.0
-        bound = tol + 2.0 ** -9 * mag
-        assert e <= bound, f"{name}: {e} > {bound} (all: {errs})"
+    errs = {}
+    try:
+        for nm, got in (("out", out), ("dq", qg.grad), ("dk", kg.grad), ("dv", vg.grad)):
+            if dtype == torch.float32:
+                errs[nm] = maxerr(fix(got), ref[nm])
+                assert errs[nm] <= tol, f"{nm}: {errs[nm]} > {tol}"
+            else:
+                check16(nm, fix(got), ref[nm], dtype, tol=tol, strict=strict and nm != "dv", errs=errs)
+        if r > 0:
+            errs["dbias_rel"] = rel_err(bg.grad, ref["dbias"])
+            errs["dbias_abs"] = maxerr(bg.grad, ref["dbias"])
+            assert errs["dbias_rel"] <= REL_TOL, f"dbias: {errs}"
+            if want_dfreqs:
+                errs["dfreqs_rel"] = rel_err(fg.grad, ref["dfreqs"])
+                assert errs["dfreqs_rel"] <= REL_TOL, f"dfreqs: {errs}"
+    finally:
+        if name:
+            record_errors(name, errs)
     return errs
 
 
@@ -176,13 +233,15 @@ def test_attention_gqa_bf16():
 
 def test_attention_config2_causal_with_padding():
     """(2,8,1024,64) bf16, PoPE dim 32, causal + key-padding prefix lengths in [512,1024]."""
-    run_case(2, 8, 8, 1024, 1024, 64, 32, torch.bfloat16, causal=True, masked=True, seed=1002)
+    run_case(2, 8, 8, 1024, 1024, 64, 32, torch.bfloat16, causal=True, masked=True, seed=1002, strict=True,
+             name="config2_fwd_bwd_causal_padding_bf16")
 
 
 def test_attention_config4_axial_video():
     """AxialPoPE(96, axial (32,32,32)) on an (8,16,16) grid, (2,8,2048,96) bf16, non-causal."""
     freqs = AxialPoPE(96, heads=8, axial_dims=(32, 32, 32))((8, 16, 16)).freqs
-    run_case(2, 8, 8, 2048, 2048, 96, 96, torch.bfloat16, causal=False, masked=False, seed=1004, freqs=freqs)
+    run_case(2, 8, 8, 2048, 2048, 96, 96, torch.bfloat16, causal=False, masked=False, seed=1004, freqs=freqs,
+             strict=True, name="config4_axial_video_bf16")
 
 
 def test_attention_config3_training_shape_slices():
@@ -201,23 +260,26 @@ def test_attention_config3_training_shape_slices():
     out.backward(do.to(DEV))
     heads = [0, 11]
     dbias_ref = torch.zeros(len(heads), D)
-    for hi, hh in enumerate(heads):
-        for bb in range(B):
-            sl = (slice(bb, bb + 1), slice(hh, hh + 1))
-            ref = O.attention_with_grads(q[sl].float(), k[sl].float(), v[sl].float(), emb.freqs,
-                                         emb.bias.detach()[hh:hh + 1], do[sl].float(), causal=True)
-            dbias_ref[hi] += ref["dbias"][0]
-            if bb in (0, 3):
-                for name, got in (("out", out), ("dq", qg.grad), ("dk", kg.grad), ("dv", vg.grad)):
-                    e = maxerr(got[sl], ref[name])
-                    # 2e-2 absolute on the value, plus the half-ulp its bf16 storage costs at that magnitude
-                    # (|dv| reaches 4.3 here: 2^-9 of it is 0.008 before any arithmetic error)
-                    bound = 2e-2 + 2.0 ** -9 * float(ref[name].abs().max())
-                    assert e <= bound, f"{name} unit ({bb},{hh}): {e} > {bound}"
-    got = bias_g.grad[heads].float().cpu()
-    rel = float((got - dbias_ref).abs().max() / dbias_ref.abs().max())
+    errs = dict(out=0.0, dq=0.0, dk=0.0, dv=0.0)
+    try:
+        for hi, hh in enumerate(heads):
+            for bb in range(B):
+                sl = (slice(bb, bb + 1), slice(hh, hh + 1))
+                ref = O.attention_with_grads(q[sl].float(), k[sl].float(), v[sl].float(), emb.freqs,
+                                             emb.bias.detach()[hh:hh + 1], do[sl].float(), causal=True)
+                dbias_ref[hi] += ref["dbias"][0]
+                if bb in (0, 3):
+                    for name, got in (("out", out), ("dq", qg.grad), ("dk", kg.grad), ("dv", vg.grad)):
+                        # out, dq, dk: plain 2e-2; dv (|dv| reaches 4.3 here, half a bf16 ulp of that is 0.008): elementwise
+                        check16(f"{name} unit ({bb},{hh})", got[sl], ref[name], torch.bfloat16, strict=name != "dv",
+                                errs=errs, key=name)
+        got = bias_g.grad[heads].float().cpu()
+        errs["dbias_rel"] = float((got - dbias_ref).abs().max() / dbias_ref.abs().max())
+        errs["dbias_abs"] = float((got - dbias_ref).abs().max())
+    finally:
+        record_errors("config3_training_shape_bf16", errs)
     # a 16384 x 4096-term reduction of bf16-rounded products: bounded relative to its magnitude
-    assert rel <= 2e-2, f"dbias relative error {rel}, abs {float((got - dbias_ref).abs().max())}"
+    assert errs["dbias_rel"] <= REL_TOL, f"dbias relative error {errs}"
 
 
 def test_attention_config5_decode_and_prefill_rows():
@@ -232,7 +294,8 @@ def test_attention_config5_decode_and_prefill_rows():
     # decode
     out = flash_attn_with_pope(q[:, :, -1:].to(DEV), kg, vg, pos_emb=(fg, bg), causal=False)
     ref = O.attention(q[:, :, -1:].float(), k.float(), v.float(), freqs, bias)
-    assert maxerr(out, ref) <= 2e-2
+    errs = dict(decode_out=maxerr(out, ref), prefill_out=0.0)
+    assert errs["decode_out"] <= 2e-2
     # prefill: full causal forward on the GPU, 64 sampled rows checked
     full = flash_attn_with_pope(q.to(DEV), kg, vg, pos_emb=(fg, bg), causal=True)
     rows = torch.randint(0, N, (64,), generator=g).tolist() + [0, N - 1]
@@ -240,7 +303,9 @@ def test_attention_config5_decode_and_prefill_rows():
     for i in rows:
         s = torch.einsum("bhd,bhjd->bhj", qe[:, :, i], ke[:, :, : i + 1]) * D ** -0.5
         ref_row = torch.einsum("bhj,bhjd->bhd", s.softmax(-1), v[:, :, : i + 1].float())
-        assert maxerr(full[:, :, i], ref_row) <= 2e-2, i
+        errs["prefill_out"] = max(errs["prefill_out"], maxerr(full[:, :, i], ref_row))
+        assert errs["prefill_out"] <= 2e-2, i
+    record_errors("config5_long_context_bf16", errs)
 
 
 # ------------------------------------------------------------------------------------------
