@@ -88,6 +88,7 @@ size_t pope_b200_workspace_bytes(int op, const void* args) {
       const PopeAttnArgs& a = *static_cast<const PopeAttnArgs*>(args);
       if (a.struct_bytes != sizeof(PopeAttnArgs) || check_shape(a.shape) != POPE_OK) return 0;
       if (!force_simt() && pope::attn_fwd_tc_supported(a)) return pope::attn_fwd_tc_workspace(a);
+      if (!force_simt() && pope::decode_stream_supported(a)) return pope::decode_stream_workspace(a);
       return pope::attn_fwd_simt_workspace(a);
     }
     case POPE_OP_ATTN_BWD: {
@@ -137,13 +138,15 @@ int pope_b200_attn_fwd(const PopeAttnArgs* a, void* stream) {
   if (!a->q || !a->k || !a->v || !a->out || !a->lse) return POPE_ERR_BAD_ARG;
   if (a->shape.d > 256) return POPE_ERR_UNSUPPORTED;
   const bool tc = !force_simt() && pope::attn_fwd_tc_supported(*a);
-  const size_t need = tc ? pope::attn_fwd_tc_workspace(*a) : pope::attn_fwd_simt_workspace(*a);
+  const bool dec = !tc && !force_simt() && pope::decode_stream_supported(*a);
+  const size_t need = tc ? pope::attn_fwd_tc_workspace(*a) : dec ? pope::decode_stream_workspace(*a) : pope::attn_fwd_simt_workspace(*a);
   if (need > 0 && (!a->workspace || a->workspace_bytes < need)) return POPE_ERR_WORKSPACE;
   if (need > 0 && (reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return POPE_ERR_MISALIGNED;
   if ((rc = check_device()) != POPE_OK) return rc;
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if ((tc ? pope::attn_fwd_tc(*a, st) : pope::attn_fwd_simt(*a, st)) != cudaSuccess) return POPE_ERR_CUDA;
-  g_last_path = tc ? "tcgen05" : "simt";
+  const cudaError_t e = tc ? pope::attn_fwd_tc(*a, st) : dec ? pope::decode_stream(*a, st) : pope::attn_fwd_simt(*a, st);
+  if (e != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = tc ? "tcgen05" : dec ? "decode_stream" : "simt";
   return POPE_OK;
 }
 

@@ -18,6 +18,10 @@ cudaError_t attn_bwd_simt(const PopeAttnBwdArgs& a, cudaStream_t st);
 bool attn_fwd_tc_supported(const PopeAttnArgs& a);
 size_t attn_fwd_tc_workspace(const PopeAttnArgs& a);
 cudaError_t attn_fwd_tc(const PopeAttnArgs& a, cudaStream_t st);
+// streaming decode (one query row, 16-bit inputs): copy-engine ring + shared-memory transform, HBM-bound
+bool decode_stream_supported(const PopeAttnArgs& a);
+size_t decode_stream_workspace(const PopeAttnArgs& a);
+cudaError_t decode_stream(const PopeAttnArgs& a, cudaStream_t st);
 bool sim_fwd_tc_supported(const PopeSimArgs& a);
 size_t sim_fwd_tc_workspace(const PopeSimArgs& a);
 cudaError_t sim_fwd_tc(const PopeSimArgs& a, cudaStream_t st);

@@ -552,6 +552,23 @@ static cudaError_t launch_decode(const PopeAttnArgs& a, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+// Merge of per-split partials (one query row per unit) for the streaming decode kernel.
+cudaError_t launch_split_combine(const PopeAttnArgs& a, int nsplit, float* part_o, float* part_ml, cudaStream_t st) {
+  const PopeShape& s = a.shape;
+  AttnP c = {};
+  c.B = s.B, c.H = s.H, c.Nq = s.Nq, c.d = s.d, c.nsplit = nsplit, c.so = a.so, c.o = a.out, c.lse = a.lse;
+  c.part_o = part_o, c.part_ml = part_ml;
+  const int HDP = simt_dch(s.d) * 32;
+  const int64_t rows = (int64_t)s.B * s.H * s.Nq;
+  const unsigned blocks = (unsigned)((rows + 7) / 8);
+  switch (s.dtype) {
+    case POPE_F32: attn_fwd_combine_kernel<float><<<blocks, 256, 0, st>>>(c, HDP); break;
+    case POPE_BF16: attn_fwd_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(c, HDP); break;
+    default: attn_fwd_combine_kernel<__half><<<blocks, 256, 0, st>>>(c, HDP); break;
+  }
+  return cudaGetLastError();
+}
+
 template <typename T>
 static cudaError_t attn_fwd_dch(const PopeAttnArgs& a, cudaStream_t st) {
   if (a.shape.d > 256) return cudaErrorInvalidValue;

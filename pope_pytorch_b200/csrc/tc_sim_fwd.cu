@@ -47,7 +47,7 @@ __global__ void pope_trig_table_f32_kernel(const float* freqs, int64_t sfn, int 
   const int pos = idx / r, c = idx % r;
   float sn, cs;
   sincosf(freqs[pos * sfn + c], &sn, &cs);
-  stab[idx] = sn, ctab[idx] = cs;
+  if (ctab) stab[idx] = sn, ctab[idx] = cs;
   if (ch) ch[idx] = __float2half_rn(cs), sh[idx] = __float2half_rn(sn);
 }
 

@@ -244,3 +244,36 @@ def test_two_shards_run_one_after_the_other_equal_the_unsharded_call(b, h, hk):
         assert plan == plan_shard(b, h, hk, rank, 2)
         parts.append(out)
     assert torch.equal(torch.cat(parts, dim=plan.dim), whole)
+
+
+# ------------------------------------------------------------------------------------------
+# single-token decode on the streaming kernel
+# ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("b,h,hk,nk,d,r,dtype,masked,seq_first", [
+    (2, 4, 4, 4096, 128, 64, torch.bfloat16, False, False),
+    (1, 8, 2, 1500, 128, 128, torch.bfloat16, True, False),     # ragged key count, grouped heads, full rotation
+    (2, 4, 4, 2048, 64, 32, torch.float16, True, True),         # (b, n, h, d) layout: rows arrive one copy each
+    (1, 4, 4, 3000, 96, 96, torch.bfloat16, False, False),
+    (1, 2, 2, 1024, 64, 0, torch.bfloat16, False, False),       # no rotated dims
+    (3, 2, 2, 1111, 128, 8, torch.bfloat16, True, True),
+])
+def test_decode_stream_matches_oracle(b, h, hk, nk, d, r, dtype, masked, seq_first):
+    g = torch.Generator().manual_seed(nk + d + r)
+    q, k, v = gen((b, h, 1, d), g, dtype), gen((b, hk, nk, d), g, dtype), gen((b, hk, nk, d), g, dtype)
+    freqs = PoPE(r, heads=hk)(nk).freqs if r > 0 else torch.empty(nk, 0)
+    bias = -torch.rand(hk, r, generator=g) * 6.0
+    mask = None
+    if masked:
+        lens = torch.randint(nk // 2, nk + 1, (b,), generator=g)
+        mask = torch.arange(nk)[None, :] < lens[:, None]
+    ref = O.attention(q.float(), k.float(), v.float(), freqs, bias, mask=mask)
+    qg, kg, vg = q.to(DEV), k.to(DEV), v.to(DEV)
+    if seq_first:
+        qg, kg, vg = (t.transpose(1, 2).contiguous() for t in (qg, kg, vg))
+    out = flash_attn_with_pope(qg, kg, vg, pos_emb=(freqs.to(DEV), bias.to(DEV)), mask=None if mask is None else mask.to(DEV),
+                               head_dimension_at_first=not seq_first)
+    assert _native.last_path() == "decode_stream" and _native.device_status() == 0
+    if seq_first:
+        out = out.transpose(1, 2)
+    check16("out", out, ref, dtype)
