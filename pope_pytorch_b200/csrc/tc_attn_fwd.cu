@@ -43,37 +43,56 @@ cudaError_t tc_clear_status() {
   return cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(zero));
 }
 
-bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
-                     int64_t sh, int64_t sb, int box_rows) {
-  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static EncodeFn encode = nullptr;
+// cuTensorMapEncodeTiled, fetched once through the runtime's driver entry point (the library links no libcuda)
+typedef CUresult (*TmapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TmapEncodeFn tmap_encoder() {
+  static TmapEncodeFn encode = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
-      encode = reinterpret_cast<EncodeFn>(fn);
+      encode = reinterpret_cast<TmapEncodeFn>(fn);
   });
+  return encode;
+}
+
+// (feature, row, head, batch) view of a strided tensor.  A size-1 axis may come with any stride: it gets a valid
+// dummy (multiple of 16 bytes, increasing); an axis with more entries must come with a usable stride.
+static bool tmap_4d(CUtensorMap* out, CUtensorMapDataType dt, int esz, const void* base, int cols, int rows, int heads,
+                    int batch, int64_t sn, int64_t sh, int64_t sb, int box_cols, int box_rows, CUtensorMapSwizzle swz) {
+  TmapEncodeFn encode = tmap_encoder();
   if (!encode) return false;
-  // a size-1 axis may come with any stride: give it a valid dummy (multiple of 16 bytes, increasing); an axis with
-  // more entries must come with a usable stride
-  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
+  cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
   int64_t st[3] = {sn, sh, sb};
-  if ((rows > 1 && st[0] < d) || (heads > 1 && st[1] <= 0) || (batch > 1 && st[2] <= 0)) return false;
-  if (rows == 1) st[0] = d;
+  if ((rows > 1 && st[0] < cols) || (heads > 1 && st[1] <= 0) || (batch > 1 && st[2] <= 0)) return false;
+  if (rows == 1) st[0] = (cols + 15) / 16 * 16;
   if (heads == 1) st[1] = st[0] * rows;
   if (batch == 1) st[2] = st[1] * heads;
-  cuuint64_t strides[3] = {(cuuint64_t)st[0] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[2] * 2};
+  cuuint64_t strides[3] = {(cuuint64_t)st[0] * esz, (cuuint64_t)st[1] * esz, (cuuint64_t)st[2] * esz};
   for (int i = 0; i < 3; ++i)
     if (strides[i] % 16 != 0) return false;
-  cuuint32_t box[4] = {8, (cuuint32_t)box_rows, 1, 1}, estr[4] = {1, 1, 1, 1};
-  const CUresult rc = encode(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1}, estr[4] = {1, 1, 1, 1};
+  return encode(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
+                     int64_t sh, int64_t sb, int box_rows) {
+  return tmap_4d(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, d, rows, heads,
+                 batch, sn, sh, sb, 8, box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+bool make_store_tmap(CUtensorMap* out, const void* base, int dtype, int cols, int rows, int heads, int batch, int64_t sn,
+                     int64_t sh, int64_t sb, int box_rows) {
+  const int esz = dtype == POPE_F32 ? 4 : 2;
+  const CUtensorMapDataType dt = dtype == POPE_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == POPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return tmap_4d(out, dt, esz, base, cols, rows, heads, batch, sn, sh, sb, 128 / esz, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 struct TcFwdP {

@@ -72,6 +72,11 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // rejects the geometry; callers then stage that operand with ordinary loads.
 bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
                      int64_t sh, int64_t sb, int box_rows);
+// Tensor map of a (batch, head, row, column) OUTPUT for tiled stores out of a 128-byte-swizzled staging tile: boxes of
+// `box_rows` rows x 128 bytes (32 fp32 or 64 16-bit columns); rows / columns beyond the tensor are clipped by the
+// copy engine.  dtype is a PopeDtype.  Returns false when the geometry breaks the 16-byte stride / base rules.
+bool make_store_tmap(CUtensorMap* out, const void* base, int dtype, int cols, int rows, int heads, int batch, int64_t sn,
+                     int64_t sh, int64_t sb, int box_rows);
 
 // Expanded-operand images (see tc_expand.cu): 64-row tiles [chunk][row][16 B], contiguous per (unit, tile).
 // Every unit is padded with zero rows to a multiple of 256 rows (4 tiles), so that a CTA which keeps 128 or 256
