@@ -116,20 +116,22 @@ constexpr int TQ = 128;   // rows per MMA tile
 constexpr int TK = 64;    // keys per step (= IMAGE_ROWS)
 static_assert(TK == IMAGE_ROWS, "a streamed K' tile is one image tile");
 
-// Warp roles of the forward kernel (11 warps, 352 threads).  Two issuing warps: a single thread spends ~55 clocks
-// per MMA instruction, so O += P V of tile j is issued by a second thread while the first is still issuing the
-// score products of tile j+1.
+// Warp roles of the forward kernel (12 warps, 384 threads).  Three issuing warps: a single thread spends ~55 clocks
+// per 128x64x16 MMA instruction against 32 clocks of tensor time, so the score products of the two row tiles are
+// issued by two threads in parallel (16 instructions each per key tile) and O += P V of tile j by a third.
 constexpr int FWD_SOFTMAX_WARPS = 8;               // warps 0-7 : one query row per thread (two 128-row tiles)
 constexpr int FWD_LOAD_WARP = FWD_SOFTMAX_WARPS;   // warp 8    : one lane issues every bulk / tensor copy
-constexpr int FWD_MMA_WARP = FWD_LOAD_WARP + 1;    // warp 9    : one lane issues S = Q' K'^T; owns the TMEM allocation
+constexpr int FWD_MMA_WARP = FWD_LOAD_WARP + 1;    // warp 9    : one lane issues S_0 = Q'_0 K'^T; owns the TMEM allocation
 constexpr int FWD_PV_WARP = FWD_MMA_WARP + 1;      // warp 10   : one lane issues O += P V
-constexpr int FWD_THREADS = 32 * (FWD_PV_WARP + 1);
+constexpr int FWD_MMA1_WARP = FWD_PV_WARP + 1;     // warp 11   : one lane issues S_1 = Q'_1 K'^T
+constexpr int FWD_THREADS = 32 * (FWD_MMA1_WARP + 1);
 
 // mbarrier slots
 enum {
   B_KFULL = 0,   // [2] K' image tile landed (transaction bytes)
   B_VFULL = 2,   // [2] V tile landed (transaction bytes)
-  B_KFREE = 4,   // [2] both score products of a key tile have completed: its K' buffer may be refilled
+  B_KFREE = 4,   // [2] both score products of a key tile have completed (one commit per issuing thread): its K' buffer
+                 //     may be refilled
   B_PVDONE = 6,  // [2] O += P V of both row tiles done (tcgen05.commit)
   B_PFULL = 8,   // [buf][row tile] probabilities written to TMEM (4 softmax warps)
   B_QFULL = 12,  // the resident Q' tiles are in shared memory
@@ -172,7 +174,7 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[B_KFULL + i], 1), mbar_init(&bars[B_VFULL + i], 1);
-      mbar_init(&bars[B_KFREE + i], 1), mbar_init(&bars[B_PVDONE + i], 1);
+      mbar_init(&bars[B_KFREE + i], 2), mbar_init(&bars[B_PVDONE + i], 1);
     }
     for (int i = 0; i < 4; ++i) mbar_init(&bars[B_PFULL + i], 4), mbar_init(&bars[B_SFULL + i], 1);
     mbar_init(&bars[B_QFULL], 1);
@@ -197,14 +199,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
       copy_resident_tiles(Qs, qimg, KD / 8, &bars[B_QFULL], lane);
       copy_resident_tiles(Qs + TQ * KD * 2, qimg + 2 * KBUF, KD / 8, &bars[B_QFULL], lane);
     }
+    // K' tiles and V tiles are streamed by two lanes on their own: a K' buffer is free as soon as the score products
+    // that read it have completed, a V buffer only after O += P V two steps later, and one lane waiting for the latter
+    // would hold back the K' copy that the next score product is waiting for.
     if (lane == 0) {
       const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * KBUF;
       for (int j = 0; j < T_tiles; ++j) {
-        const int buf = j & 1, n0 = j * TK;
+        const int buf = j & 1;
         if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_KFREE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
         if (failed) break;
         mbar_expect_tx(&bars[B_KFULL + buf], KBUF);
         bulk_load(Ks + buf * KBUF, kimg + (int64_t)j * KBUF, KBUF, &bars[B_KFULL + buf]);
+      }
+    } else if (lane == 1) {
+      for (int j = 0; j < T_tiles; ++j) {
+        const int buf = j & 1, n0 = j * TK;
         if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
         if (failed) break;
         mbar_expect_tx(&bars[B_VFULL + buf], VBUF);
@@ -213,17 +222,25 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
       }
     }
     __syncwarp();
-  } else if (warp == FWD_MMA_WARP) {
-    // =============================== MMA issue ================================================
+  } else if (warp == FWD_MMA_WARP || warp == FWD_MMA1_WARP) {
+    // =============================== MMA issue: S_t = Q'_t K'^T, one thread per row tile ==========
     if (lane == 0) {
+      const int t = warp == FWD_MMA_WARP ? 0 : 1;
+      const int T_t = t == 0 ? T0 : T1;
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, TQ, TK, false, false);
       const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks);
-      auto issue_s = [&](int jt) {   // S(jt) = Q'_t K'(jt)^T into score buffer jt & 1
-        const int buf = jt & 1;
-        for (int t = 0; t < 2; ++t) {
-          if (jt >= (t == 0 ? T0 : T1)) continue;
+      const uint64_t ad = smem_desc(qs_addr + t * (TQ * KD * 2), TQ * 16, 128);
+      if (!mbar_wait(&bars[B_QFULL], 0, WAIT_LIMIT)) failed = true;
+      for (int j = 0; j < T_tiles && !failed; ++j) {
+        const int buf = j & 1;
+        // (also paces a thread whose row tile is finished: it arrives on KFREE of tile j only after the tile has landed,
+        // i.e. after the phase of tile j - 2 has completed)
+        failed = !mbar_wait(&bars[B_KFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
+        if (j < T_t) {
+          // score buffer j & 1 still holds P(j-2) until PV(j-2) has read it
+          if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+          fence_after_sync();
           const uint32_t d = tmem + (buf * 2 + t) * 64;
-          const uint64_t ad = smem_desc(qs_addr + t * (TQ * KD * 2), TQ * 16, 128);
           const uint64_t bd = smem_desc(ks_addr + buf * KBUF, CS, 128);
           uint32_t alo = desc_lo(ad), blo = desc_lo(bd);
           mma_ss_lh(d, alo, desc_hi(ad), blo, desc_hi(bd), idesc_s, 0u);
@@ -234,15 +251,9 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
           }
           mma_commit(&bars[B_SFULL + buf * 2 + t]);   // this row tile's softmax may start
         }
+        // one arrival per issuing thread and key tile, also for tiles this row tile does not take part in (the commit
+        // then completes at once): the K' buffer is free when both have arrived
         mma_commit(&bars[B_KFREE + buf]);
-      };
-      if (!mbar_wait(&bars[B_QFULL], 0, WAIT_LIMIT)) failed = true;
-      for (int j = 0; j < T_tiles && !failed; ++j) {
-        failed = !mbar_wait(&bars[B_KFULL + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
-        // score buffer j & 1 still holds P(j-2) until PV(j-2) has read it
-        if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + (j & 1)], ((j - 2) >> 1) & 1, WAIT_LIMIT);
-        fence_after_sync();
-        issue_s(j);
       }
     }
     __syncwarp();
