@@ -15,7 +15,10 @@ enum { KB_QFULL = 0,     // [3] Q' tile j (and its lse / delta rows) has landed 
        KB_CONS_DP = 13,  // 8 warps: dP^T copied to registers, the next S^T may overwrite it
        KB_GRAD = 14,     // 8 warps: P^T and dS^T of the current tile are written to TMEM
        KB_RESIDENT = 15, // the resident K' and V tiles have landed
-       KB_COUNT = 16 };
+       KB_ISS_S = 16,    // [2] S^T of tile j has been ISSUED (slot j & 1): what another thread issues after this executes
+                         //     behind it in the tensor pipe
+       KB_ISS_DP = 18,   // [2] the same for dP^T of tile j
+       KB_COUNT = 20 };
 constexpr int KQ_NST = 3, KG_NST = 2;
 
 template <int D, typename T>
@@ -46,6 +49,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     mbar_init(&bars[KB_SDONE], 1), mbar_init(&bars[KB_DPDONE], 1);
     mbar_init(&bars[KB_CONS_S], BWD_E_WARPS), mbar_init(&bars[KB_CONS_DP], BWD_E_WARPS), mbar_init(&bars[KB_GRAD], BWD_E_WARPS);
     mbar_init(&bars[KB_RESIDENT], 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&bars[KB_ISS_S + i], 1), mbar_init(&bars[KB_ISS_DP + i], 1);
     mbar_init_fence();
   }
   // query tiles: under the causal mask rows i < j0 see none of this CTA's keys
@@ -100,26 +104,25 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     }
     __syncwarp();
   } else if (warp == BWD_M_WARP) {
-    // =============================== MMA issue ===================================================
-    // One thread issues everything, in the order the tensor pipe should execute it: the accumulation products of
-    // tile j-1 fill the two gaps in which the elementwise warps copy S^T(j), resp. dP^T(j), out of TMEM.
-    //   S^T(j) | dV(j-1) | dP^T(j) | dK'(j-1)
-    // (The second issuing warp of this CTA shape stays idle in this kernel: issued from it, the accumulation
-    // products ran ahead of S^T(j) in the pipe and delayed the critical score -> elementwise -> score chain.)
+    // =============================== MMA issue: the score chain  S^T(j), dP^T(j) =================
+    // Two issuing threads.  One thread that issued everything was busy all the time (about 2200 clocks of issue and
+    // 1000 clocks of barrier checks per tile of 3400) and the elementwise warps waited for it.  This thread issues the
+    // critical chain S^T(j) -> dP^T(j); the second one issues the accumulation products of tile j - 1, each only after
+    // it has seen the ISSUED barrier of the score product behind which it should run in the tensor pipe, which keeps the
+    // order  S^T(j) | dV(j-1) | dP^T(j) | dK'(j-1)  (issued freely from a second thread, the accumulation products ran
+    // ahead of S^T(j) and delayed the chain).
     if (lane == 0 && T_tiles > 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
-      const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
-      const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
       const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
       const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128), va = smem_desc(vs_addr, BQ * 16, 128);
       if (!mbar_wait(&bars[KB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
-      for (int j = 0; j <= T_tiles && !failed; ++j) {
-        const int sq = j % KQ_NST, sg = j % KG_NST, pq = (j + KQ_NST - 1) % KQ_NST, pg = (j + KG_NST - 1) % KG_NST;
-        if (j < T_tiles) {
-          failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);
-          // the elementwise warps hold dP^T of the previous tile in registers
-          if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_CONS_DP], (j - 1) & 1, WAIT_LIMIT);
-          fence_after_sync();
+      for (int j = 0; j < T_tiles && !failed; ++j) {
+        const int sq = j % KQ_NST, sg = j % KG_NST;
+        failed = !mbar_wait(&bars[KB_QFULL + sq], (j / KQ_NST) & 1, WAIT_LIMIT);
+        // the elementwise warps hold dP^T of the previous tile in registers
+        if (j >= 1 && !failed) failed = !mbar_wait(&bars[KB_CONS_DP], (j - 1) & 1, WAIT_LIMIT);
+        fence_after_sync();
+        {
           const uint64_t qb = smem_desc(qb_addr + sq * KBUF, BCS, 128);
           uint32_t alo = desc_lo(ka), blo = desc_lo(qb);
           mma_ss_lh(tmem + TK_SD, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 0u);
@@ -129,10 +132,38 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
             mma_ss_lh(tmem + TK_SD, alo, desc_hi(ka), blo, desc_hi(qb), idesc_s, 1u);
           }
           mma_commit(&bars[KB_SDONE]);
+          mbar_arrive(&bars[KB_ISS_S + (j & 1)]);
         }
-        if (j >= 1) {   // dV += P^T dO of tile j-1 (P^T from TMEM; the dO tile re-described as an MN-major B operand)
-          if (!failed) failed = !mbar_wait(&bars[KB_GRAD], (j - 1) & 1, WAIT_LIMIT);
-          fence_after_sync();
+        if (!failed) failed = !mbar_wait(&bars[KB_GFULL + sg], (j / KG_NST) & 1, WAIT_LIMIT);
+        // ... and S^T of this tile
+        if (!failed) failed = !mbar_wait(&bars[KB_CONS_S], j & 1, WAIT_LIMIT);
+        fence_after_sync();
+        {
+          const uint64_t gb = smem_desc(gb_addr + sg * VBUF, BCS, 128);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks)
+            mma_ss_lh(tmem + TK_SD, desc_lo(va) + ks * ((2 * BQ * 16) >> 4), desc_hi(va), desc_lo(gb) + ks * ((2 * BCS) >> 4),
+                      desc_hi(gb), idesc_s, ks > 0);
+          mma_commit(&bars[KB_DPDONE]);
+          mbar_arrive(&bars[KB_ISS_DP + (j & 1)]);
+        }
+      }
+      if (failed) atomicOr(p.status, 1u);
+    }
+    __syncwarp();
+  } else if (warp == BWD_A_WARP) {
+    // =============================== MMA issue: the accumulation products  dV(j-1), dK'(j-1) =====
+    if (lane == 0 && T_tiles > 0) {
+      const uint32_t idesc_v = instr_desc(TcFmt<T>::fmt, BQ, D, false, true);
+      const uint32_t idesc_k = instr_desc(TcFmt<T>::fmt, BQ, KD, false, true);
+      const uint32_t qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
+      for (int j = 1; j <= T_tiles && !failed; ++j) {
+        const int pq = (j - 1) % KQ_NST, pg = (j - 1) % KG_NST;
+        // dV += P^T dO of tile j-1 (P^T from TMEM; the dO tile re-described as an MN-major B operand)
+        failed = !mbar_wait(&bars[KB_GRAD], (j - 1) & 1, WAIT_LIMIT);
+        if (j < T_tiles && !failed) failed = !mbar_wait(&bars[KB_ISS_S + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
+        fence_after_sync();
+        {
           const uint64_t gd = smem_desc(gb_addr + pg * VBUF, 128, BCS);
 #pragma unroll
           for (int ks = 0; ks < BT / 16; ++ks)
@@ -140,19 +171,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
                       (j > 1 || ks > 0) ? 1u : 0u);
           mma_commit(&bars[KB_ACCG + pg]);
         }
-        if (j < T_tiles) {
-          if (!failed) failed = !mbar_wait(&bars[KB_GFULL + sg], (j / KG_NST) & 1, WAIT_LIMIT);
-          // ... and S^T of this tile
-          if (!failed) failed = !mbar_wait(&bars[KB_CONS_S], j & 1, WAIT_LIMIT);
-          fence_after_sync();
-          const uint64_t gb = smem_desc(gb_addr + sg * VBUF, BCS, 128);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks)
-            mma_ss_lh(tmem + TK_SD, desc_lo(va) + ks * ((2 * BQ * 16) >> 4), desc_hi(va), desc_lo(gb) + ks * ((2 * BCS) >> 4),
-                      desc_hi(gb), idesc_s, ks > 0);
-          mma_commit(&bars[KB_DPDONE]);
-        }
-        if (j >= 1) {   // dK' += dS^T Q' of tile j-1
+        // dK' += dS^T Q' of tile j-1
+        if (j < T_tiles && !failed) failed = !mbar_wait(&bars[KB_ISS_DP + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
+        {
           const uint64_t qd = smem_desc(qb_addr + pq * KBUF, 128, BCS);
 #pragma unroll
           for (int ks = 0; ks < BT / 16; ++ks)
@@ -531,7 +552,7 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const size_t stage = (size_t)BT * KD * 2 + (size_t)BT * D * 2;
   size_t smem_q = (size_t)BQ * KD * 2 + DQ_NST * stage + (BB_COUNT + 1) * 8 + 16;
   size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + KQ_NST * (size_t)BT * KD * 2 + KG_NST * (size_t)BT * D * 2 + KQ_NST * 512 +
-                  (KB_COUNT + 1) * 8 + 16;
+                  (KB_COUNT + 1) * 8 + 16;   // 231.2 KB at d = r = 128
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;
