@@ -95,7 +95,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
-        self.gpu_index, self.proc, self.path = gpu_index, None, None
+        self.gpu_index, self.proc, self.path, self.skip = gpu_index, None, None, 0
 
     def start(self):
         try:
@@ -107,6 +107,22 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def wait_running(self, timeout_s=3.0):
+        """Block until nvidia-smi has written its first sample (it needs a few hundred ms to start), then remember
+        how many idle samples to discard: only samples taken from here on count."""
+        if self.proc is None:
+            return
+        t_end = time.time() + timeout_s
+        while time.time() < t_end:
+            try:
+                n = sum(1 for _ in open(self.path))
+            except OSError:
+                n = 0
+            if n > 0:
+                self.skip = n
+                return
+            time.sleep(0.02)
+
     def stop(self):
         out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
         if self.proc is None:
@@ -117,7 +133,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, reasons, mx = [], set(), None
-        for line in open(self.path).read().splitlines():
+        for line in open(self.path).read().splitlines()[self.skip:]:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -550,13 +566,16 @@ def main():
             ev[3 * i + 2].record()
         return out, grads
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    path = _native.last_path()
-
+    # the clock sampler runs from the first warm-up step on (every sample is taken under the same load); it is started
+    # early because nvidia-smi takes longer to deliver its first sample than the whole timed region lasts
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_running()
+    barrier()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    path = _native.last_path()
     barrier()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
