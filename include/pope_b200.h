@@ -87,10 +87,19 @@ typedef struct PopeShape {
   int32_t dtype; /* PopeDtype of q, k, v and their grads  */
 } PopeShape;
 
-/* The (freqs, bias) pair every operator takes -- PolarEmbedReturn, PoPE_pytorch/pope.py:18. */
+/* The (freqs, bias) pair every operator takes -- PolarEmbedReturn, PoPE_pytorch/pope.py:18.
+ * Optional factored form of the same table: when `positions` is not NULL the caller states that
+ *   freqs[pos, c] == positions[pos * pos_stride_n + axis_of[c]] * inv_freqs[c]      (one fp32 multiply,
+ * as PoPE.forward, PoPE_pytorch/pope.py:141, and AxialPoPE.forward, pope_nd.py:88-100, build it; axis_of
+ * NULL = a single position axis), for a table without batch / head axes.  Kernels that derive their own
+ * phase tables then recompute the phases from the 4-byte positions instead of loading the table; all other
+ * kernels keep reading `freqs`, which must always be valid. */
 typedef struct PopeEmbed {
   const float* freqs; PopeStride3 sf;      /* ignored when r == 0 */
   const float* bias;  int64_t bias_stride_h;
+  const float* positions; int64_t pos_stride_n;   /* may be NULL */
+  const float* inv_freqs;                         /* (r) */
+  const int32_t* axis_of;                         /* (r), may be NULL */
 } PopeEmbed;
 
 /* ---- similarity: sim[b,h,i,j] = <q'_i, k'_j> --------------------------------------------
@@ -175,6 +184,41 @@ typedef struct PopeAttnBwdArgs {
   void* workspace; size_t workspace_bytes;
 } PopeAttnBwdArgs;
 
+/* ---- the stand-alone transform ---------------------------------------------------------------
+ * Replaces the pure-PyTorch body of apply_pope_to_qk, PoPE_pytorch/pope.py:37-86 (return_complex
+ * excluded): q (B,H,Nq,d) and k (B,Hk,Nk,d) -> q_out (B,H,Nq,d+r), k_out (B,Hk,Nk,d+r) in fp32, the
+ * rotated features as interleaved pairs (a cos, a sin) followed by the pass-through features
+ * (:69-70, :77-78, :82-84).  One pass over the data.  freqs may carry batch / head strides (3-D and 4-D
+ * tables, :53-56).  Output rows must start on 8-byte boundaries (even d + r and row strides). */
+typedef struct PopeApplyArgs {
+  uint32_t struct_bytes;
+  int32_t reserved0;
+  PopeShape shape;
+  PopeEmbed embed;
+  const void* q; PopeStride3 sq;
+  const void* k; PopeStride3 sk;
+  float* q_out;  PopeStride3 sqo;
+  float* k_out;  PopeStride3 sko;
+} PopeApplyArgs;
+
+/* Backward of the transform (autograd does it in the reference): dq_out / dk_out are the fp32 gradients
+ * of the two outputs; dq, dk are written (dtype of q); dfreqs / dbias are optional fp32 ACCUMULATORS
+ * the caller zero-fills, as in PopeSimBwdArgs. */
+typedef struct PopeApplyBwdArgs {
+  uint32_t struct_bytes;
+  int32_t reserved0;
+  PopeShape shape;
+  PopeEmbed embed;
+  const void* q; PopeStride3 sq;
+  const void* k; PopeStride3 sk;
+  const float* dq_out; PopeStride3 sdqo;
+  const float* dk_out; PopeStride3 sdko;
+  void* dq; PopeStride3 sdq;
+  void* dk; PopeStride3 sdk;
+  float* dfreqs; PopeStride3 sdf;
+  float* dbias; int64_t dbias_stride_h;
+} PopeApplyBwdArgs;
+
 POPE_API int pope_b200_abi_version(void);
 POPE_API const char* pope_b200_status_str(int status);
 
@@ -205,6 +249,8 @@ POPE_API int pope_b200_sim_fwd(const PopeSimArgs* args, void* stream);
 POPE_API int pope_b200_sim_bwd(const PopeSimBwdArgs* args, void* stream);
 POPE_API int pope_b200_attn_fwd(const PopeAttnArgs* args, void* stream);
 POPE_API int pope_b200_attn_bwd(const PopeAttnBwdArgs* args, void* stream);
+POPE_API int pope_b200_apply_qk_fwd(const PopeApplyArgs* args, void* stream);
+POPE_API int pope_b200_apply_qk_bwd(const PopeApplyBwdArgs* args, void* stream);
 
 /* ---- attention forward for callers that cannot allocate -----------------------------------------
  * (No counterpart in the reference: its wrappers always allocate through torch.)

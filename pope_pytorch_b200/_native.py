@@ -32,7 +32,8 @@ class Shape(C.Structure):
 
 
 class Embed(C.Structure):
-    _fields_ = [("freqs", C.c_void_p), ("sf", Stride3), ("bias", C.c_void_p), ("bias_stride_h", C.c_int64)]
+    _fields_ = [("freqs", C.c_void_p), ("sf", Stride3), ("bias", C.c_void_p), ("bias_stride_h", C.c_int64),
+                ("positions", C.c_void_p), ("pos_stride_n", C.c_int64), ("inv_freqs", C.c_void_p), ("axis_of", C.c_void_p)]
 
 
 class SimArgs(C.Structure):
@@ -72,7 +73,21 @@ class AttnBwdArgs(C.Structure):
 
 
 ABI_VERSION = 2
-EXPORTS = ("pope_b200_abi_version", "pope_b200_status_str", "pope_b200_last_path", "pope_b200_device_status",
+class ApplyArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("reserved0", C.c_int32), ("shape", Shape), ("embed", Embed),
+                ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
+                ("q_out", C.c_void_p), ("sqo", Stride3), ("k_out", C.c_void_p), ("sko", Stride3)]
+
+
+class ApplyBwdArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("reserved0", C.c_int32), ("shape", Shape), ("embed", Embed),
+                ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
+                ("dq_out", C.c_void_p), ("sdqo", Stride3), ("dk_out", C.c_void_p), ("sdko", Stride3),
+                ("dq", C.c_void_p), ("sdq", Stride3), ("dk", C.c_void_p), ("sdk", Stride3),
+                ("dfreqs", C.c_void_p), ("sdf", Stride3), ("dbias", C.c_void_p), ("dbias_stride_h", C.c_int64)]
+
+
+EXPORTS = ("pope_b200_abi_version", "pope_b200_apply_qk_fwd", "pope_b200_apply_qk_bwd", "pope_b200_status_str", "pope_b200_last_path", "pope_b200_device_status",
            "pope_b200_clear_device_status", "pope_b200_selftest_bounded_wait",
            "pope_b200_workspace_bytes", "pope_b200_attn_fwd_noalloc",
            "pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd")
@@ -88,7 +103,8 @@ def _bind(lib):
     lib.pope_b200_last_path.restype = C.c_char_p
     lib.pope_b200_workspace_bytes.restype = C.c_size_t
     lib.pope_b200_workspace_bytes.argtypes = [C.c_int, C.c_void_p]
-    for name in ("pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd"):
+    for name in ("pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd",
+                 "pope_b200_apply_qk_fwd", "pope_b200_apply_qk_bwd"):
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.c_void_p, C.c_void_p]
@@ -190,10 +206,26 @@ def _prep_embed(freqs: torch.Tensor, bias: torch.Tensor, nk: int, r: int):
     return freqs, bias
 
 
-def _embed_struct(freqs, bias, r) -> Embed:
+def _factors_of(freqs):
+    """(positions, inv_freqs, axis_of) riding on a table built by PoPE / AxialPoPE, when usable as is."""
+    f = getattr(freqs, "_pope_factored", None)
+    if f is None or freqs.ndim != 2:
+        return None
+    pos, inv, axis = f
+    ok = (pos.device == freqs.device and inv.device == freqs.device and pos.dtype == torch.float32 and inv.dtype == torch.float32
+          and pos.shape[0] == freqs.shape[0] and inv.numel() == freqs.shape[1] and pos.stride(-1) == 1 and inv.is_contiguous()
+          and (axis is None or (axis.device == freqs.device and axis.dtype == torch.int32 and axis.is_contiguous())))
+    return f if ok else None
+
+
+def _embed_struct(freqs, bias, r, factors=None) -> Embed:
     if r == 0:
-        return Embed(None, Stride3(0, 0, 0), None, 0)
-    return Embed(freqs.data_ptr(), _freq_strides(freqs), bias.data_ptr(), bias.stride(0))
+        return Embed(None, Stride3(0, 0, 0), None, 0, None, 0, None, None)
+    if factors is None:
+        return Embed(freqs.data_ptr(), _freq_strides(freqs), bias.data_ptr(), bias.stride(0), None, 0, None, None)
+    pos, inv, axis = factors
+    return Embed(freqs.data_ptr(), _freq_strides(freqs), bias.data_ptr(), bias.stride(0), pos.data_ptr(),
+                 pos.stride(0) if pos.ndim == 2 else 1, inv.data_ptr(), None if axis is None else axis.data_ptr())
 
 
 def _shape(q, k, r) -> Shape:
@@ -221,18 +253,81 @@ def _validate(q, k, freqs, bias):
 
 
 # ----------------------------------------------------------------------------------------------
+# the stand-alone transform
+# ----------------------------------------------------------------------------------------------
+
+def apply_qk_supported(q, k, freqs, bias) -> bool:
+    """CUDA 4-D head-first q / k of one supported dtype, fp32 table, even expanded width."""
+    if not (q.is_cuda and k.is_cuda and freqs.is_cuda and bias.is_cuda and q.ndim == 4 and k.ndim == 4):
+        return False
+    d, r = q.shape[-1], freqs.shape[-1]
+    return (q.dtype in _DTYPES and k.dtype == q.dtype and d <= 256 and (d + r) % 2 == 0 and q.shape[1] % k.shape[1] == 0
+            and freqs.ndim in (2, 3, 4) and bias.ndim == 2 and is_available())
+
+
+class _ApplyQK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, freqs, bias):
+        lib = load_library()
+        r = freqs.shape[-1]
+        qc, kc = _inner_contig(q), _inner_contig(k)
+        fr, bi = _prep_embed(freqs, bias, k.shape[2], r)
+        q_out = torch.empty(*q.shape[:-1], q.shape[-1] + r, dtype=torch.float32, device=q.device)
+        k_out = torch.empty(*k.shape[:-1], k.shape[-1] + r, dtype=torch.float32, device=q.device)
+        a = ApplyArgs(C.sizeof(ApplyArgs), 0, _shape(qc, kc, r), _embed_struct(fr, bi, r),
+                      qc.data_ptr(), _s3(qc), kc.data_ptr(), _s3(kc), q_out.data_ptr(), _s3(q_out), k_out.data_ptr(), _s3(k_out))
+        with torch.cuda.device(q.device):
+            _check(lib.pope_b200_apply_qk_fwd(C.addressof(a), _stream_ptr(q)), "pope_b200_apply_qk_fwd")
+        ctx.save_for_backward(qc, kc, fr, bi)
+        ctx.shapes = (freqs.shape, bias.shape, freqs.dtype, bias.dtype)
+        return q_out, k_out
+
+    @staticmethod
+    def backward(ctx, dq_out, dk_out):
+        lib = load_library()
+        q, k, freqs, bias = ctx.saved_tensors
+        r = freqs.shape[-1]
+        dq_out, dk_out = dq_out.contiguous().float(), dk_out.contiguous().float()
+        dq, dk = torch.empty_like(q), torch.empty_like(k)
+        need_df, need_db = ctx.needs_input_grad[2] and r > 0, ctx.needs_input_grad[3] and r > 0
+        dfreqs = torch.zeros(freqs.shape, dtype=torch.float32, device=q.device) if need_df else None
+        dbias = torch.zeros(bias.shape, dtype=torch.float32, device=q.device) if need_db else None
+        a = ApplyBwdArgs(C.sizeof(ApplyBwdArgs), 0, _shape(q, k, r), _embed_struct(freqs, bias, r),
+                         q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), dq_out.data_ptr(), _s3(dq_out), dk_out.data_ptr(), _s3(dk_out),
+                         dq.data_ptr(), _s3(dq), dk.data_ptr(), _s3(dk),
+                         dfreqs.data_ptr() if dfreqs is not None else None,
+                         _freq_strides(dfreqs) if dfreqs is not None else Stride3(0, 0, 0),
+                         dbias.data_ptr() if dbias is not None else None, dbias.stride(0) if dbias is not None else 0)
+        with torch.cuda.device(q.device):
+            _check(lib.pope_b200_apply_qk_bwd(C.addressof(a), _stream_ptr(q)), "pope_b200_apply_qk_bwd")
+        fshape, bshape, fdt, bdt = ctx.shapes
+        if ctx.needs_input_grad[2] and dfreqs is None:
+            dfreqs = torch.zeros(fshape, dtype=fdt, device=q.device)
+        if ctx.needs_input_grad[3] and dbias is None:
+            dbias = torch.zeros(bshape, dtype=bdt, device=q.device)
+        return dq, dk, None if dfreqs is None else dfreqs.to(fdt), None if dbias is None else dbias.to(bdt)
+
+
+def apply_qk(q, k, freqs, bias):
+    """Differentiable fused transform on head-first (b,h,n,d) tensors -> fp32 (q', k') in the
+    reference's interleaved layout."""
+    return _ApplyQK.apply(q, k, freqs, bias)
+
+
+# ----------------------------------------------------------------------------------------------
 # similarity
 # ----------------------------------------------------------------------------------------------
 
-def sim_forward(q, k, freqs, bias, allow_tf32=True) -> torch.Tensor:
+def sim_forward(q, k, freqs, bias, allow_tf32=True, factors=None) -> torch.Tensor:
     """q (b,h,nq,d), k (b,hk,nk,d) head-first views -> sim (b,h,nq,nk) in q's dtype."""
     lib = load_library()
     r = freqs.shape[-1]
     _validate(q, k, freqs, bias)
     q, k = _inner_contig(q), _inner_contig(k)
+    factors = factors or _factors_of(freqs)
     freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
     sim = torch.empty(q.shape[0], q.shape[1], q.shape[2], k.shape[2], dtype=q.dtype, device=q.device)
-    a = SimArgs(C.sizeof(SimArgs), int(allow_tf32), _shape(q, k, r), _embed_struct(freqs, bias, r),
+    a = SimArgs(C.sizeof(SimArgs), int(allow_tf32), _shape(q, k, r), _embed_struct(freqs, bias, r, factors),
                 q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), sim.data_ptr(), _s3(sim), None, 0)
     ws = _workspace(OP_SIM_FWD, a, q.device)
     with torch.cuda.device(q.device):
@@ -300,18 +395,19 @@ def _mask_u8(mask: Optional[torch.Tensor]):
     return m.view(torch.uint8) if m.dtype == torch.bool else m
 
 
-def attn_forward(q, k, v, freqs, bias, mask, causal, scale):
+def attn_forward(q, k, v, freqs, bias, mask, causal, scale, factors=None):
     """Head-first VIEWS (b,h,n,d) of any stride with contiguous features -> (out, lse)."""
     lib = load_library()
     r = freqs.shape[-1]
     _validate(q, k, freqs, bias)
     q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
+    factors = factors or _factors_of(freqs)
     freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
     # the output takes the memory layout of q, so a (b,n,h,d) caller gets a (b,n,h,d)-contiguous result
     out = torch.empty_like(q)
     lse = torch.empty(q.shape[0], q.shape[1], q.shape[2], dtype=torch.float32, device=q.device)
     m8 = _mask_u8(mask)
-    a = AttnArgs(C.sizeof(AttnArgs), int(causal), float(scale), 0, _shape(q, k, r), _embed_struct(freqs, bias, r),
+    a = AttnArgs(C.sizeof(AttnArgs), int(causal), float(scale), 0, _shape(q, k, r), _embed_struct(freqs, bias, r, factors),
                  q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), v.data_ptr(), _s3(v), out.data_ptr(), _s3(out),
                  lse.data_ptr(), m8.data_ptr() if m8 is not None else None,
                  m8.stride(0) if m8 is not None else 0, m8.stride(1) if m8 is not None else 0, None, 0)
@@ -322,17 +418,18 @@ def attn_forward(q, k, v, freqs, bias, mask, causal, scale):
     return out, lse
 
 
-def attn_backward(dout, q, k, v, out, lse, freqs, bias, mask, causal, scale, need_dfreqs, need_dbias):
+def attn_backward(dout, q, k, v, out, lse, freqs, bias, mask, causal, scale, need_dfreqs, need_dbias, factors=None):
     lib = load_library()
     r = freqs.shape[-1]
     q, k, v, out, dout = (_inner_contig(t) for t in (q, k, v, out, dout))
+    factors = factors or _factors_of(freqs)
     freqs, bias = _prep_embed(freqs, bias, k.shape[2], r)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dfreqs = torch.zeros(freqs.shape, dtype=torch.float32, device=q.device) if (need_dfreqs and r > 0) else None
     dbias = torch.zeros(bias.shape, dtype=torch.float32, device=q.device) if (need_dbias and r > 0) else None
     m8 = _mask_u8(mask)
     a = AttnBwdArgs(C.sizeof(AttnBwdArgs), int(causal), float(scale), 0, _shape(q, k, r),
-                    _embed_struct(freqs, bias, r),
+                    _embed_struct(freqs, bias, r, factors),
                     q.data_ptr(), _s3(q), k.data_ptr(), _s3(k), v.data_ptr(), _s3(v), out.data_ptr(), _s3(out),
                     dout.data_ptr(), _s3(dout), lse.data_ptr(),
                     m8.data_ptr() if m8 is not None else None,
@@ -379,7 +476,8 @@ def attn_forward_noalloc(q, k, v, freqs, bias, mask, causal, scale, out, lse):
 class _FlashAttn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, freqs, bias, mask, causal, scale):
-        out, lse = attn_forward(q, k, v, freqs, bias, mask, causal, scale)
+        ctx.factors = _factors_of(freqs)        # saved tensors come back as new objects: keep the factors here
+        out, lse = attn_forward(q, k, v, freqs, bias, mask, causal, scale, ctx.factors)
         ctx.save_for_backward(q, k, v, freqs, bias, out, lse)
         ctx.mask, ctx.causal, ctx.scale = mask, causal, scale
         return out
@@ -389,7 +487,7 @@ class _FlashAttn(torch.autograd.Function):
         q, k, v, freqs, bias, out, lse = ctx.saved_tensors
         dq, dk, dv, dfreqs, dbias = attn_backward(dout.to(q.dtype), q, k, v, out, lse, freqs, bias, ctx.mask,
                                                   ctx.causal, ctx.scale,
-                                                  ctx.needs_input_grad[3], ctx.needs_input_grad[4])
+                                                  ctx.needs_input_grad[3], ctx.needs_input_grad[4], ctx.factors)
         if dfreqs is not None:
             dfreqs = dfreqs.to(freqs.dtype)
         if dbias is not None:

@@ -168,4 +168,36 @@ int pope_b200_attn_bwd(const PopeAttnBwdArgs* a, void* stream) {
   return POPE_OK;
 }
 
+static bool rows_on_8_bytes(const float* ptr, const PopeStride3& st) {
+  return (reinterpret_cast<uintptr_t>(ptr) & 7) == 0 && st.b % 2 == 0 && st.h % 2 == 0 && st.n % 2 == 0;
+}
+
+int pope_b200_apply_qk_fwd(const PopeApplyArgs* a, void* stream) {
+  if (!a || a->struct_bytes != sizeof(PopeApplyArgs)) return POPE_ERR_BAD_ARG;
+  int rc = check_shape(a->shape);
+  if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
+  if (rc != POPE_OK) return rc;
+  if (!a->q || !a->k || !a->q_out || !a->k_out) return POPE_ERR_BAD_ARG;
+  if (a->shape.d > 256) return POPE_ERR_UNSUPPORTED;
+  if (!rows_on_8_bytes(a->q_out, a->sqo) || !rows_on_8_bytes(a->k_out, a->sko)) return POPE_ERR_MISALIGNED;
+  if ((rc = check_device()) != POPE_OK) return rc;
+  if (pope::apply_qk_fwd(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = "simt";
+  return POPE_OK;
+}
+
+int pope_b200_apply_qk_bwd(const PopeApplyBwdArgs* a, void* stream) {
+  if (!a || a->struct_bytes != sizeof(PopeApplyBwdArgs)) return POPE_ERR_BAD_ARG;
+  int rc = check_shape(a->shape);
+  if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
+  if (rc != POPE_OK) return rc;
+  if (!a->q || !a->k || !a->dq_out || !a->dk_out || !a->dq || !a->dk) return POPE_ERR_BAD_ARG;
+  if (a->shape.d > 256) return POPE_ERR_UNSUPPORTED;
+  if (!rows_on_8_bytes(a->dq_out, a->sdqo) || !rows_on_8_bytes(a->dk_out, a->sdko)) return POPE_ERR_MISALIGNED;
+  if ((rc = check_device()) != POPE_OK) return rc;
+  if (pope::apply_qk_bwd(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = "simt";
+  return POPE_OK;
+}
+
 }  // extern "C"

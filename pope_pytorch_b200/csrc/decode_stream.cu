@@ -320,7 +320,7 @@ static cudaError_t launch_decode_stream(const PopeAttnArgs& a, cudaStream_t st) 
   p.status = tc_status_ptr();
   if (!p.status) return cudaErrorInvalidSymbol;
   cudaError_t e;
-  if (s.r > 0 && (e = launch_trig_tables(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, nullptr, nullptr, ch, sh, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, ch, sh, st)) != cudaSuccess) return e;
   constexpr int TILE = DS_WORKERS * KPL * 32 / LPK;
   const size_t stage = (size_t)TILE * (2 * D * 2 + 2 * s.r * 2);
   const size_t fixed = (2 * D + DS_WORKERS * D + 2 * DS_WORKERS) * sizeof(float) + 2 * 8 * 8 + 64;

@@ -18,6 +18,9 @@ cudaError_t attn_bwd_simt(const PopeAttnBwdArgs& a, cudaStream_t st);
 bool attn_fwd_tc_supported(const PopeAttnArgs& a);
 size_t attn_fwd_tc_workspace(const PopeAttnArgs& a);
 cudaError_t attn_fwd_tc(const PopeAttnArgs& a, cudaStream_t st);
+// stand-alone transform q, k -> q', k' (interleaved fp32 layout of the reference) and its backward
+cudaError_t apply_qk_fwd(const PopeApplyArgs& a, cudaStream_t st);
+cudaError_t apply_qk_bwd(const PopeApplyBwdArgs& a, cudaStream_t st);
 // streaming decode (one query row, 16-bit inputs): copy-engine ring + shared-memory transform, HBM-bound
 bool decode_stream_supported(const PopeAttnArgs& a);
 size_t decode_stream_workspace(const PopeAttnArgs& a);

@@ -460,7 +460,7 @@ static void decode_plan(const PopeShape& s, int& nsplit, int& split_len) {
   nsplit = (s.Nk + split_len - 1) / split_len;
 }
 
-cudaError_t launch_trig_table_f32(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, cudaStream_t st);
+cudaError_t launch_trig_table_f32(const PopeEmbed& e, int n, int r, float* ctab, float* stab, cudaStream_t st);
 
 // ---- forward launch --------------------------------------------------------------------------
 static void plan_split(const PopeShape& s, int causal, int& nsplit, int& split_len) {
@@ -539,7 +539,7 @@ static cudaError_t launch_decode(const PopeAttnArgs& a, cudaStream_t st) {
   float* stab = ctab + (size_t)s.Nk * s.r;
   p.ctab = ctab, p.stab = stab;
   cudaError_t e = cudaSuccess;
-  if (s.r > 0 && (e = launch_trig_table_f32(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, ctab, stab, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_table_f32(a.embed, s.Nk, s.r, ctab, stab, st)) != cudaSuccess) return e;
   dim3 grid(p.nsplit, s.B * s.H);
   if (s.d <= 128) attn_decode_kernel<T, 1><<<grid, DEC_WARPS * 32, 0, st>>>(p);
   else attn_decode_kernel<T, 2><<<grid, DEC_WARPS * 32, 0, st>>>(p);

@@ -529,7 +529,7 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
       rowstat);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   if (fork && (e = cudaEventRecord(fk->stats, sk)) != cudaSuccess) return e;
-  if (s.r > 0 && (e = launch_trig_tables(a.embed.freqs, a.embed.sf.n, s.Nk, s.r, tt.ctab, tt.stab, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, tt.ctab, tt.stab, tt.ch, tt.sh, st)) != cudaSuccess) return e;
   // K' (phase bias folded in), Q', and V / dO as the same tiles without rotated features (a pure re-layout)
   ExpandJobs jobs;
   jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg);

@@ -107,9 +107,28 @@ inline ExpandJob expand_job(const void* x, const PopeStride3& sx, int batch, int
 cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const void* ch, const void* sh,
                                  cudaStream_t st);
 // fp32 cos / sin of freqs[pos][c] into ctab / stab ([n][r] each); launch_trig_tables also writes fp16 copies (ch, sh).
-cudaError_t launch_trig_table_f32(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, cudaStream_t st);
-cudaError_t launch_trig_tables(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, void* ch, void* sh,
-                               cudaStream_t st);
+// Where a phase comes from: the caller's table, or (factored form) position x inverse frequency, one fp32 multiply.
+struct PhaseSrc {
+  const float* freqs;
+  int64_t sfn;
+  const float* pos;
+  int64_t spos;
+  const float* inv;
+  const int32_t* axis;
+  __device__ __forceinline__ float at(int64_t row, int c) const {
+    if (pos) return __fmul_rn(pos[row * spos + (axis ? axis[c] : 0)], inv[c]);
+    return freqs[row * sfn + c];
+  }
+};
+inline PhaseSrc phase_src(const PopeEmbed& e) {
+  PhaseSrc s;
+  s.freqs = e.freqs, s.sfn = e.sf.n;
+  const bool factored = e.positions && e.inv_freqs && e.sf.b == 0 && e.sf.h == 0;
+  s.pos = factored ? e.positions : nullptr, s.spos = e.pos_stride_n, s.inv = e.inv_freqs, s.axis = e.axis_of;
+  return s;
+}
+cudaError_t launch_trig_table_f32(const PopeEmbed& e, int n, int r, float* ctab, float* stab, cudaStream_t st);
+cudaError_t launch_trig_tables(const PopeEmbed& e, int n, int r, float* ctab, float* stab, void* ch, void* sh, cudaStream_t st);
 // Table block of the attention workspace: [cos fp32][sin fp32][cos fp16][sin fp16], n*r entries each.
 struct TrigTables {
   float *ctab, *stab;

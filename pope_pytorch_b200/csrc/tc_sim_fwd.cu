@@ -54,26 +54,24 @@ constexpr int SIM_THREADS = 320;
 
 // ch / sh (may be null): the same tables rounded to fp16 (cos and sin lie in [-1, 1]: 2^-12 absolute error), read by
 // the operand-image pre-pass, whose result is rounded to 8 or 11 bits anyway.
-__global__ void pope_trig_table_f32_kernel(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab,
-                                           __half* ch, __half* sh) {
+__global__ void pope_trig_table_f32_kernel(PhaseSrc src, int n, int r, float* ctab, float* stab, __half* ch, __half* sh) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)n * r) return;
   const int pos = idx / r, c = idx % r;
   float sn, cs;
-  sincosf(freqs[pos * sfn + c], &sn, &cs);
+  sincosf(src.at(pos, c), &sn, &cs);
   if (ctab) stab[idx] = sn, ctab[idx] = cs;
   if (ch) ch[idx] = __float2half_rn(cs), sh[idx] = __float2half_rn(sn);
 }
 
-cudaError_t launch_trig_tables(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, void* ch, void* sh,
-                               cudaStream_t st) {
+cudaError_t launch_trig_tables(const PopeEmbed& e, int n, int r, float* ctab, float* stab, void* ch, void* sh, cudaStream_t st) {
   const int64_t total = (int64_t)n * r;
-  pope_trig_table_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(freqs, sfn, n, r, ctab, stab,
+  pope_trig_table_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(phase_src(e), n, r, ctab, stab,
                                                                                static_cast<__half*>(ch), static_cast<__half*>(sh));
   return cudaGetLastError();
 }
-cudaError_t launch_trig_table_f32(const float* freqs, int64_t sfn, int n, int r, float* ctab, float* stab, cudaStream_t st) {
-  return launch_trig_tables(freqs, sfn, n, r, ctab, stab, nullptr, nullptr, st);
+cudaError_t launch_trig_table_f32(const PopeEmbed& e, int n, int r, float* ctab, float* stab, cudaStream_t st) {
+  return launch_trig_tables(e, n, r, ctab, stab, nullptr, nullptr, st);
 }
 
 template <typename T> struct Load8;
@@ -139,7 +137,7 @@ constexpr int SIM_STG_WARP = 32 * 128;     // staging tile of one worker warp: 3
 // cover whole rows.  Rows past the end of the operand become zeros.
 template <typename T, bool SPLIT>
 __global__ void __launch_bounds__(256) sim_prepass_kernel(const T* __restrict__ q, Strides sq, const T* __restrict__ k, Strides sk,
-                                                          const float* __restrict__ freqs, int64_t sfn,
+                                                          PhaseSrc src,
                                                           const float* __restrict__ bias, int64_t bias_sh, int B, int H, int Hk, int Nq,
                                                           int Nk, int d, int r, int qtiles, int ktiles,
                                                           uint8_t* __restrict__ qimg, uint8_t* __restrict__ kimg) {
@@ -166,7 +164,12 @@ __global__ void __launch_bounds__(256) sim_prepass_kernel(const T* __restrict__ 
       float vc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, vs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       if (ok) {
         float fr[8];
-        Load8<float>::run(freqs + (int64_t)(pos0 + j) * sfn + c * 8, fr);
+        if (src.pos) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) fr[e] = src.at(pos0 + j, c * 8 + e);
+        } else {
+          Load8<float>::run(src.freqs + (int64_t)(pos0 + j) * src.sfn + c * 8, fr);
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           float sn, cs;
@@ -431,7 +434,7 @@ static cudaError_t launch_sim_tc(const PopeSimArgs& a, cudaStream_t st) {
   p.rblocks = (qtiles + MT - 1) / MT;
   p.total_tiles = (int64_t)s.B * s.H * p.rblocks * p.ktiles;
   sim_prepass_kernel<T, SPLIT><<<dim3(4 * (qtiles + p.ktiles), s.B * s.H), 256, 0, st>>>(
-      static_cast<const T*>(a.q), Strides(a.sq), static_cast<const T*>(a.k), Strides(a.sk), a.embed.freqs, a.embed.sf.n,
+      static_cast<const T*>(a.q), Strides(a.sq), static_cast<const T*>(a.k), Strides(a.sk), phase_src(a.embed),
       a.embed.bias, a.embed.bias_stride_h, s.B, s.H, s.Hk, s.Nq, s.Nk, s.d, s.r, qtiles, p.ktiles, qimg, kimg);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;

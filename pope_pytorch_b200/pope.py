@@ -18,6 +18,21 @@ from torch import Tensor, nn
 
 PolarEmbedReturn = namedtuple("PolarEmbedReturn", ("freqs", "bias"))
 
+
+class FactoredPolarEmbed(PolarEmbedReturn):
+    """The ``(freqs, bias)`` pair of the reference (it unpacks and indexes like PolarEmbedReturn) that
+    also remembers how the table was built: ``freqs[p, c] = positions[p, axis_of[c]] * inv_freqs[c]``.
+    Kernels that derive their own phase tables recompute the phases from the 4-byte positions
+    (bit-identical: it is the same single fp32 multiply) instead of loading the fp32 table.  The
+    factors also ride on the ``freqs`` tensor itself, so they survive ``freqs, bias = pos_emb``."""
+
+    def __new__(cls, freqs, bias, positions=None, inv_freqs=None, axis_of=None):
+        self = super().__new__(cls, freqs, bias)
+        self.positions, self.inv_freqs, self.axis_of = positions, inv_freqs, axis_of
+        if positions is not None and freqs.ndim == 2:
+            freqs._pope_factored = (positions, inv_freqs, axis_of)
+        return self
+
 TWO_PI = 2.0 * math.pi
 
 
@@ -39,6 +54,11 @@ def apply_pope_to_qk(pope, q: Tensor, k: Tensor, to_magnitude=F.softplus, return
     freqs, bias = pope
     n_q, n_k, d, r = q.shape[-2], k.shape[-2], q.shape[-1], freqs.shape[-1]
     assert n_q <= n_k and r <= d
+
+    if to_magnitude is F.softplus and not return_complex:
+        from . import _native          # CUDA tensors: one fused pass in the native library (no fallback when it is present)
+        if _native.apply_qk_supported(q, k, freqs, bias):
+            return _native.apply_qk(q, k, freqs, bias)
 
     if freqs.ndim == 3:                       # (b, n, r) -> (b, 1, n, r)
         freqs = freqs.unsqueeze(1)
@@ -94,4 +114,7 @@ class PoPE(nn.Module):
             positions = torch.arange(pos_or_seq_len, device=self.device, dtype=self.inv_freqs.dtype)
         positions = positions + offset
         freqs = positions.unsqueeze(-1) * self.inv_freqs          # (..., n, dim)
-        return PolarEmbedReturn(freqs, self.bias.clamp(-TWO_PI, 0.0))
+        bias = self.bias.clamp(-TWO_PI, 0.0)
+        if positions.ndim == 1 and positions.dtype == torch.float32 and self.inv_freqs.dtype == torch.float32:
+            return FactoredPolarEmbed(freqs, bias, positions.contiguous(), self.inv_freqs.contiguous())
+        return PolarEmbedReturn(freqs, bias)

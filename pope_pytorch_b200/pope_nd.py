@@ -12,7 +12,7 @@ from typing import Optional, Tuple, Union
 import torch
 from torch import Tensor, nn
 
-from .pope import TWO_PI, PolarEmbedReturn, apply_pope_to_qk
+from .pope import TWO_PI, FactoredPolarEmbed, PolarEmbedReturn, apply_pope_to_qk
 
 
 class AxialPoPE(nn.Module):
@@ -49,4 +49,10 @@ class AxialPoPE(nn.Module):
             if isinstance(pos_or_dims, tuple) else pos_or_dims
         assert positions.shape[-1] == len(self.axial_dims)
         per_axis = [positions[..., axis, None] * inv for axis, inv in enumerate(self.inv_freqs)]
-        return PolarEmbedReturn(torch.cat(per_axis, dim=-1), self.bias.clamp(-TWO_PI, 0.0))
+        freqs, bias = torch.cat(per_axis, dim=-1), self.bias.clamp(-TWO_PI, 0.0)
+        if positions.ndim == 2 and positions.dtype == torch.float32:
+            axis_of = torch.cat([torch.full((n,), axis, dtype=torch.int32, device=freqs.device)
+                                 for axis, n in enumerate(self.axial_dims)])
+            inv_flat = torch.cat([inv.detach().float() for inv in self.inv_freqs])
+            return FactoredPolarEmbed(freqs, bias, positions.contiguous(), inv_flat, axis_of)
+        return PolarEmbedReturn(freqs, bias)

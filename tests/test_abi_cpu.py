@@ -42,6 +42,8 @@ def test_struct_layout_matches_c(tmp_path):
         "PopeSimBwdArgs": (N.SimBwdArgs, ["dsim", "dq", "dfreqs", "dbias_stride_h"]),
         "PopeAttnArgs": (N.AttnArgs, ["softmax_scale", "shape", "embed", "v", "lse", "mask", "workspace_bytes"]),
         "PopeAttnBwdArgs": (N.AttnBwdArgs, ["dout", "lse", "mask_stride_n", "dq", "dv", "dfreqs", "dbias", "workspace"]),
+        "PopeApplyArgs": (N.ApplyArgs, ["shape", "embed", "q", "k", "q_out", "sqo", "k_out", "sko"]),
+        "PopeApplyBwdArgs": (N.ApplyBwdArgs, ["dq_out", "dk_out", "dq", "dk", "dfreqs", "dbias", "dbias_stride_h"]),
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for cname, (_, fl) in fields.items():

@@ -277,3 +277,78 @@ def test_decode_stream_matches_oracle(b, h, hk, nk, d, r, dtype, masked, seq_fir
     if seq_first:
         out = out.transpose(1, 2)
     check16("out", out, ref, dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# the stand-alone transform (apply_pope_to_qk) as one fused pass
+# ------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("b,h,hk,nq,nk,d,r,dtype,kind", [
+    (1, 8, 8, 1024, 1024, 64, 64, torch.float32, "2d"),       # shapes of the reference's own test (tests/test_pope.py:6-29)
+    (1, 8, 8, 1, 1024, 64, 32, torch.float32, "2d"),          # decode: the query sits at the last position
+    (2, 4, 2, 96, 200, 128, 64, torch.bfloat16, "3d"),
+    (2, 4, 4, 33, 33, 48, 16, torch.float16, "4d"),
+    (1, 2, 2, 50, 50, 32, 0, torch.float32, "2d"),
+])
+def test_apply_pope_to_qk_fused_forward_and_gradients(b, h, hk, nq, nk, d, r, dtype, kind):
+    from pope_pytorch_b200 import apply_pope_to_qk
+    g = torch.Generator().manual_seed(nq + nk + d + r)
+    q, k = gen((b, h, nq, d), g, dtype), gen((b, hk, nk, d), g, dtype)
+    freqs = batched_freqs(kind, b, hk, nk, r, g)
+    bias = -torch.rand(hk, r, generator=g) * 6.0
+    gq, gk = gen((b, h, nq, d + r), g), gen((b, hk, nk, d + r), g)
+    # oracle: its own restatement of the transform, gradients by autograd, all in fp32 on the rounded inputs
+    qr, kr = q.float().clone().requires_grad_(True), k.float().clone().requires_grad_(True)
+    fr, br = freqs.clone().requires_grad_(True), bias.clone().requires_grad_(True)
+    qe, ke = O.apply_pope(fr, br, qr, kr)   # a table without a head axis serves any number of query heads
+    (qe * gq).sum().backward(retain_graph=True)
+    (ke * gk).sum().backward()
+    qg, kg = q.to(DEV).requires_grad_(True), k.to(DEV).requires_grad_(True)
+    fg, bg = freqs.to(DEV).requires_grad_(True), bias.to(DEV).requires_grad_(True)
+    q_out, k_out = apply_pope_to_qk((fg, bg), qg, kg)
+    assert q_out.dtype == torch.float32 and q_out.shape == (b, h, nq, d + r) and k_out.shape == (b, hk, nk, d + r)
+    assert_close32(q_out, qe, "q'", rtol=1e-5, atol=1e-5), assert_close32(k_out, ke, "k'", rtol=1e-5, atol=1e-5)
+    (q_out * gq.to(DEV)).sum().backward(retain_graph=True)
+    (k_out * gk.to(DEV)).sum().backward()
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)
+    assert_close32(qg.grad, qr.grad, "dq", **tol), assert_close32(kg.grad, kr.grad, "dk", **tol)
+    if r > 0:
+        mag = max(1.0, float(br.grad.abs().max()))
+        assert_close32(bg.grad, br.grad, "dbias", rtol=1e-4, atol=1e-4 * mag)
+        assert_close32(fg.grad, fr.grad, "dfreqs", rtol=1e-4, atol=1e-4 * max(1.0, float(fr.grad.abs().max())))
+
+
+# ------------------------------------------------------------------------------------------
+# factored phase tables: positions x inverse frequencies recomputed inside the table builders
+# ------------------------------------------------------------------------------------------
+
+def test_factored_embeds_give_bitwise_the_results_of_the_plain_table():
+    from pope_pytorch_b200 import AxialPoPE, FactoredPolarEmbed
+    g = torch.Generator().manual_seed(98)
+    n, d = 1024, 64
+    q, k, v = (gen((1, 4, n, d), g, torch.bfloat16).to(DEV) for _ in range(3))
+    for module, arg in ((PoPE(32, heads=4).to(DEV), n), (AxialPoPE(48, heads=4, axial_dims=(16, 16, 16)).to(DEV), (4, 16, 16))):
+        emb = module(arg)
+        assert isinstance(emb, FactoredPolarEmbed) and _native._factors_of(emb.freqs) is not None
+        freqs, bias = emb                                      # unpacking keeps the factors on the tensor
+        plain = (freqs.detach().clone(), bias.detach())        # a copy of the table carries none
+        assert _native._factors_of(plain[0]) is None
+        a = flash_attn_with_pope(q, k, v, pos_emb=(freqs, bias.detach()), causal=True)
+        b = flash_attn_with_pope(q, k, v, pos_emb=plain, causal=True)
+        assert _native.last_path() == "tcgen05" and torch.equal(a, b)
+        a = flash_attn_with_pope(q[:, :, -1:], k, v, pos_emb=(freqs, bias.detach()))
+        b = flash_attn_with_pope(q[:, :, -1:], k, v, pos_emb=plain)
+        assert _native.last_path() == "decode_stream" and torch.equal(a, b)
+        a = compute_attn_similarity(q.float(), k.float(), (freqs, bias.detach()))
+        b = compute_attn_similarity(q.float(), k.float(), plain)
+        assert _native.last_path() == "tcgen05" and torch.equal(a, b)
+    # a module called with an offset, and gradients through the factored path
+    pope = PoPE(32, heads=4).to(DEV)
+    qg = q.clone().requires_grad_(True)
+    out = flash_attn_with_pope(qg, k, v, pos_emb=pope(n, offset=7), causal=True)
+    out.float().square().sum().backward()
+    qp = q.clone().requires_grad_(True)
+    pe = pope(n, offset=7)
+    out_p = flash_attn_with_pope(qp, k, v, pos_emb=(pe.freqs.detach().clone(), pe.bias), causal=True)
+    out_p.float().square().sum().backward()
+    assert torch.equal(out, out_p) and torch.equal(qg.grad, qp.grad)
