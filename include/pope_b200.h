@@ -264,9 +264,9 @@ POPE_API int pope_b200_apply_qk_bwd(const PopeApplyBwdArgs* args, void* stream);
  *
  * Limits and rules
  *   - Only the tensor-core shapes are served (bf16/fp16, d in {64,96,128}, r % 16 == 0, Nq >= 64,
- *     2-D freqs, 16-byte aligned rows); anything else returns POPE_ERR_UNSUPPORTED.
+ *     16-byte aligned rows); anything else returns POPE_ERR_UNSUPPORTED.
  *   - The scratch a call needs is what pope_b200_workspace_bytes reports for the forward
- *     (12 Nk r bytes of table -- fp32 and fp16 copies of cos and sin -- rounded up to 256, plus
+ *     (4 Nk r bytes of table -- fp16 cos and sin -- rounded up to 256, plus
  *     2 (d + r) bytes per query and key row of every head, rows padded to a multiple of 256);
  *     more than POPE_B200_NOALLOC_MAX_SCRATCH returns POPE_ERR_TOO_LARGE and launches nothing.  Every GPU that loads the library holds that many
  *     bytes until the process exits.

@@ -29,7 +29,6 @@ struct TcBwdP {
   Strides sq, sk, sv, sdo, sdq, sdk, sdv, sdf;
   const float *freqs, *bias, *lse, *delta;
   int64_t sfn, bias_sh, dbias_sh;
-  const float *ctab, *stab;   // fp32 cos / sin of the phase table, [Nk][r]
   const uint8_t* kimg;   // expanded K' image tiles, (B * Hk) units (no phase bias)
   const uint8_t* qimg;   // expanded Q' image tiles, (B * H) units (no phase bias)
   const uint8_t* vimg;   // V re-laid as image tiles, (B * Hk) units

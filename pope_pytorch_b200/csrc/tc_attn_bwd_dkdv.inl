@@ -382,8 +382,9 @@ bool attn_bwd_tc_supported(const PopeAttnBwdArgs& a) {
   if (s.d != 64 && s.d != 96 && s.d != 128) return false;
   if (s.r % 16 != 0) return false;
   if (s.Nq < 64) return false;
-  if (s.r > 0 && (a.embed.sf.b != 0 || a.embed.sf.h != 0)) return false;
-  if (a.dfreqs && (a.sdf.b != 0 || a.sdf.h != 0)) return false;
+  // a phase table with a head axis (b, h, n, r) serves queries and keys alike only when both have the same heads
+  if (s.r > 0 && a.embed.sf.h != 0 && s.H != s.Hk) return false;
+  if (a.dfreqs && a.sdf.h != 0 && s.H != s.Hk) return false;
   const void* ptrs[] = {a.q, a.k, a.v, a.out, a.dout, a.dq, a.dk, a.dv};
   for (const void* ptr : ptrs)
     if (!bwd_aligned16(ptr)) return false;
@@ -433,12 +434,12 @@ __global__ void __launch_bounds__(256) bwd_rowstat_kernel(const T* __restrict__ 
 // rounded up to 256 bytes
 static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 static size_t delta_bytes(const PopeShape& s) { return up256((size_t)s.B * s.H * s.Nq * sizeof(float)); }
-static size_t bwd_table_bytes(const PopeShape& s) { return trig_tables_bytes(s.Nk, s.r); }
+static size_t bwd_table_bytes(const PopeShape& s, const PopeEmbed& e) { return trig_tables_bytes(s.Nk, s.r, table_slices(e, s.B, s.H)); }
 static size_t rowstat_bytes(const PopeShape& s) { return up256((size_t)s.B * s.H * image_tiles(s.Nq) * 2 * BT * sizeof(float)); }
 
 size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a) {
   const PopeShape& s = a.shape;
-  return delta_bytes(s) + bwd_table_bytes(s) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) +
+  return delta_bytes(s) + bwd_table_bytes(s, a.embed) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) +
          up256(image_bytes(s.B * s.H, s.Nq, s.d + s.r)) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d)) +
          up256(image_bytes(s.B * s.H, s.Nq, s.d)) + rowstat_bytes(s);
 }
@@ -510,8 +511,9 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const bool bf16 = s.dtype == POPE_BF16;
   uint8_t* ws = reinterpret_cast<uint8_t*>(a.workspace);
   float* delta = reinterpret_cast<float*>(ws);
-  const TrigTables tt = trig_tables_at(ws + delta_bytes(s), s.Nk, s.r);
-  uint8_t* kimg = ws + delta_bytes(s) + bwd_table_bytes(s);
+  const int slices = table_slices(a.embed, s.B, s.H), tab_heads = table_heads(a.embed, s.H), by_batch = a.embed.sf.b != 0;
+  const TrigTables tt = trig_tables_at(ws + delta_bytes(s), s.Nk, s.r, slices);
+  uint8_t* kimg = ws + delta_bytes(s) + bwd_table_bytes(s, a.embed);
   uint8_t* qimg = kimg + up256(image_bytes(s.B * s.Hk, s.Nk, KD));
   uint8_t* vimg = qimg + up256(image_bytes(s.B * s.H, s.Nq, KD));
   uint8_t* gimg = vimg + up256(image_bytes(s.B * s.Hk, s.Nk, s.d));
@@ -529,11 +531,11 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
       rowstat);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   if (fork && (e = cudaEventRecord(fk->stats, sk)) != cudaSuccess) return e;
-  if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, tt.ctab, tt.stab, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, tt.ch, tt.sh, st, slices, tab_heads)) != cudaSuccess) return e;
   // K' (phase bias folded in), Q', and V / dO as the same tiles without rotated features (a pure re-layout)
   ExpandJobs jobs;
-  jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg);
-  jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg);
+  jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg, s.Nk, by_batch, tab_heads);
+  jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg, s.Nk, by_batch, tab_heads);
   jobs.job[2] = expand_job(a.v, a.sv, s.B, s.Hk, s.Nk, 0, 0, nullptr, 0, vimg);
   jobs.job[3] = expand_job(a.dout, a.sdo, s.B, s.H, s.Nq, 0, 0, nullptr, 0, gimg);
   if ((e = launch_expand_images(jobs, 4, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
@@ -544,7 +546,7 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.sdo = a.sdo, p.sdq = a.sdq, p.sdk = a.sdk, p.sdv = a.sdv, p.sdf = a.sdf;
   p.freqs = a.embed.freqs, p.bias = a.embed.bias, p.lse = a.lse, p.delta = delta;
   p.sfn = a.embed.sf.n, p.bias_sh = a.embed.bias_stride_h, p.dbias_sh = a.dbias_stride_h;
-  p.ctab = tt.ctab, p.stab = tt.stab, p.kimg = kimg, p.qimg = qimg, p.vimg = vimg, p.gimg = gimg, p.rowstat = rowstat;
+  p.kimg = kimg, p.qimg = qimg, p.vimg = vimg, p.gimg = gimg, p.rowstat = rowstat;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   p.dfreqs = s.r > 0 ? a.dfreqs : nullptr, p.dbias = s.r > 0 ? a.dbias : nullptr;
   p.status = tc_status_ptr();

@@ -433,7 +433,8 @@ bool attn_fwd_tc_supported(const PopeAttnArgs& a) {
   if (s.d != 64 && s.d != 96 && s.d != 128) return false;
   if (s.r % 16 != 0) return false;
   if (s.Nq < 64) return false;  // short query blocks take the key-split path
-  if (s.r > 0 && (a.embed.sf.b != 0 || a.embed.sf.h != 0)) return false;  // one phase table for all units
+  // a phase table with a head axis (b, h, n, r) serves queries and keys alike only when both have the same heads
+  if (s.r > 0 && a.embed.sf.h != 0 && s.H != s.Hk) return false;
   if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || !aligned16(a.out)) return false;
   if (!stride_ok(a.sq) || !stride_ok(a.sk) || !stride_ok(a.sv) || !stride_ok(a.so)) return false;
   // V is read by TMA boxes over (feature, row, head, batch): an axis with more than one entry needs a real, positive
@@ -447,7 +448,8 @@ static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 size_t attn_fwd_tc_workspace(const PopeAttnArgs& a) {
   const PopeShape& s = a.shape;
-  return trig_tables_bytes(s.Nk, s.r) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) + image_bytes(s.B * s.H, s.Nq, s.d + s.r);
+  return trig_tables_bytes(s.Nk, s.r, table_slices(a.embed, s.B, s.H)) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) +
+         image_bytes(s.B * s.H, s.Nq, s.d + s.r);
 }
 
 template <int D, typename T>
@@ -456,8 +458,9 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   const int KD = s.d + s.r;
   const bool bf16 = s.dtype == POPE_BF16;
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
-  const TrigTables tt = trig_tables_at(ws, s.Nk, s.r);
-  uint8_t* kimg = ws + trig_tables_bytes(s.Nk, s.r);
+  const int slices = table_slices(a.embed, s.B, s.H), tab_heads = table_heads(a.embed, s.H), by_batch = a.embed.sf.b != 0;
+  const TrigTables tt = trig_tables_at(ws, s.Nk, s.r, slices);
+  uint8_t* kimg = ws + trig_tables_bytes(s.Nk, s.r, slices);
   uint8_t* qimg = kimg + up256(image_bytes(s.B * s.Hk, s.Nk, KD));
   TcFwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
@@ -468,10 +471,10 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   p.qimg = qimg, p.kimg = kimg;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   cudaError_t e;
-  if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, tt.ctab, tt.stab, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+  if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, tt.ch, tt.sh, st, slices, tab_heads)) != cudaSuccess) return e;
   ExpandJobs jobs;
-  jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg);
-  jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg);
+  jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg, s.Nk, by_batch, tab_heads);
+  jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg, s.Nk, by_batch, tab_heads);
   if ((e = launch_expand_images(jobs, 2, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
   CUtensorMap tmap_v;
   if (!make_chunk_tmap(&tmap_v, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, TK)) return cudaErrorNotSupported;

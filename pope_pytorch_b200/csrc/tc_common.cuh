@@ -91,15 +91,18 @@ struct ExpandJob {
   const void* x;
   PopeStride3 sx;
   int units, heads, rows, r, pos0;
+  int tab_rows, tab_by_batch, tab_heads;   // table slice of a unit: (tab_by_batch ? batch : 0) * tab_heads + head % tab_heads
   const float* bias;
   int64_t bias_sh;
   void* img;
 };
 struct ExpandJobs { ExpandJob job[4]; };
 inline ExpandJob expand_job(const void* x, const PopeStride3& sx, int batch, int heads, int rows, int r, int pos0,
-                            const float* bias, int64_t bias_sh, void* img) {
+                            const float* bias, int64_t bias_sh, void* img, int tab_rows = 0, int tab_by_batch = 0,
+                            int tab_heads = 1) {
   ExpandJob j;
   j.x = x, j.sx = sx, j.units = batch * heads, j.heads = heads, j.rows = rows, j.r = r, j.pos0 = pos0;
+  j.tab_rows = tab_rows, j.tab_by_batch = tab_by_batch, j.tab_heads = tab_heads;
   j.bias = r > 0 ? bias : nullptr, j.bias_sh = bias_sh, j.img = img;
   return j;
 }
@@ -110,7 +113,8 @@ cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool 
 // Where a phase comes from: the caller's table, or (factored form) position x inverse frequency, one fp32 multiply.
 struct PhaseSrc {
   const float* freqs;
-  int64_t sfn;
+  int64_t sfn, sfb, sfh;   // row stride; batch / head strides of a batched table (0 = that axis is broadcast)
+  int tab_heads;           // table slices per batch entry: the head count when the table has a head axis, else 1
   const float* pos;
   int64_t spos;
   const float* inv;
@@ -122,23 +126,28 @@ struct PhaseSrc {
 };
 inline PhaseSrc phase_src(const PopeEmbed& e) {
   PhaseSrc s;
-  s.freqs = e.freqs, s.sfn = e.sf.n;
+  s.freqs = e.freqs, s.sfn = e.sf.n, s.sfb = e.sf.b, s.sfh = e.sf.h, s.tab_heads = 1;
   const bool factored = e.positions && e.inv_freqs && e.sf.b == 0 && e.sf.h == 0;
   s.pos = factored ? e.positions : nullptr, s.spos = e.pos_stride_n, s.inv = e.inv_freqs, s.axis = e.axis_of;
   return s;
 }
 cudaError_t launch_trig_table_f32(const PopeEmbed& e, int n, int r, float* ctab, float* stab, cudaStream_t st);
-cudaError_t launch_trig_tables(const PopeEmbed& e, int n, int r, float* ctab, float* stab, void* ch, void* sh, cudaStream_t st);
-// Table block of the attention workspace: [cos fp32][sin fp32][cos fp16][sin fp16], n*r entries each.
+// `slices` tables of n x r entries, slice = batch index x tab_heads + head index of a batched caller table (1 slice for a
+// plain (n, r) table); every output pointer may be null
+cudaError_t launch_trig_tables(const PopeEmbed& e, int n, int r, float* ctab, float* stab, void* ch, void* sh, cudaStream_t st,
+                               int slices = 1, int tab_heads = 1);
+// slices of the phase table an attention call needs: one per batch entry and / or head that the caller's table tells apart
+inline int table_heads(const PopeEmbed& e, int heads) { return e.sf.h != 0 ? heads : 1; }
+inline int table_slices(const PopeEmbed& e, int batch, int heads) { return (e.sf.b != 0 ? batch : 1) * table_heads(e, heads); }
+// Table block of the attention workspace: [cos fp16][sin fp16], slices * n * r entries each (cos and sin lie in [-1, 1]:
+// 2^-12 absolute error, and the operand the image pre-pass builds from them is rounded to 8 or 11 bits anyway).
 struct TrigTables {
-  float *ctab, *stab;
   void *ch, *sh;
 };
-inline size_t trig_tables_bytes(int n, int r) { return ((size_t)n * r * 12 + 255) & ~(size_t)255; }
-inline TrigTables trig_tables_at(void* base, int n, int r) {
+inline size_t trig_tables_bytes(int n, int r, int slices = 1) { return ((size_t)slices * n * r * 4 + 255) & ~(size_t)255; }
+inline TrigTables trig_tables_at(void* base, int n, int r, int slices = 1) {
   TrigTables t;
-  t.ctab = static_cast<float*>(base), t.stab = t.ctab + (size_t)n * r;
-  t.ch = t.stab + (size_t)n * r, t.sh = static_cast<uint8_t*>(t.ch) + (size_t)n * r * 2;
+  t.ch = base, t.sh = static_cast<uint8_t*>(base) + (size_t)slices * n * r * 2;
   return t;
 }
 

@@ -24,6 +24,7 @@ namespace pope {
 template <typename T, int D>
 __global__ void __launch_bounds__(256) expand_image_kernel(ExpandJobs jobs, const __half* __restrict__ ctab,
                                                             const __half* __restrict__ stab) {
+  // (ctab / stab are advanced to the unit's table slice below)
   extern __shared__ __align__(16) uint8_t stage[];
   const ExpandJob& jb = jobs.job[blockIdx.z];
   const int tid = threadIdx.x, tile = blockIdx.x, u = blockIdx.y;
@@ -37,6 +38,10 @@ __global__ void __launch_bounds__(256) expand_image_kernel(ExpandJobs jobs, cons
   const Strides sx(jb.sx);
   const T* base = static_cast<const T*>(jb.x) + (int64_t)(u / jb.heads) * sx.b + (int64_t)(u % jb.heads) * sx.h;
   const float* bias = jb.bias;
+  {   // this unit's slice of the phase tables (a batched caller table has one slice per batch entry and / or head)
+    const int64_t slice = (int64_t)(jb.tab_by_batch ? u / jb.heads : 0) * jb.tab_heads + (u % jb.heads) % jb.tab_heads;
+    ctab += slice * jb.tab_rows * r, stab += slice * jb.tab_rows * r;
+  }
   if (bias) {
     for (int c = tid; c < r; c += 256) sincosf(bias[(int64_t)(u % jb.heads) * jb.bias_sh + c], &bias_s[c], &bias_c[c]);
     __syncthreads();

@@ -54,20 +54,26 @@ constexpr int SIM_THREADS = 320;
 
 // ch / sh (may be null): the same tables rounded to fp16 (cos and sin lie in [-1, 1]: 2^-12 absolute error), read by
 // the operand-image pre-pass, whose result is rounded to 8 or 11 bits anyway.
+// grid.y = table slice (batch entry x head of a batched caller table)
 __global__ void pope_trig_table_f32_kernel(PhaseSrc src, int n, int r, float* ctab, float* stab, __half* ch, __half* sh) {
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)n * r) return;
-  const int pos = idx / r, c = idx % r;
+  const int pos = idx / r, c = idx % r, slice = blockIdx.y;
+  if (!src.pos) src.freqs += (slice / src.tab_heads) * src.sfb + (slice % src.tab_heads) * src.sfh;
   float sn, cs;
   sincosf(src.at(pos, c), &sn, &cs);
+  idx += (int64_t)slice * n * r;
   if (ctab) stab[idx] = sn, ctab[idx] = cs;
   if (ch) ch[idx] = __float2half_rn(cs), sh[idx] = __float2half_rn(sn);
 }
 
-cudaError_t launch_trig_tables(const PopeEmbed& e, int n, int r, float* ctab, float* stab, void* ch, void* sh, cudaStream_t st) {
+cudaError_t launch_trig_tables(const PopeEmbed& e, int n, int r, float* ctab, float* stab, void* ch, void* sh, cudaStream_t st,
+                               int slices, int tab_heads) {
   const int64_t total = (int64_t)n * r;
-  pope_trig_table_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(phase_src(e), n, r, ctab, stab,
-                                                                               static_cast<__half*>(ch), static_cast<__half*>(sh));
+  PhaseSrc src = phase_src(e);
+  src.tab_heads = tab_heads;
+  pope_trig_table_f32_kernel<<<dim3((unsigned)((total + 255) / 256), (unsigned)slices), 256, 0, st>>>(
+      src, n, r, ctab, stab, static_cast<__half*>(ch), static_cast<__half*>(sh));
   return cudaGetLastError();
 }
 cudaError_t launch_trig_table_f32(const PopeEmbed& e, int n, int r, float* ctab, float* stab, cudaStream_t st) {

@@ -48,7 +48,11 @@ def test_attention_batched_freqs(kind, dtype, nq):
     qg, kg, vg = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
     fg, bg = freqs.to(DEV).requires_grad_(True), bias.to(DEV).requires_grad_(True)
     out = flash_attn_with_pope(qg, kg, vg, pos_emb=(fg, bg), causal=causal)
+    if dtype == torch.bfloat16 and nq >= 64:      # batched tables are served by the tensor-core kernels too
+        assert _native.last_path() == "tcgen05"
     out.backward(dout.to(DEV))
+    if dtype == torch.bfloat16 and nq >= 64:
+        assert _native.last_path() == "tcgen05" and _native.device_status() == 0
     assert fg.grad.shape == freqs.shape
     errs = {}
     for name, got in (("out", out), ("dq", qg.grad), ("dk", kg.grad), ("dv", vg.grad)):
