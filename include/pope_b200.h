@@ -132,6 +132,7 @@ typedef struct PopeSimBwdArgs {
   void* dk; PopeStride3 sdk;
   float* dfreqs; PopeStride3 sdf;   /* may be NULL */
   float* dbias; int64_t dbias_stride_h; /* may be NULL */
+  void* workspace; size_t workspace_bytes;  /* pope_b200_workspace_bytes(POPE_OP_SIM_BWD, &args); may be NULL when 0 */
 } PopeSimBwdArgs;
 
 /* ---- attention ----------------------------------------------------------------------------

@@ -47,7 +47,8 @@ class SimBwdArgs(C.Structure):
                 ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
                 ("dsim", C.c_void_p), ("sds", Stride3), ("dq", C.c_void_p), ("sdq", Stride3),
                 ("dk", C.c_void_p), ("sdk", Stride3), ("dfreqs", C.c_void_p), ("sdf", Stride3),
-                ("dbias", C.c_void_p), ("dbias_stride_h", C.c_int64)]
+                ("dbias", C.c_void_p), ("dbias_stride_h", C.c_int64),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
 class AttnArgs(C.Structure):
@@ -350,9 +351,11 @@ def sim_backward(dsim, q, k, freqs, bias, need_dfreqs, need_dbias, allow_tf32=Tr
                    dfreqs.data_ptr() if dfreqs is not None else None,
                    _freq_strides(dfreqs) if dfreqs is not None else Stride3(0, 0, 0),
                    dbias.data_ptr() if dbias is not None else None,
-                   dbias.stride(0) if dbias is not None else 0)
+                   dbias.stride(0) if dbias is not None else 0, None, 0)
+    ws = _workspace(OP_SIM_BWD, a, q.device)
     with torch.cuda.device(q.device):
         _check(lib.pope_b200_sim_bwd(C.addressof(a), _stream_ptr(q)), "pope_b200_sim_bwd")
+    del ws
     if need_dfreqs and dfreqs is None:
         dfreqs = torch.zeros_like(freqs)
     if need_dbias and dbias is None:

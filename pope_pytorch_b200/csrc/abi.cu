@@ -84,6 +84,11 @@ size_t pope_b200_workspace_bytes(int op, const void* args) {
       if (a.struct_bytes != sizeof(PopeSimArgs) || check_shape(a.shape) != POPE_OK) return 0;
       return (!force_simt() && pope::sim_fwd_tc_supported(a)) ? pope::sim_fwd_tc_workspace(a) : 0;
     }
+    case POPE_OP_SIM_BWD: {
+      const PopeSimBwdArgs& a = *static_cast<const PopeSimBwdArgs*>(args);
+      if (a.struct_bytes != sizeof(PopeSimBwdArgs) || check_shape(a.shape) != POPE_OK) return 0;
+      return (!force_simt() && pope::sim_bwd_tc_supported(a)) ? pope::sim_bwd_tc_workspace(a) : 0;
+    }
     case POPE_OP_ATTN_FWD: {
       const PopeAttnArgs& a = *static_cast<const PopeAttnArgs*>(args);
       if (a.struct_bytes != sizeof(PopeAttnArgs) || check_shape(a.shape) != POPE_OK) return 0;
@@ -124,9 +129,13 @@ int pope_b200_sim_bwd(const PopeSimBwdArgs* a, void* stream) {
   if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
   if (rc != POPE_OK) return rc;
   if (!a->q || !a->k || !a->dsim || !a->dq || !a->dk) return POPE_ERR_BAD_ARG;
+  // the tensor-core kernels need the operand images; a caller that passes no workspace gets the exact family
+  const bool tc = !force_simt() && pope::sim_bwd_tc_supported(*a) && a->workspace &&
+                  a->workspace_bytes >= pope::sim_bwd_tc_workspace(*a) && (reinterpret_cast<uintptr_t>(a->workspace) & 15) == 0;
   if ((rc = check_device()) != POPE_OK) return rc;
-  if (pope::sim_bwd_simt(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
-  g_last_path = "simt";
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((tc ? pope::sim_bwd_tc(*a, st) : pope::sim_bwd_simt(*a, st)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = tc ? "tcgen05" : "simt";
   return POPE_OK;
 }
 

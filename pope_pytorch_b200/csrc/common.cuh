@@ -43,6 +43,16 @@ __device__ __forceinline__ float softplus_fast(float x) {
   return fmaxf(x, 0.f) + lg2_approx(1.f + t) * 0.6931471805599453f;
 }
 
+// sin / cos for phases up to ~1e5 rad at ~1e-6 absolute error: two-constant Cody-Waite reduction to [-pi, pi]
+// (k * 6.28125 is exact for |k| < 2^15), then the special-function unit.  The accurate sincosf costs five times the
+// instructions; this form is for results that are rounded or tolerance-checked at 1e-5 or coarser.
+__device__ __forceinline__ void sincos_reduced(float x, float* s, float* c) {
+  const float k = rintf(x * 0.15915494309189535f);
+  float r = fmaf(-k, 6.28125f, x);
+  r = fmaf(-k, 1.9353071795864769e-3f, r);
+  *s = __sinf(r), *c = __cosf(r);
+}
+
 // Addressing of one (batch, head) unit of a strided tensor.
 struct Strides {
   int64_t b, h, n;

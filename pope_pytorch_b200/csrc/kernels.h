@@ -28,6 +28,9 @@ cudaError_t decode_stream(const PopeAttnArgs& a, cudaStream_t st);
 bool sim_fwd_tc_supported(const PopeSimArgs& a);
 size_t sim_fwd_tc_workspace(const PopeSimArgs& a);
 cudaError_t sim_fwd_tc(const PopeSimArgs& a, cudaStream_t st);
+bool sim_bwd_tc_supported(const PopeSimBwdArgs& a);
+size_t sim_bwd_tc_workspace(const PopeSimBwdArgs& a);
+cudaError_t sim_bwd_tc(const PopeSimBwdArgs& a, cudaStream_t st);
 bool attn_bwd_tc_supported(const PopeAttnBwdArgs& a);
 size_t attn_bwd_tc_workspace(const PopeAttnBwdArgs& a);
 cudaError_t attn_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st);

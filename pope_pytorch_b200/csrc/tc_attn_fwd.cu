@@ -87,6 +87,12 @@ bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, in
                  batch, sn, sh, sb, 8, box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
+bool make_load_tmap_f32(CUtensorMap* out, const void* base, int cols, int rows, int heads, int batch, int64_t sn, int64_t sh,
+                        int64_t sb, int box_rows) {
+  return tmap_4d(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, cols, rows, heads, batch, sn, sh, sb, 32, box_rows,
+                 CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 bool make_store_tmap(CUtensorMap* out, const void* base, int dtype, int cols, int rows, int heads, int batch, int64_t sn,
                      int64_t sh, int64_t sb, int box_rows) {
   const int esz = dtype == POPE_F32 ? 4 : 2;

@@ -134,22 +134,25 @@ constexpr int SIM_CSQ = SIM_M * 16;        // Q' chunk stride
 constexpr int SIM_STG_WARP = 32 * 128;     // staging tile of one worker warp: 32 rows x 128 bytes, 128-byte swizzled
 
 // ---- pre-pass: expanded operand tiles ------------------------------------------------------------------------------
-// grid.x = 4 x (query row tiles + key tiles), grid.y = max(B * H, B * Hk) units.  A block expands 32 rows (a quarter of a
-// 128-row tile: small blocks keep the pre-pass of a small problem short) of one unit into the tile image
-// [hi | lo][chunk][128 rows][16 B].  Expanded columns: d cos/pass columns, then r sin columns.  Phases as the reference
+// grid.x = (query rows + key rows) / 32 (each rounded up to whole tiles), grid.y = max(B * H, B * Hk) units.  A block
+// expands 32 rows (small blocks keep the pre-pass of a small problem short) of one unit into the tile image
+// [hi | lo][chunk][tile_rows rows][16 B]; tile_rows is 128 for the forward kernel and 64 for the backward kernel, whose
+// steps consume 64 rows of the swept operand.  Expanded columns: d cos/pass columns, then r sin columns.  Phases as the reference
 // computes them (PoPE_pytorch/pope.py:56-79): query row i uses freqs[Nk - Nq + i], key row j uses fl(freqs[j] + bias[hk]);
-// accurate sincosf, softplus through ex2 / lg2 (2^-22 relative, far inside the 1e-5 the split product needs).
+// range-reduced sin / cos (1e-6 absolute) and softplus through ex2 / lg2 (2^-22 relative): far inside the 1e-5 the split
+// product needs.
 // The 8-feature chunks of the 32 rows are numbered row-major and thread t takes chunks t, t + 256, ...: a warp's loads
 // cover whole rows.  Rows past the end of the operand become zeros.
 template <typename T, bool SPLIT>
 __global__ void __launch_bounds__(256) sim_prepass_kernel(const T* __restrict__ q, Strides sq, const T* __restrict__ k, Strides sk,
                                                           PhaseSrc src,
                                                           const float* __restrict__ bias, int64_t bias_sh, int B, int H, int Hk, int Nq,
-                                                          int Nk, int d, int r, int qtiles, int ktiles,
+                                                          int Nk, int d, int r, int qtiles, int ktiles, int tile_rows,
                                                           uint8_t* __restrict__ qimg, uint8_t* __restrict__ kimg) {
   const int tid = threadIdx.x, u = blockIdx.y;
-  const bool is_q = (int)blockIdx.x < 4 * qtiles;
-  const int blk = is_q ? blockIdx.x : blockIdx.x - 4 * qtiles, tile = blk >> 2, quarter = blk & 3;
+  const int bpt = tile_rows / 32;   // blocks per tile
+  const bool is_q = (int)blockIdx.x < bpt * qtiles;
+  const int blk = is_q ? blockIdx.x : blockIdx.x - bpt * qtiles, tile = blk / bpt, quarter = blk % bpt;
   const int heads = is_q ? H : Hk, rows = is_q ? Nq : Nk, tiles = is_q ? qtiles : ktiles;
   const int b = u / heads, h = u % heads;
   if (b >= B) return;   // grid.y covers the larger of the two unit counts
@@ -158,10 +161,10 @@ __global__ void __launch_bounds__(256) sim_prepass_kernel(const T* __restrict__ 
   const T* base = (is_q ? q : k) + (int64_t)b * sx.b + (int64_t)h * sx.h;
   const int pos0 = is_q ? Nk - Nq : 0;
   const float* brow = is_q ? nullptr : bias + (int64_t)h * bias_sh;
-  const int csb = is_q ? SIM_CSQ : SIM_CSK;
+  const int csb = tile_rows * 16;
   uint8_t* img = (is_q ? qimg : kimg) + ((int64_t)u * tiles + tile) * ((int64_t)KC * (SPLIT ? 2 : 1) * csb);
   for (int f = tid; f < 32 * DC; f += 256) {
-    const int row = quarter * 32 + f / DC, c = f % DC, j = tile * SIM_M + row;
+    const int row = quarter * 32 + f / DC, c = f % DC, j = tile * tile_rows + row;
     const bool ok = j < rows;
     uint8_t* dst = img + row * 16;
     float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -179,7 +182,7 @@ __global__ void __launch_bounds__(256) sim_prepass_kernel(const T* __restrict__ 
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           float sn, cs;
-          sincosf(brow ? fr[e] + brow[c * 8 + e] : fr[e], &sn, &cs);
+          sincos_reduced(brow ? fr[e] + brow[c * 8 + e] : fr[e], &sn, &cs);
           const float a = softplus_fast(x[e]);
           vc[e] = a * cs, vs[e] = a * sn;
         }
@@ -423,6 +426,34 @@ static size_t sim_qimg_bytes(const PopeShape& s) {
 }
 static size_t sim_kimg_bytes(const PopeShape& s) { return (size_t)s.B * s.Hk * ((s.Nk + SIM_N - 1) / SIM_N) * sim_tile_bytes(s); }
 size_t sim_fwd_tc_workspace(const PopeSimArgs& a) { return sim_qimg_bytes(a.shape) + sim_kimg_bytes(a.shape); }
+// the same images serve the backward (tc_sim_bwd.cu): total bytes, and the offset of the K' images
+size_t sim_fwd_tc_image_bytes(const PopeShape& s, size_t* q_bytes) {
+  if (q_bytes) *q_bytes = sim_qimg_bytes(s);
+  return sim_qimg_bytes(s) + sim_kimg_bytes(s);
+}
+
+cudaError_t sim_launch_prepass(const PopeShape& s, const PopeEmbed& e, const void* q, const PopeStride3& sq, const void* k,
+                               const PopeStride3& sk, uint8_t* qimg, uint8_t* kimg, int tile_rows, cudaStream_t st) {
+  const int qtiles = (s.Nq + tile_rows - 1) / tile_rows, ktiles = (s.Nk + tile_rows - 1) / tile_rows;
+  const dim3 grid((tile_rows / 32) * (qtiles + ktiles), s.B * s.H);
+  switch (s.dtype) {
+    case POPE_F32:
+      sim_prepass_kernel<float, true><<<grid, 256, 0, st>>>(static_cast<const float*>(q), Strides(sq), static_cast<const float*>(k),
+                                                            Strides(sk), phase_src(e), e.bias, e.bias_stride_h, s.B, s.H, s.Hk,
+                                                            s.Nq, s.Nk, s.d, s.r, qtiles, ktiles, tile_rows, qimg, kimg);
+      break;
+    case POPE_BF16:
+      sim_prepass_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(q), Strides(sq), static_cast<const __nv_bfloat16*>(k), Strides(sk), phase_src(e), e.bias,
+          e.bias_stride_h, s.B, s.H, s.Hk, s.Nq, s.Nk, s.d, s.r, qtiles, ktiles, tile_rows, qimg, kimg);
+      break;
+    default:
+      sim_prepass_kernel<__half, false><<<grid, 256, 0, st>>>(static_cast<const __half*>(q), Strides(sq), static_cast<const __half*>(k),
+                                                              Strides(sk), phase_src(e), e.bias, e.bias_stride_h, s.B, s.H, s.Hk,
+                                                              s.Nq, s.Nk, s.d, s.r, qtiles, ktiles, tile_rows, qimg, kimg);
+  }
+  return cudaGetLastError();
+}
 
 template <typename T, bool SPLIT, int MT, int NKB>
 static cudaError_t launch_sim_tc(const PopeSimArgs& a, cudaStream_t st) {
@@ -439,10 +470,7 @@ static cudaError_t launch_sim_tc(const PopeSimArgs& a, cudaStream_t st) {
   p.ktiles = (s.Nk + SIM_N - 1) / SIM_N;
   p.rblocks = (qtiles + MT - 1) / MT;
   p.total_tiles = (int64_t)s.B * s.H * p.rblocks * p.ktiles;
-  sim_prepass_kernel<T, SPLIT><<<dim3(4 * (qtiles + p.ktiles), s.B * s.H), 256, 0, st>>>(
-      static_cast<const T*>(a.q), Strides(a.sq), static_cast<const T*>(a.k), Strides(a.sk), phase_src(a.embed),
-      a.embed.bias, a.embed.bias_stride_h, s.B, s.H, s.Hk, s.Nq, s.Nk, s.d, s.r, qtiles, p.ktiles, qimg, kimg);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = sim_launch_prepass(s, a.embed, a.q, a.sq, a.k, a.sk, qimg, kimg, SIM_M, st);
   if (e != cudaSuccess) return e;
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));

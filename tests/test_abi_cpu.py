@@ -39,7 +39,7 @@ def test_exports_match_header(lib):
 def test_struct_layout_matches_c(tmp_path):
     fields = {
         "PopeSimArgs": (N.SimArgs, ["shape", "embed", "q", "sim", "ss", "workspace", "workspace_bytes"]),
-        "PopeSimBwdArgs": (N.SimBwdArgs, ["dsim", "dq", "dfreqs", "dbias_stride_h"]),
+        "PopeSimBwdArgs": (N.SimBwdArgs, ["dsim", "dq", "dfreqs", "dbias_stride_h", "workspace", "workspace_bytes"]),
         "PopeAttnArgs": (N.AttnArgs, ["softmax_scale", "shape", "embed", "v", "lse", "mask", "workspace_bytes"]),
         "PopeAttnBwdArgs": (N.AttnBwdArgs, ["dout", "lse", "mask_stride_n", "dq", "dv", "dfreqs", "dbias", "workspace"]),
         "PopeApplyArgs": (N.ApplyArgs, ["shape", "embed", "q", "k", "q_out", "sqo", "k_out", "sko"]),

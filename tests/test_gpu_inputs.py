@@ -102,6 +102,7 @@ def test_similarity_multi_tile_forward_and_gradients(b, h, hk, nq, nk, d, r, all
     errs = dict(sim_rel=maxerr(sim, ref["sim"]) / scale)
     assert errs["sim_rel"] <= 1e-4
     sim.backward(dsim.to(DEV))
+    assert _native.last_path() == "tcgen05" and _native.device_status() == 0   # forward AND backward on the tensor cores
     # gradients are sums over up to 1024 score gradients of magnitude ~1: the reference's own bound
     # (rtol 1e-3, atol 1e-4) applies to unit-scale entries, so the absolute part scales with the largest entry
     for name, got in (("dq", qg.grad), ("dk", kg.grad), ("dbias", bg.grad), ("dfreqs", fg.grad)):
