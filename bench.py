@@ -44,12 +44,11 @@ UNIT = "TFLOP/s"
 
 # DRAM bytes (read + write) per launch of each kernel of one training step at B=1 (16 units), from the ncu
 # captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); traffic is proportional to
-# the number of (batch, head) units, so a B=4 launch moves 4x these.  Constants, not live measurements.  The row
-# statistics kernel was not captured: its entry is its algorithmic bytes (one read of out and dO).
+# the number of (batch, head) units, so a B=4 launch moves 4x these.  Constants, not live measurements.
 NCU_TRAFFIC_B1 = {
-    "fwd": {"expand_image_kernel": 49.6e6, "attn_fwd_tc_kernel": 89.2e6},
-    "bwd": {"bwd_rowstat_kernel": 33.6e6, "expand_image_kernel": 117.9e6, "attn_bwd_dq_tc_kernel": 109.8e6,
-            "attn_bwd_dkdv_tc_kernel": 117.4e6},
+    "fwd": {"expand_image_kernel": 49.6e6, "attn_fwd_tc_kernel": 89.0e6},
+    "bwd": {"bwd_rowstat_kernel": 33.8e6, "expand_image_kernel": 118.9e6, "attn_bwd_dq_tc_kernel": 108.8e6,
+            "attn_bwd_dkdv_tc_kernel": 117.0e6},
 }
 
 
