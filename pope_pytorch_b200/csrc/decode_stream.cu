@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(32 * (NW + 1), MINB) attn_decode_stream_kernel
       const int s = jt % p.nstages, key0 = kb + jt * TILE, n = min(TILE, ke - key0);
       uint8_t* st = smem + (size_t)s * stage_bytes;
       if (jt >= p.nstages) failed = !mbar_wait(&empty[s], ((jt / p.nstages) - 1) & 1, WAIT_LIMIT);
-      if (failed) break;
+      if (failed) { drain_copies(full, p.nstages, jt - p.nstages, jt); break; }
       if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)(2 * n * D * 2 + 2 * n * r * 2));
       __syncwarp();
       if (p.k_rows_contiguous) {

@@ -50,6 +50,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return false;
 }
 
+// After a wait has given up, a copy-issuing thread calls this for the copies it still has in flight (tiles
+// [first, end) of a ring of `nst` stages whose "landed" barriers start at `full`), so that the CTA does not leave while
+// the copy engine still writes into its shared memory.  Bounded as well (about 40 ms per stage).
+__device__ __forceinline__ void drain_copies(uint64_t* full, int nst, int first, int end) {
+  for (int t = first < 0 ? 0 : first; t < end; ++t) mbar_wait(&full[t % nst], (uint32_t)(t / nst) & 1u, 1u << 12);
+}
+
 // ---- TMA: tiled bulk tensor load into this CTA's shared memory (no multicast) -------------------
 // `tmap` is the address of a CUtensorMap kernel parameter (__grid_constant__).  The innermost coordinate
 // times the element size must be a multiple of 16 bytes.  Rows outside the tensor arrive as zeros.

@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         const int st = j % DQ_NST, n0 = tile_start(j);
         // the stage was last read by the accumulation step of tile j - NST
         if (j >= DQ_NST && !failed) failed = !mbar_wait(&bars[BB_ACC + st], ((j - DQ_NST) / DQ_NST) & 1, WAIT_LIMIT);
-        if (failed) break;
+        if (failed) { drain_copies(&bars[BB_FULL], DQ_NST, j - DQ_NST, j); break; }
         mbar_expect_tx(&bars[BB_FULL + st], KBUF + VBUF);
         bulk_load(Ks + st * KBUF, kimg + (int64_t)(n0 / BT) * KBUF, KBUF, &bars[BB_FULL + st]);
         bulk_load(Vs + st * VBUF, vimg + (int64_t)(n0 / BT) * VBUF, VBUF, &bars[BB_FULL + st]);

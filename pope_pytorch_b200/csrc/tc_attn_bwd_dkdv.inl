@@ -91,12 +91,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
         const int sq = j % KQ_NST, sg = j % KG_NST, m0 = tile_start(j), h = tile_head(j);
         const int64_t t = (int64_t)(b * p.H + h) * qtiles + m0 / BT;
         if (j >= KQ_NST && !failed) failed = !mbar_wait(&bars[KB_ACCQ + sq], ((j - KQ_NST) / KQ_NST) & 1, WAIT_LIMIT);
-        if (failed) break;
+        if (failed) { drain_copies(&bars[KB_QFULL], KQ_NST, j - KQ_NST, j), drain_copies(&bars[KB_GFULL], KG_NST, j - KG_NST, j); break; }
         mbar_expect_tx(&bars[KB_QFULL + sq], KBUF + 2 * BT * 4);
         bulk_load(Qb + sq * KBUF, p.qimg + t * KBUF, KBUF, &bars[KB_QFULL + sq]);
         bulk_load(rowstat + sq * 128, p.rowstat + t * 128, 2 * BT * 4, &bars[KB_QFULL + sq]);
         if (j >= KG_NST && !failed) failed = !mbar_wait(&bars[KB_ACCG + sg], ((j - KG_NST) / KG_NST) & 1, WAIT_LIMIT);
-        if (failed) break;
+        if (failed) { drain_copies(&bars[KB_QFULL], KQ_NST, j + 1 - KQ_NST, j + 1), drain_copies(&bars[KB_GFULL], KG_NST, j - KG_NST, j); break; }
         mbar_expect_tx(&bars[KB_GFULL + sg], VBUF);
         bulk_load(Gb + sg * VBUF, p.gimg + t * VBUF, VBUF, &bars[KB_GFULL + sg]);
       }

@@ -210,18 +210,21 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
     // would hold back the K' copy that the next score product is waiting for.
     if (lane == 0) {
       const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * KBUF;
-      for (int j = 0; j < T_tiles; ++j) {
+      int j = 0;
+      for (; j < T_tiles; ++j) {
         const int buf = j & 1;
         if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_KFREE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
         if (failed) break;
         mbar_expect_tx(&bars[B_KFULL + buf], KBUF);
         bulk_load(Ks + buf * KBUF, kimg + (int64_t)j * KBUF, KBUF, &bars[B_KFULL + buf]);
       }
+      if (failed) drain_copies(&bars[B_KFULL], 2, j - 2, j), drain_copies(&bars[B_QFULL], 1, 0, 1);
     } else if (lane == 1) {
-      for (int j = 0; j < T_tiles; ++j) {
+      int j = 0;
+      for (; j < T_tiles; ++j) {
         const int buf = j & 1, n0 = j * TK;
         if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
-        if (failed) break;
+        if (failed) { drain_copies(&bars[B_VFULL], 2, j - 2, j); break; }
         mbar_expect_tx(&bars[B_VFULL + buf], VBUF);
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) tma_load_4d(Vs + buf * VBUF + c * CS, &tmap_v, &bars[B_VFULL + buf], c * 8, n0, hk, b);

@@ -19,90 +19,112 @@
 
 namespace pope {
 
-// grid (tiles, units, jobs), 256 threads; dynamic shared memory (d+r)/8 * CS64 bytes + 2 r floats.  One launch
+// grid (tiles / 4, units, jobs), 256 threads; dynamic shared memory (d+r)/8 * CS64 bytes + 2 r floats.  One launch
 // builds the images of up to four operands (blockIdx.z picks the job); CTAs outside a job's tile / unit range leave.
+// A CTA builds EXPAND_TPC consecutive tiles of one unit.  A thread keeps the same 16-byte feature group (chunk) for
+// every row it touches, so whether it rotates at all, and the cos / sin of the head's phase offset for its eight
+// features, are fixed for its lifetime (registers instead of 16 shared-memory loads per group); the raw rows of the
+// next tile are requested before the current tile is worked on.
+constexpr int EXPAND_TPC = 4;
 template <typename T, int D>
-__global__ void __launch_bounds__(256) expand_image_kernel(ExpandJobs jobs, const __half* __restrict__ ctab,
+__global__ void __launch_bounds__(256, 3) expand_image_kernel(ExpandJobs jobs, const __half* __restrict__ ctab,
                                                             const __half* __restrict__ stab) {
   // (ctab / stab are advanced to the unit's table slice below)
   extern __shared__ __align__(16) uint8_t stage[];
   const ExpandJob& jb = jobs.job[blockIdx.z];
-  const int tid = threadIdx.x, tile = blockIdx.x, u = blockIdx.y;
-  const int tiles = (int)image_tiles(jb.rows);
-  if (tile >= tiles || u >= jb.units) return;
+  const int tid = threadIdx.x, u = blockIdx.y;
+  const int tiles = (int)image_tiles(jb.rows);   // a multiple of EXPAND_TPC
+  const int tile0 = blockIdx.x * EXPAND_TPC;
+  if (tile0 >= tiles || u >= jb.units) return;
   const int r = jb.r, rows = jb.rows;
   constexpr int DC = D >> 3;
+  constexpr int RPP = 256 / DC;                          // rows per pass of the 256 threads
+  constexpr int NIT = (IMAGE_ROWS + RPP - 1) / RPP;      // passes per tile
   const int RC = r >> 3, KC = DC + RC;
+  const int c = tid % DC, row0 = tid / DC;
+  const bool active = row0 < RPP, rotated = c < RC;
   float* bias_c = reinterpret_cast<float*>(stage + KC * CS64);   // cos / sin of this head's phase offset
   float* bias_s = bias_c + r;
   const Strides sx(jb.sx);
-  const T* base = static_cast<const T*>(jb.x) + (int64_t)(u / jb.heads) * sx.b + (int64_t)(u % jb.heads) * sx.h;
+  const T* base = static_cast<const T*>(jb.x) + (int64_t)(u / jb.heads) * sx.b + (int64_t)(u % jb.heads) * sx.h + c * 8;
   const float* bias = jb.bias;
   {   // this unit's slice of the phase tables (a batched caller table has one slice per batch entry and / or head)
     const int64_t slice = (int64_t)(jb.tab_by_batch ? u / jb.heads : 0) * jb.tab_heads + (u % jb.heads) % jb.tab_heads;
-    ctab += slice * jb.tab_rows * r, stab += slice * jb.tab_rows * r;
+    ctab += slice * jb.tab_rows * r + c * 8, stab += slice * jb.tab_rows * r + c * 8;
   }
+  float cb[8], sb[8];
   if (bias) {
-    for (int c = tid; c < r; c += 256) sincosf(bias[(int64_t)(u % jb.heads) * jb.bias_sh + c], &bias_s[c], &bias_c[c]);
+    for (int i = tid; i < r; i += 256) sincosf(bias[(int64_t)(u % jb.heads) * jb.bias_sh + i], &bias_s[i], &bias_c[i]);
     __syncthreads();
+    if (rotated) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) cb[e] = bias_c[c * 8 + e], sb[e] = bias_s[c * 8 + e];
+    }
   }
-  // phase 1: 16-byte groups in row-major order (a warp reads 512 contiguous bytes of a row pair); the
-  // padded chunk stride keeps the shared-memory stores of a warp on distinct banks.  All raw rows of the
-  // thread are requested before the first one is used.
-  constexpr int NIT = IMAGE_ROWS * DC / 256;
-  uint4 raw[NIT];
+  auto load_raw = [&](int tile, uint4 (&raw)[NIT]) {
 #pragma unroll
-  for (int it = 0; it < NIT; ++it) {
-    const int f = tid + it * 256, row = f / DC, c = f - row * DC, j = tile * IMAGE_ROWS + row;
-    raw[it] = make_uint4(0, 0, 0, 0);
-    if (j < rows) raw[it] = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)j * sx.n + c * 8));
-  }
+    for (int it = 0; it < NIT; ++it) {
+      const int row = row0 + it * RPP, jrow = tile * IMAGE_ROWS + row;
+      raw[it] = make_uint4(0, 0, 0, 0);
+      if (active && row < IMAGE_ROWS && jrow < rows) raw[it] = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)jrow * sx.n));
+    }
+  };
+  for (int tt = 0; tt < EXPAND_TPC; ++tt) {
+    const int tile = tile0 + tt;
+    uint4 raw[NIT];
+    load_raw(tile, raw);
+    // phase 1: 16-byte groups in row-major order (a warp reads 512 contiguous bytes of a row pair); the
+    // padded chunk stride keeps the shared-memory stores of a warp on distinct banks.
+    if (rotated) {
+      uint4 cq[NIT], sq[NIT];
 #pragma unroll
-  for (int it = 0; it < NIT; ++it) {
-    const int f = tid + it * 256, row = f / DC, c = f - row * DC, j = tile * IMAGE_ROWS + row;
-    if (c < RC) {
-      uint4 oc = make_uint4(0, 0, 0, 0), os = oc;
-      if (j < rows) {
-        const uint4 cq = __ldg(reinterpret_cast<const uint4*>(ctab + (int64_t)(jb.pos0 + j) * r + c * 8));
-        const uint4 sq = __ldg(reinterpret_cast<const uint4*>(stab + (int64_t)(jb.pos0 + j) * r + c * 8));
-        const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w}, sw[4] = {sq.x, sq.y, sq.z, sq.w};
-        float co[8], si[8];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 cv = unpack2<__half>(cw[e]), sv = unpack2<__half>(sw[e]);
-          co[2 * e] = cv.x, co[2 * e + 1] = cv.y, si[2 * e] = sv.x, si[2 * e + 1] = sv.y;
+      for (int it = 0; it < NIT; ++it) {
+        const int row = row0 + it * RPP, jrow = tile * IMAGE_ROWS + row;
+        cq[it] = sq[it] = make_uint4(0, 0, 0, 0);
+        if (active && row < IMAGE_ROWS && jrow < rows) {
+          cq[it] = __ldg(reinterpret_cast<const uint4*>(ctab + (int64_t)(jb.pos0 + jrow) * r));
+          sq[it] = __ldg(reinterpret_cast<const uint4*>(stab + (int64_t)(jb.pos0 + jrow) * r));
         }
-        if (bias) {   // cos(f + b), sin(f + b)
+      }
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float cb = bias_c[c * 8 + e], sb = bias_s[c * 8 + e], cf = co[e], sf = si[e];
-            co[e] = cf * cb - sf * sb;
-            si[e] = sf * cb + cf * sb;
-          }
-        }
+      for (int it = 0; it < NIT; ++it) {
+        const int row = row0 + it * RPP;
+        if (!active || row >= IMAGE_ROWS) continue;
+        // (rows past the end carry zero raw words and zero table words: softplus(0) * 0 = 0)
+        const uint32_t cw[4] = {cq[it].x, cq[it].y, cq[it].z, cq[it].w}, sw[4] = {sq[it].x, sq[it].y, sq[it].z, sq[it].w};
         const uint32_t rw[4] = {raw[it].x, raw[it].y, raw[it].z, raw[it].w};
         uint32_t o1[4], o2[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
+          float2 cv = unpack2<__half>(cw[e]), sv = unpack2<__half>(sw[e]);
+          if (bias) {   // cos(f + b), sin(f + b)
+            const float c0 = cv.x * cb[2 * e] - sv.x * sb[2 * e], s0 = sv.x * cb[2 * e] + cv.x * sb[2 * e];
+            const float c1 = cv.y * cb[2 * e + 1] - sv.y * sb[2 * e + 1], s1 = sv.y * cb[2 * e + 1] + cv.y * sb[2 * e + 1];
+            cv = make_float2(c0, c1), sv = make_float2(s0, s1);
+          }
           const float2 xv = unpack2<T>(rw[e]);
           const float a0 = softplus_fast(xv.x), a1 = softplus_fast(xv.y);
-          o1[e] = pack2<T>(a0 * co[2 * e], a1 * co[2 * e + 1]);
-          o2[e] = pack2<T>(a0 * si[2 * e], a1 * si[2 * e + 1]);
+          o1[e] = pack2<T>(a0 * cv.x, a1 * cv.y);
+          o2[e] = pack2<T>(a0 * sv.x, a1 * sv.y);
         }
-        oc = make_uint4(o1[0], o1[1], o1[2], o1[3]), os = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+        *reinterpret_cast<uint4*>(stage + c * CS64 + row * 16) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+        *reinterpret_cast<uint4*>(stage + (DC + c) * CS64 + row * 16) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
       }
-      *reinterpret_cast<uint4*>(stage + c * CS64 + row * 16) = oc;
-      *reinterpret_cast<uint4*>(stage + (DC + c) * CS64 + row * 16) = os;
     } else {
-      *reinterpret_cast<uint4*>(stage + c * CS64 + row * 16) = raw[it];
+#pragma unroll
+      for (int it = 0; it < NIT; ++it) {
+        const int row = row0 + it * RPP;
+        if (active && row < IMAGE_ROWS) *reinterpret_cast<uint4*>(stage + c * CS64 + row * 16) = raw[it];
+      }
     }
-  }
-  __syncthreads();
-  // phase 2: the image leaves in its own byte order, 16 bytes per thread, fully coalesced
-  uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(jb.img) + ((int64_t)u * tiles + tile) * ((int64_t)IMAGE_ROWS * KC * 16));
-  for (int g = tid; g < IMAGE_ROWS * KC; g += 256) {
-    const int c = g / IMAGE_ROWS, row = g - c * IMAGE_ROWS;
-    out[g] = *reinterpret_cast<const uint4*>(stage + c * CS64 + row * 16);
+    __syncthreads();
+    // phase 2: the image leaves in its own byte order, 16 bytes per thread, fully coalesced
+    uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(jb.img) + ((int64_t)u * tiles + tile) * ((int64_t)IMAGE_ROWS * KC * 16));
+    for (int g = tid; g < IMAGE_ROWS * KC; g += 256) {
+      const int cc = g / IMAGE_ROWS, row = g - cc * IMAGE_ROWS;
+      out[g] = *reinterpret_cast<const uint4*>(stage + cc * CS64 + row * 16);
+    }
+    if (tt + 1 < EXPAND_TPC) __syncthreads();   // the stage is rewritten by the next tile
   }
 }
 
@@ -115,7 +137,7 @@ static cudaError_t launch_expand_t(const ExpandJobs& jobs, int njobs, int d, con
     units = std::max(units, jobs.job[i].units);
     rmax = std::max(rmax, jobs.job[i].r);
   }
-  const dim3 grid((unsigned)tiles, (unsigned)units, (unsigned)njobs);
+  const dim3 grid((unsigned)(tiles / EXPAND_TPC), (unsigned)units, (unsigned)njobs);
   const size_t smem = (size_t)((d + rmax) / 8) * CS64 + 2 * (size_t)rmax * sizeof(float);
   switch (d) {
     case 64: expand_image_kernel<T, 64><<<grid, 256, smem, st>>>(jobs, ctab, stab); break;

@@ -125,6 +125,9 @@ __global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p,
           bulk_load(Img + buf * img_bytes, tile, img_bytes, &bars[WB_IFULL + buf]);
         }
       }
+      // a wait gave up: let the copies in flight land before the CTA may leave (the G tile of step s was issued
+      // unless its own wait failed; counting it in costs one more bounded wait at most)
+      if (failed && lane == 0) drain_copies(&bars[WB_GFULL], SBW_GST, s + 1 - SBW_GST, s + 1), drain_copies(&bars[WB_IFULL], 2, s - 2, s);
       failed = __shfl_sync(0xffffffffu, failed, 0);
     }
     if (failed && lane == 0) atomicOr(p.status, 1u);

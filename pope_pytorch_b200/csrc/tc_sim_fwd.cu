@@ -262,7 +262,8 @@ __global__ void __launch_bounds__(SIM_THREADS, 1) sim_fwd_tc_kernel(TcSimP p, co
   if (warp == SIM_LOAD_WARP) {
     // =============================== copies: one K' tile per step ==============================
     if (lane == 0) {
-      for (int t = 0; t < ntiles && !failed; ++t) {
+      int t = 0;
+      for (; t < ntiles && !failed; ++t) {
         const int64_t g = g_begin + t, rbg = g / p.ktiles;
         const int kt = (int)(g - rbg * p.ktiles), u = (int)(rbg / p.rblocks), b = u / p.H, hk = (u % p.H) % p.Hk;
         if (starts_block(t)) {
@@ -283,7 +284,11 @@ __global__ void __launch_bounds__(SIM_THREADS, 1) sim_fwd_tc_kernel(TcSimP p, co
         mbar_expect_tx(full, opk_bytes);
         bulk_load(Kb + (t % NKB) * opk_bytes, p.kimg + ((int64_t)(b * p.Hk + hk) * p.ktiles + kt) * opk_bytes, opk_bytes, full);
       }
-      if (failed) atomicOr(p.status, 1u);
+      if (failed) {   // let the copies in flight land before the CTA may leave (the Q' tiles: whichever phase is pending)
+        drain_copies(&bars[SB_KFULL], NKB, t - NKB, t);
+        mbar_wait(&bars[SB_QFULL], 0, 1u << 11), mbar_wait(&bars[SB_QFULL], 1, 1u << 11);
+        atomicOr(p.status, 1u);
+      }
     }
     __syncwarp();
   } else if (warp == SIM_MMA_WARP) {
