@@ -44,7 +44,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
 #endif
 // Bounded wait: gives up after `limit` parked tries (about limit x 10 us in the worst case) and returns
 // false; the caller records the failure in a status word and unwinds.  A healthy wait takes microseconds.
+// non-blocking test of a phase
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok)
+               : "r"(smem_u32(bar)), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 17)) {
+  if (mbar_test(bar, parity)) return true;   // a phase that is already complete: no parked wait at all
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity, POPE_WAIT_HINT_NS)) return true;
   return false;

@@ -4,18 +4,20 @@
 // followed by the chain rule through the transform (PoPE_pytorch/triton_pope.py:129-151, 174-194, 246-256):
 //   dx = (dXc cos + dXs sin) sigmoid(x),  dphase = a (dXs cos - dXc sin)  -> dfreqs, and dbias on the key side.
 //
-// The work is one read of G per side (bytes = 4 Nq Nk per unit and side: HBM-bound), so the kernel is built around that
-// stream.  Two launches of one template: the query side keeps 128 query rows and their 128 x (d + r) accumulator
-// resident and sweeps the keys 64 at a time; the key side keeps 128 key rows resident and sweeps the query rows of all
-// grouped query heads.  Per step
-//   loader warp   : the 32 KB tile of G by tensor-map copies (boxes of 32 fp32 columns, 128-byte swizzled; rows and
-//                   columns past the end arrive as zeros) and the matching 64-row tile of the OTHER operand's expanded
-//                   image (hi | lo, built by the pre-pass in the forward kernel's file with 64-row tiles) by one bulk copy
+// The work is one read of G per side (bytes = 4 Nq Nk per unit and side), so the kernel is built around that stream.
+// ONE launch runs both sides: a query-side CTA keeps 128 query rows and their 128 x (d + r) accumulator resident and
+// sweeps the keys 64 at a time; a key-side CTA keeps 128 key rows resident and sweeps the query rows of all grouped
+// query heads.  The CTAs of a head run in the same wave and sweep in opposite directions from their diagonal block, so
+// the second read of every block of G is served by L2 (DRAM traffic 1.2 x G instead of 2 x).  Per step
+//   loader warp   : two lanes, each streaming on its own: the 32 KB tile of G by tensor-map copies (boxes of 32 fp32
+//                   columns, 128-byte swizzled; rows and columns past the end arrive as zeros), and the matching 64-row
+//                   tile of the OTHER operand's expanded image (hi | lo, built by the pre-pass in the forward kernel's
+//                   file with 64-row tiles) by one bulk copy
 //   8 worker warps: a thread per row pulls its 32 values out of the staging tile, splits each into two bf16 numbers
 //                   G = hi + lo and writes them as 16-byte chunks of 8 keys; that one layout serves both sides -- as the
 //                   K-major A operand of G K' and, re-described as MN-major, as the A operand of G^T Q'
-//   issuing warp  : three MMA chains per step, hi*hi' + hi*lo' + lo*hi' (fp32 accuracy from bf16 products, as in the
-//                   forward), accumulating in TMEM over the whole sweep
+//   issuing warps : two, taking the even and the odd steps: three MMA chains per step, hi*hi' + hi*lo' + lo*hi' (fp32
+//                   accuracy from bf16 products, as in the forward), accumulating in TMEM over the whole sweep
 // and the epilogue applies the chain rule with accurate sincosf / softplus on the rows it owns.
 #include <algorithm>
 #include <cstring>
@@ -25,8 +27,8 @@
 
 namespace pope {
 
-constexpr int SBW_THREADS = 320;     // 8 worker warps, the MMA-issuing warp, the loader warp
-constexpr int SBW_MMA_WARP = 8, SBW_LOAD_WARP = 9;
+constexpr int SBW_THREADS = 352;     // 8 worker warps, two MMA-issuing warps (even / odd steps), the loader warp
+constexpr int SBW_MMA_WARP = 8, SBW_LOAD_WARP = 9, SBW_MMA2_WARP = 10;
 constexpr int SBW_STG = 32 * 1024;   // one staged G tile (fp32) and one converted G tile (hi | lo bf16)
 constexpr int SBW_GST = 3;           // staging buffers of G: two tiles in flight while one is converted
 constexpr int SBW_CS_HALF = 64 * 16; // chunk stride of a 64-row operand image tile
@@ -55,10 +57,13 @@ enum { WB_GFULL = 0,     // [3] the G tile of step s has landed in staging buffe
        WB_CONV = 6,      // [2] 8 worker warps: the converted tile of step s is in buffer s & 1
        WB_IFULL = 8,     // [2] the operand tile of step s has landed in buffer s & 1 (transaction bytes)
        WB_DONE = 10,     // [2] tcgen05.commit: the chains of step s have completed: both buffers s & 1 are free
-       WB_COUNT = 12 };
+       WB_HEAD = 12,     // the first instruction of step 0 (the one that overwrites the accumulator) has been issued
+       WB_COUNT = 13 };
 
+// One side of the backward for one CTA: resident block `blk` (128 rows) of unit `u` (batch x query heads on the query
+// side, batch x key heads on the key side).
 template <typename T, bool KEY_SIDE>
-__global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p, const __grid_constant__ CUtensorMap tmap_g) {
+__device__ __forceinline__ void sim_bwd_side(const TcSimBwdP& p, const CUtensorMap* tmap_g, int blk, int u) {
   static_assert(sizeof(T) == 4, "the tensor-core similarity backward serves fp32");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -77,9 +82,9 @@ __global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p,
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int heads_out = KEY_SIDE ? p.Hk : p.H;
-  const int u = blockIdx.y, b = u / heads_out, ho = u % heads_out, hk = KEY_SIDE ? ho : ho % p.Hk;
+  const int b = u / heads_out, ho = u % heads_out, hk = KEY_SIDE ? ho : ho % p.Hk;
   const int groups = KEY_SIDE ? p.H / p.Hk : 1;
-  const int blk0 = blockIdx.x * 128;                     // first resident row (query row or key row)
+  const int blk0 = blk * 128;                            // first resident row (query row or key row)
   const int inner = KEY_SIDE ? p.Nq : p.Nk;              // swept length per head
   const int steps_per_head = (inner + 63) / 64;
   const int S = steps_per_head * groups;
@@ -93,6 +98,7 @@ __global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p,
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[WB_CONV + i], 8), mbar_init(&bars[WB_IFULL + i], 1), mbar_init(&bars[WB_DONE + i], 1);
     }
+    mbar_init(&bars[WB_HEAD], 1);
     mbar_init_fence();
   }
   fence_before_sync();
@@ -103,41 +109,64 @@ __global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p,
 
   if (warp == SBW_LOAD_WARP) {
     // =============================== copies =====================================================
-    for (int s = 0; s < S && !failed; ++s) {
-      const int buf = s & 1, g = s / steps_per_head, m0 = (s - g * steps_per_head) * 64;   // swept rows m0 .. m0 + 63
-      const int hq = KEY_SIDE ? g * p.Hk + hk : ho;                                         // query head of this G tile
-      if (lane == 0) {
-        const int gst = s % SBW_GST;
-        if (s >= SBW_GST) failed = !mbar_wait(&bars[WB_GFREE + gst], ((s - SBW_GST) / SBW_GST) & 1, WAIT_LIMIT);
-        if (!failed) {
-          mbar_expect_tx(&bars[WB_GFULL + gst], SBW_STG);
-          const int col0 = KEY_SIDE ? blk0 : m0, row0 = KEY_SIDE ? m0 : blk0;
-#pragma unroll
-          for (int bx = 0; bx < GBOX; ++bx)
-            tma_load_4d(Gstg + gst * SBW_STG + bx * (GROWS * 128), &tmap_g, &bars[WB_GFULL + gst], col0 + bx * 32, row0, hq, b);
-        }
-        // the 64-row tile of the swept operand: rows m0 .. m0 + 63
-        if (s >= 2 && !failed) failed = !mbar_wait(&bars[WB_DONE + buf], ((s - 2) >> 1) & 1, WAIT_LIMIT);
-        if (!failed) {
-          const uint8_t* tile = KEY_SIDE ? p.qimg + ((int64_t)(b * p.H + hq) * p.qtiles + m0 / 64) * (int64_t)img_bytes
-                                         : p.kimg + ((int64_t)(b * p.Hk + hk) * p.ktiles + m0 / 64) * (int64_t)img_bytes;
-          mbar_expect_tx(&bars[WB_IFULL + buf], img_bytes);
-          bulk_load(Img + buf * img_bytes, tile, img_bytes, &bars[WB_IFULL + buf]);
-        }
-      }
-      // a wait gave up: let the copies in flight land before the CTA may leave (the G tile of step s was issued
-      // unless its own wait failed; counting it in costs one more bounded wait at most)
-      if (failed && lane == 0) drain_copies(&bars[WB_GFULL], SBW_GST, s + 1 - SBW_GST, s + 1), drain_copies(&bars[WB_IFULL], 2, s - 2, s);
-      failed = __shfl_sync(0xffffffffu, failed, 0);
-    }
-    if (failed && lane == 0) atomicOr(p.status, 1u);
-  } else if (warp == SBW_MMA_WARP) {
-    // =============================== MMA issue ====================================================
+    // Swept rows m0 .. m0 + 63 of step s.  The sweep starts at the CTA's own diagonal block and the two sides walk in
+    // opposite directions: query block i reads key step (2 i + t) and key block j reads query step (2 j + 1 - t) at time
+    // t, so the two CTAs that share a 128 x 128 block of G read it within the same two steps, and whichever comes
+    // second finds it in L2 (both sides of a head are in flight together: see the launch).
+    auto swept = [&](int s, int& hq) {
+      const int g = s / steps_per_head, t = s - g * steps_per_head;
+      int st = KEY_SIDE ? (2 * blk + 1 - t) % steps_per_head : (2 * blk + t) % steps_per_head;
+      if (st < 0) st += steps_per_head;
+      hq = KEY_SIDE ? g * p.Hk + hk : ho;   // query head of this G tile
+      return st * 64;
+    };
+    // Two lanes stream on their own: the G tiles (three staging buffers, freed as soon as the workers have read them)
+    // and the operand image tiles (two buffers, freed by the MMAs two steps later); one lane doing both would hold
+    // back the next G copy while it waits for an image buffer.
     if (lane == 0) {
+      int s = 0;
+      for (; s < S; ++s) {
+        int hq;
+        const int m0 = swept(s, hq), gst = s % SBW_GST;
+        if (s >= SBW_GST) failed = !mbar_wait(&bars[WB_GFREE + gst], ((s - SBW_GST) / SBW_GST) & 1, WAIT_LIMIT);
+        if (failed) break;
+        mbar_expect_tx(&bars[WB_GFULL + gst], SBW_STG);
+        const int col0 = KEY_SIDE ? blk0 : m0, row0 = KEY_SIDE ? m0 : blk0;
+#pragma unroll
+        for (int bx = 0; bx < GBOX; ++bx)
+          tma_load_4d(Gstg + gst * SBW_STG + bx * (GROWS * 128), tmap_g, &bars[WB_GFULL + gst], col0 + bx * 32, row0, hq, b);
+      }
+      // a wait gave up: let the copies in flight land before the CTA may leave
+      if (failed) drain_copies(&bars[WB_GFULL], SBW_GST, s - SBW_GST, s);
+    } else if (lane == 1) {
+      int s = 0;
+      for (; s < S; ++s) {
+        int hq;
+        const int m0 = swept(s, hq), buf = s & 1;
+        if (s >= 2) failed = !mbar_wait(&bars[WB_DONE + buf], ((s - 2) >> 1) & 1, WAIT_LIMIT);
+        if (failed) break;
+        const uint8_t* tile = KEY_SIDE ? p.qimg + ((int64_t)(b * p.H + hq) * p.qtiles + m0 / 64) * (int64_t)img_bytes
+                                       : p.kimg + ((int64_t)(b * p.Hk + hk) * p.ktiles + m0 / 64) * (int64_t)img_bytes;
+        mbar_expect_tx(&bars[WB_IFULL + buf], img_bytes);
+        bulk_load(Img + buf * img_bytes, tile, img_bytes, &bars[WB_IFULL + buf]);
+      }
+      if (failed) drain_copies(&bars[WB_IFULL], 2, s - 2, s);
+    }
+    failed = __any_sync(0xffffffffu, failed);
+    if (failed && lane == 0) atomicOr(p.status, 1u);
+  } else if (warp == SBW_MMA_WARP || warp == SBW_MMA2_WARP) {
+    // =============================== MMA issue ====================================================
+    // Two issuing threads take the even and the odd steps.  Around the 12 instructions of a step (about 630 clocks of
+    // issue) one thread spends as long again on its waits, fences and commits, and it alone set the pace of the loop;
+    // alternating, each has two steps' time for one step's work.  Every instruction accumulates into the same columns
+    // except the first of step 0, so the odd thread starts once that one has been issued.
+    if (lane == 0) {
+      const int first = warp == SBW_MMA_WARP ? 0 : 1;
+      if (first == 1 && S > 1) failed = !mbar_wait(&bars[WB_HEAD], 0, WAIT_LIMIT);
       // query side: A = G (K-major: 128 query rows x 16 keys per step); key side: A = G^T (MN-major: 128 keys x 16 query rows)
       const uint32_t idesc = instr_desc(FMT_BF16, 128, KD, KEY_SIDE, true);
       const uint32_t g_addr = smem_u32(Gbf), i_addr = smem_u32(Img);
-      for (int s = 0; s < S && !failed; ++s) {
+      for (int s = first; s < S && !failed; s += 2) {
         const int buf = s & 1;
         failed = !mbar_wait(&bars[WB_CONV + buf], (s >> 1) & 1, WAIT_LIMIT);
         if (!failed) failed = !mbar_wait(&bars[WB_IFULL + buf], (s >> 1) & 1, WAIT_LIMIT);
@@ -155,6 +184,7 @@ __global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p,
             const uint32_t astep = KEY_SIDE ? ks * ((2 * 128) >> 4) : ks * ((2 * GCS) >> 4);
             mma_ss_lh(tmem, desc_lo(ad) + astep, desc_hi(ad), desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc,
                       (s > 0 || ch > 0 || ks > 0) ? 1u : 0u);
+            if (s == 0 && ch == 0 && ks == 0) mbar_arrive(&bars[WB_HEAD]);
           }
         }
         mma_commit(&bars[WB_DONE + buf]);
@@ -204,6 +234,7 @@ __global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p,
     // global memory: the accumulator goes through the (now dead) staging buffers first, and the chain rule runs with
     // consecutive threads on consecutive 8-feature groups of a row, so that every global access is contiguous.
     if (S > 0 && !failed) failed = !mbar_wait(&bars[WB_DONE + ((S - 1) & 1)], ((S - 1) >> 1) & 1, WAIT_LIMIT);
+    if (S > 1 && !failed) failed = !mbar_wait(&bars[WB_DONE + ((S - 2) & 1)], ((S - 2) >> 1) & 1, WAIT_LIMIT);   // the other issuing thread's last step
     fence_after_sync();
     const int ASTR = KD * 4 + 16;                       // bytes of a staged fp32 row (padded: conflict-free 16-byte stores)
     uint8_t* accs = Gstg;                               // 128 x ASTR <= 96 KB for KD <= 188; larger KD spill into Gbf (dead too)
@@ -304,6 +335,31 @@ __global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p,
   if (warp == SBW_MMA_WARP) tmem_dealloc(tmem, 256);
 }
 
+// Both sides in ONE launch, 1-D grid.  Blocks are numbered so that the CTAs of one (batch, key head) group are
+// neighbours -- its query-side CTAs (all grouped query heads) and its key-side CTAs, alternating when both sides have
+// the same number of blocks -- because the block scheduler hands out blocks in index order: the two CTAs that read the
+// same block of G then run in the same wave, and with the opposite sweep directions above the second read of every
+// block comes out of L2 instead of HBM.
+template <typename T>
+__global__ void __launch_bounds__(SBW_THREADS, 1) sim_bwd_tc_kernel(TcSimBwdP p, const __grid_constant__ CUtensorMap tmap_q,
+                                                                     const __grid_constant__ CUtensorMap tmap_k) {
+  const int qblocks = (p.Nq + 127) / 128, kblocks = (p.Nk + 127) / 128, groups = p.H / p.Hk;
+  const int nq = groups * qblocks, per = nq + kblocks;
+  const int grp = blockIdx.x / per, w = blockIdx.x - grp * per;   // grp = batch * Hk + key head
+  const int b = grp / p.Hk, hk = grp - b * p.Hk;
+  bool key_side;
+  int blk, head = 0;
+  if (nq == kblocks) {        // one query head per key head, square: q0 k0 q1 k1 ...
+    key_side = (w & 1) != 0, blk = w >> 1;
+  } else if (w < nq) {
+    key_side = false, head = w / qblocks, blk = w - head * qblocks;
+  } else {
+    key_side = true, blk = w - nq;
+  }
+  if (key_side) sim_bwd_side<T, true>(p, &tmap_k, blk, b * p.Hk + hk);
+  else sim_bwd_side<T, false>(p, &tmap_q, blk, b * p.H + head * p.Hk + hk);
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 size_t sim_fwd_tc_image_bytes(const PopeShape& s, size_t* q_bytes);   // tc_sim_fwd.cu: sizes of the Q' / K' tile images
 cudaError_t sim_launch_prepass(const PopeShape& s, const PopeEmbed& e, const void* q, const PopeStride3& sq, const void* k,
@@ -330,23 +386,6 @@ size_t sim_bwd_tc_workspace(const PopeSimBwdArgs& a) { return sim_fwd_tc_image_b
 bool make_load_tmap_f32(CUtensorMap* out, const void* base, int cols, int rows, int heads, int batch, int64_t sn, int64_t sh,
                         int64_t sb, int box_rows);
 
-template <bool KEY_SIDE>
-static cudaError_t launch_sim_bwd_side(const TcSimBwdP& p, const PopeSimBwdArgs& a, cudaStream_t st) {
-  const PopeShape& s = a.shape;
-  CUtensorMap tmap;
-  memset(&tmap, 0, sizeof(tmap));
-  if (!make_load_tmap_f32(&tmap, a.dsim, s.Nk, s.Nq, s.H, s.B, a.sds.n, a.sds.h, a.sds.b, KEY_SIDE ? 64 : 128))
-    return cudaErrorNotSupported;
-  const int KC = (s.d + s.r) / 8;
-  size_t smem = (SBW_GST + 2) * (size_t)SBW_STG + 2 * (size_t)(2 * KC * SBW_CS_HALF) + (WB_COUNT + 1) * 8 + 16 + 1024;
-  if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: the TMEM columns are allocated per CTA
-  cudaError_t e = ensure_max_smem<sim_bwd_tc_kernel<float, KEY_SIDE>>();
-  if (e != cudaSuccess) return e;
-  const int rows = KEY_SIDE ? s.Nk : s.Nq, heads = KEY_SIDE ? s.Hk : s.H;
-  sim_bwd_tc_kernel<float, KEY_SIDE><<<dim3((rows + 127) / 128, s.B * heads), SBW_THREADS, smem, st>>>(p, tmap);
-  return cudaGetLastError();
-}
-
 cudaError_t sim_bwd_tc(const PopeSimBwdArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
   size_t q_bytes = 0;
@@ -366,8 +405,19 @@ cudaError_t sim_bwd_tc(const PopeSimBwdArgs& a, cudaStream_t st) {
   p.qimg = qimg, p.kimg = kimg;
   p.status = tc_status_ptr();
   if (!p.status) return cudaErrorInvalidSymbol;
-  if ((e = launch_sim_bwd_side<false>(p, a, st)) != cudaSuccess) return e;
-  return launch_sim_bwd_side<true>(p, a, st);
+  CUtensorMap tmap_q, tmap_k;   // the same tensor, boxes of 128 rows (query side) and of 64 rows (key side)
+  memset(&tmap_q, 0, sizeof(tmap_q)), memset(&tmap_k, 0, sizeof(tmap_k));
+  if (!make_load_tmap_f32(&tmap_q, a.dsim, s.Nk, s.Nq, s.H, s.B, a.sds.n, a.sds.h, a.sds.b, 128) ||
+      !make_load_tmap_f32(&tmap_k, a.dsim, s.Nk, s.Nq, s.H, s.B, a.sds.n, a.sds.h, a.sds.b, 64))
+    return cudaErrorNotSupported;
+  const int KC = (s.d + s.r) / 8;
+  size_t smem = (SBW_GST + 2) * (size_t)SBW_STG + 2 * (size_t)(2 * KC * SBW_CS_HALF) + (WB_COUNT + 1) * 8 + 16 + 1024;
+  if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: the TMEM columns are allocated per CTA
+  if ((e = ensure_max_smem<sim_bwd_tc_kernel<float>>()) != cudaSuccess) return e;
+  const int groups = s.H / s.Hk;
+  const unsigned grid = (unsigned)(s.B * s.Hk) * (unsigned)(groups * ((s.Nq + 127) / 128) + (s.Nk + 127) / 128);
+  sim_bwd_tc_kernel<float><<<grid, SBW_THREADS, smem, st>>>(p, tmap_q, tmap_k);
+  return cudaGetLastError();
 }
 
 }  // namespace pope
