@@ -87,6 +87,13 @@ bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, in
                  batch, sn, sh, sb, 8, box_rows, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
+// 16-bit rows cut into boxes of 64 features (128 bytes) x box_rows rows, 128-byte swizzled
+static bool make_wide_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
+                           int64_t sh, int64_t sb, int box_rows) {
+  return tmap_4d(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, d, rows, heads,
+                 batch, sn, sh, sb, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 bool make_load_tmap_f32(CUtensorMap* out, const void* base, int cols, int rows, int heads, int batch, int64_t sn, int64_t sh,
                         int64_t sb, int box_rows) {
   return tmap_4d(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, cols, rows, heads, batch, sn, sh, sb, 32, box_rows,
@@ -432,6 +439,12 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
   if (warp == FWD_MMA_WARP) tmem_dealloc(tmem, 512);
 }
 
+}  // namespace pope
+
+#include "tc_attn_fwd2.inl"
+
+namespace pope {
+
 // ---- host side ---------------------------------------------------------------------------------
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static bool stride_ok(const PopeStride3& s) { return s.b % 8 == 0 && s.h % 8 == 0 && s.n % 8 == 0; }
@@ -484,7 +497,13 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   ExpandJobs jobs;
   jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg, s.Nk, by_batch, tab_heads);
   jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg, s.Nk, by_batch, tab_heads);
+#ifndef POPE_FWD_V1
+  jobs.job[0].tile128 = 1;   // the kernel streams K' 128 keys at a time
+#endif
   if ((e = launch_expand_images(jobs, 2, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+#ifndef POPE_FWD_V1
+  return launch_fwd2_kernel<D, T>(a, p, st);
+#endif
   CUtensorMap tmap_v;
   if (!make_chunk_tmap(&tmap_v, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, TK)) return cudaErrorNotSupported;
   size_t smem = (size_t)2 * TQ * KD * 2 + 2 * (size_t)TK * KD * 2 + 2 * (size_t)TK * D * 2 + (B_COUNT + 1) * 8 + 16;

@@ -95,6 +95,7 @@ struct ExpandJob {
   const float* bias;
   int64_t bias_sh;
   void* img;
+  int tile128;   // 1: pairs of 64-row tiles are interleaved into 128-row tiles [chunk][128 rows][16 B] (one bulk copy per 128-key stage)
 };
 struct ExpandJobs { ExpandJob job[4]; };
 inline ExpandJob expand_job(const void* x, const PopeStride3& sx, int batch, int heads, int rows, int r, int pos0,
@@ -103,7 +104,7 @@ inline ExpandJob expand_job(const void* x, const PopeStride3& sx, int batch, int
   ExpandJob j;
   j.x = x, j.sx = sx, j.units = batch * heads, j.heads = heads, j.rows = rows, j.r = r, j.pos0 = pos0;
   j.tab_rows = tab_rows, j.tab_by_batch = tab_by_batch, j.tab_heads = tab_heads;
-  j.bias = r > 0 ? bias : nullptr, j.bias_sh = bias_sh, j.img = img;
+  j.bias = r > 0 ? bias : nullptr, j.bias_sh = bias_sh, j.img = img, j.tile128 = 0;
   return j;
 }
 // ch / sh = fp16 cos / sin of the phase table, [positions][r].  All jobs share d and the dtype; one launch.

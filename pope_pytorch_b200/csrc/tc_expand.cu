@@ -119,10 +119,19 @@ __global__ void __launch_bounds__(256, 3) expand_image_kernel(ExpandJobs jobs, c
     }
     __syncthreads();
     // phase 2: the image leaves in its own byte order, 16 bytes per thread, fully coalesced
-    uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(jb.img) + ((int64_t)u * tiles + tile) * ((int64_t)IMAGE_ROWS * KC * 16));
-    for (int g = tid; g < IMAGE_ROWS * KC; g += 256) {
-      const int cc = g / IMAGE_ROWS, row = g - cc * IMAGE_ROWS;
-      out[g] = *reinterpret_cast<const uint4*>(stage + cc * CS64 + row * 16);
+    if (jb.tile128) {   // tile 2 t and 2 t + 1 share one 128-row tile: chunk stride 2 KB, this tile's rows in one half of it
+      uint8_t* out = static_cast<uint8_t*>(jb.img) + (((int64_t)u * tiles + tile) >> 1) * ((int64_t)2 * IMAGE_ROWS * KC * 16) +
+                     (tile & 1) * (IMAGE_ROWS * 16);
+      for (int g = tid; g < IMAGE_ROWS * KC; g += 256) {
+        const int cc = g / IMAGE_ROWS, row = g - cc * IMAGE_ROWS;
+        *reinterpret_cast<uint4*>(out + cc * (2 * IMAGE_ROWS * 16) + row * 16) = *reinterpret_cast<const uint4*>(stage + cc * CS64 + row * 16);
+      }
+    } else {
+      uint4* out = reinterpret_cast<uint4*>(static_cast<uint8_t*>(jb.img) + ((int64_t)u * tiles + tile) * ((int64_t)IMAGE_ROWS * KC * 16));
+      for (int g = tid; g < IMAGE_ROWS * KC; g += 256) {
+        const int cc = g / IMAGE_ROWS, row = g - cc * IMAGE_ROWS;
+        out[g] = *reinterpret_cast<const uint4*>(stage + cc * CS64 + row * 16);
+      }
     }
     if (tt + 1 < EXPAND_TPC) __syncthreads();   // the stage is rewritten by the next tile
   }
