@@ -257,8 +257,8 @@ POPE_API int pope_b200_apply_qk_bwd(const PopeApplyBwdArgs* args, void* stream);
  * (No counterpart in the reference: its wrappers always allocate through torch.)
  *
  * Same arguments and results as pope_b200_attn_fwd, but `workspace` / `workspace_bytes` are
- * ignored: the kernel's scratch (the position phase table and the expanded operand tiles of q
- * and k) lives in a fixed array inside the library instead.  Meant for hosts that may not touch a device allocator where they call us --
+ * ignored: the kernel's scratch (the position phase table and the expanded operand tiles of k)
+ * lives in a fixed array inside the library instead.  Meant for hosts that may not touch a device allocator where they call us --
  * an inference loop whose memory plan is frozen, a plugin that is only ever handed input and
  * output buffers, a latency-critical thread that must not take the allocator's lock.  The call
  * itself performs no device allocation or free of any kind.
@@ -268,7 +268,7 @@ POPE_API int pope_b200_apply_qk_bwd(const PopeApplyBwdArgs* args, void* stream);
  *     16-byte aligned rows); anything else returns POPE_ERR_UNSUPPORTED.
  *   - The scratch a call needs is what pope_b200_workspace_bytes reports for the forward
  *     (4 Nk r bytes of table -- fp16 cos and sin -- rounded up to 256, plus
- *     2 (d + r) bytes per query and key row of every head, rows padded to a multiple of 256);
+ *     2 (d + r) bytes per key row of every key head, rows padded to a multiple of 256);
  *     more than POPE_B200_NOALLOC_MAX_SCRATCH returns POPE_ERR_TOO_LARGE and launches nothing.  Every GPU that loads the library holds that many
  *     bytes until the process exits.
  *   - The first call on each device looks up the array's device address (a one-time runtime

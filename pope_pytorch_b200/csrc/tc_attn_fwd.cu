@@ -1,18 +1,23 @@
 // PoPE flash-attention forward on the Blackwell tensor cores (tcgen05 + TMEM), sm_100a only.
 //
-// One CTA owns 256 query rows (two 128-row MMA tiles) of one (batch, head) unit and sweeps the keys 64 at a
-// time.  The expanded operands Q' and K' = [a cos | pass | a sin] come from the operand images that a pre-pass
-// builds once per call (tc_expand.cu), so the main loop contains no transform work:
-//   loader warp   : Q' (resident, 2 x 2 image tiles) and one K' image tile per step by cp.async.bulk; the V tile
-//                   of the step by cp.async.bulk.tensor boxes straight from the caller's strided V
-//   score warp    : one lane issues tcgen05.mma  S_t = Q'_t K'^T  into TMEM (t = 0, 1)
-//   softmax warps : every thread owns one query row: it pulls its 64 scores out of TMEM, applies the causal /
-//                   key-padding masks, keeps the running max and sum, and writes P (16-bit) back into TMEM over
-//                   the scores
-//   PV warp       : one lane issues  O_t += P_t V  with P read straight from TMEM
+// One CTA owns 128 query rows of one (batch, head) unit and sweeps the keys 128 at a time.
+//   Q' = [a cos | pass | a sin] of its rows is expanded by the CTA itself, from q and the fp16 phase tables, straight
+//        into TENSOR memory ((d + r) / 2 columns): it is the TMEM-side A operand of every score product and never
+//        exists in global or shared memory
+//   K' comes from the operand images that a pre-pass builds once per call (tc_expand.cu, 128-row tiles, the per-head
+//        phase bias of the keys folded in): every CTA of a unit re-reads it, so it is expanded once, not per CTA
+//   loader warps  : one K' image tile per step by one cp.async.bulk; the V tile of the step by cp.async.bulk.tensor
+//                   boxes (128-byte swizzled rows) straight from the caller's strided V
+//   score warp    : one lane issues  S = Q' K'^T  (128x128x16 products, A from tensor memory) into one of two buffers
+//   softmax warps : two threads per query row: each pulls its 64 scores out of TMEM, applies the causal / key-padding
+//                   masks, keeps the running max (row maxima exchanged through shared memory) and sum, and writes P
+//                   (16-bit) back into TMEM over the scores
+//   PV warp       : one lane issues  O += P V  with P read straight from TMEM
 // All hand-offs are mbarriers (copy completion by transaction bytes, MMA completion by tcgen05.commit).
-//
-// The per-head phase bias of the keys is part of the K' images.
+// Tensor memory: Q' [0, 128), S / P double-buffered [128, 384), O [384, 512); shared memory holds nothing but two
+// stages of (K' tile, V tile).  An earlier version kept two 128-row Q' tiles in SHARED memory and swept 64 keys per
+// step: its 128x64x16 score products read 6 KB of operands for 32 clocks of tensor time, and shared-memory bandwidth
+// set its pace (0.535 ms against 0.49 ms at B=4, H=16, N=4096, d=r=128).
 //
 // Semantics follow PoPE_pytorch/triton_pope_flash_attn.py:23-117 (top-left causal mask,
 // bottom-right positions, mask True = keep, zero output and -inf LSE for empty rows).
@@ -119,79 +124,77 @@ struct TcFwdP {
   int64_t sfn;
   const float* bias;
   int64_t bias_sh;
-  const uint8_t* qimg; // expanded Q' image tiles, (B * H) units
   const uint8_t* kimg; // expanded K' image tiles (phase bias folded in), (B * Hk) units
+  const __half *ch, *sh;         // fp16 cos / sin phase tables, [slice][Nk][r]
+  int64_t tab_slice_stride;      // elements per table slice (Nk * r)
+  int tab_by_batch, tab_heads;   // slice of a unit: (tab_by_batch ? batch : 0) * tab_heads + head % tab_heads
   const uint8_t* mask;
   int64_t msb, msn;
 };
 
 constexpr int TQ = 128;   // rows per MMA tile
-constexpr int TK = 64;    // keys per step (= IMAGE_ROWS)
-static_assert(TK == IMAGE_ROWS, "a streamed K' tile is one image tile");
 
-// Warp roles of the forward kernel (12 warps, 384 threads).  Three issuing warps: a single thread spends ~55 clocks
-// per 128x64x16 MMA instruction against 32 clocks of tensor time, so the score products of the two row tiles are
-// issued by two threads in parallel (16 instructions each per key tile) and O += P V of tile j by a third.
-constexpr int FWD_SOFTMAX_WARPS = 8;               // warps 0-7 : one query row per thread (two 128-row tiles)
-constexpr int FWD_LOAD_WARP = FWD_SOFTMAX_WARPS;   // warp 8    : one lane issues every bulk / tensor copy
-constexpr int FWD_MMA_WARP = FWD_LOAD_WARP + 1;    // warp 9    : one lane issues S_0 = Q'_0 K'^T; owns the TMEM allocation
-constexpr int FWD_PV_WARP = FWD_MMA_WARP + 1;      // warp 10   : one lane issues O += P V
-constexpr int FWD_MMA1_WARP = FWD_PV_WARP + 1;     // warp 11   : one lane issues S_1 = Q'_1 K'^T
-constexpr int FWD_THREADS = 32 * (FWD_MMA1_WARP + 1);
+constexpr int FW_TK = 128;                         // keys per step
+constexpr int FW_NPR = 2;                          // softmax threads per query row (2 or 4; 4 measured the same), 128 / FW_NPR scores each
+constexpr int FW_SM_WARPS = 4 * FW_NPR;            // softmax warps
+constexpr int FW_KLOAD_WARP = FW_SM_WARPS;         // one lane issues the K' copies (one 128-row image tile per step)
+constexpr int FW_S_WARP = FW_SM_WARPS + 1;         // one lane issues S = Q' K'^T; owns the TMEM allocation
+constexpr int FW_PV_WARP = FW_SM_WARPS + 2;        // one lane issues O += P V
+constexpr int FW_VLOAD_WARP = FW_SM_WARPS + 3;     // one lane issues the V boxes
+constexpr int FW_THREADS = 32 * (FW_VLOAD_WARP + 1);
+constexpr uint32_t FW_TS = 128, FW_TO = 384;       // first TMEM column of the S / P buffers and of O (Q' starts at 0)
 
-// mbarrier slots
+constexpr int FW_VST = 2;                          // V stages (up to 3; a third one changed nothing measurable)
 enum {
-  B_KFULL = 0,   // [2] K' image tile landed (transaction bytes)
-  B_VFULL = 2,   // [2] V tile landed (transaction bytes)
-  B_KFREE = 4,   // [2] both score products of a key tile have completed (one commit per issuing thread): its K' buffer
-                 //     may be refilled
-  B_PVDONE = 6,  // [2] O += P V of both row tiles done (tcgen05.commit)
-  B_PFULL = 8,   // [buf][row tile] probabilities written to TMEM (4 softmax warps)
-  B_QFULL = 12,  // the resident Q' tiles are in shared memory
-  B_SFULL = 13,  // [buf][row tile] scores of one row tile written to TMEM (tcgen05.commit)
-  B_ODONE = 17,  // [row tile] the last O += P V of that row tile has completed: one phase per barrier, so the epilogue's
-                 //     wait cannot alias with a later completion (B_PVDONE of a buffer completes again two steps later
-                 //     for the other row tile when the causal mask ends tile 0 early)
-  B_COUNT = 19
+  FW_KFULL = 0,    // [2] K' tile landed (transaction bytes)
+  FW_KFREE = 2,    // [2] tcgen05.commit: S(j) has completed, its K' buffer may be refilled
+  FW_PVDONE = 4,   // [2] tcgen05.commit: O += P V of tile j has completed: S / P buffer j & 1 is free
+  FW_SFULL = 6,    // [2] tcgen05.commit: the scores of tile j are in TMEM
+  FW_PFULL = 8,    // [2] the softmax warps: the probabilities of tile j are in TMEM
+  FW_QFULL = 10,   // the softmax warps: Q' is in TMEM
+  FW_ODONE = 11,   // tcgen05.commit: the last O += P V has completed
+  FW_VFULL = 12,   // [3] V tile landed in stage j % FW_VST (transaction bytes)
+  FW_VFREE = 15,   // [3] tcgen05.commit: O += P V of tile j has completed: V stage j % FW_VST is free
+  FW_COUNT = 18
 };
 
 template <int D, typename T>
-__global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, const __grid_constant__ CUtensorMap tmap_v) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int KD = D + p.r, KSTEPS = KD >> 4;
-  constexpr int CS = TK * 16;                       // bytes of one 16-byte chunk column of a streamed tile
-  const int KBUF = (KD / 8) * CS;                   // one K' tile = one image tile
-  constexpr int VBUF = (D / 8) * CS;
-  uint8_t* Qs = smem;                               // 2 tiles x [KD/8 chunks][128 rows][16 B]
-  uint8_t* Ks = Qs + 2 * TQ * KD * 2;               // 2 bufs  x [KD/8 chunks][64 keys][16 B]
-  uint8_t* Vs = Ks + 2 * KBUF;                      // 2 bufs  x [D/8 chunks][64 keys][16 B]; 128-byte aligned (KD % 16 == 0)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + 2 * VBUF);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT + 1);
+__global__ void __launch_bounds__(FW_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, const __grid_constant__ CUtensorMap tmap_v) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles sit on 1 KB boundaries
+  // V tiles: D a multiple of 64 -> boxes of 64 features (128-byte rows, 128-byte swizzled); else 16-byte chunk columns
+  constexpr bool VWIDE = D % 64 == 0;
+  const int KD = D + p.r, KC = KD >> 3, KSTEPS = KD >> 4;
+  const int KBUF = FW_TK * KD * 2;                  // one K' stage: [KD/8 chunks][128 keys][16 B]
+  constexpr int VBUF = FW_TK * D * 2;               // one V stage:  [D/8 chunks][128 keys][16 B]
+  constexpr int CSV = FW_TK * 16;                   // chunk stride of both
+  uint8_t* Ks = smem;
+  uint8_t* Vs = Ks + 2 * KBUF;
+  float* xch = reinterpret_cast<float*>(Vs + FW_VST * VBUF);       // [2 step parities][FW_NPR parts][128 rows] row maxima
+  float* lxch = xch;                                                 // [FW_NPR parts][128 rows] row sums (epilogue: xch is dead)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xch + 2 * FW_NPR * TQ);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + FW_COUNT + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
-  const int i0 = (gridDim.x - 1 - blockIdx.x) * (2 * TQ);  // heavy (late) row blocks first
-
+  const int i0 = (gridDim.x - 1 - blockIdx.x) * TQ;  // heavy (late) row blocks first
   int n_end = p.Nk;
-  if (p.causal) n_end = min(n_end, min(i0 + 2 * TQ, p.Nq));
-  const int T_tiles = (n_end + TK - 1) / TK;
-  const bool has_rows1 = i0 + TQ < p.Nq;
-  // number of key tiles tile t takes part in (under the causal mask tile 0 stops 128 keys earlier)
-  const int T0 = p.causal ? min(T_tiles, (min(n_end, i0 + TQ) + TK - 1) / TK) : T_tiles;
-  const int T1 = has_rows1 ? T_tiles : 0;
+  if (p.causal) n_end = min(n_end, min(i0 + TQ, p.Nq));
+  const int T_tiles = (n_end + FW_TK - 1) / FW_TK;
 
-  if (warp == FWD_MMA_WARP) {
+  if (warp == FW_S_WARP) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars[B_KFULL + i], 1), mbar_init(&bars[B_VFULL + i], 1);
-      mbar_init(&bars[B_KFREE + i], 2), mbar_init(&bars[B_PVDONE + i], 1);
+      mbar_init(&bars[FW_KFULL + i], 1);
+      mbar_init(&bars[FW_KFREE + i], 1), mbar_init(&bars[FW_PVDONE + i], 1);
+      mbar_init(&bars[FW_SFULL + i], 1), mbar_init(&bars[FW_PFULL + i], FW_SM_WARPS);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[B_PFULL + i], 4), mbar_init(&bars[B_SFULL + i], 1);
-    mbar_init(&bars[B_QFULL], 1);
-    mbar_init(&bars[B_ODONE], 1), mbar_init(&bars[B_ODONE + 1], 1);
+    for (int i = 0; i < FW_VST; ++i) mbar_init(&bars[FW_VFULL + i], 1), mbar_init(&bars[FW_VFREE + i], 1);
+    mbar_init(&bars[FW_QFULL], FW_SM_WARPS);
+    mbar_init(&bars[FW_ODONE], 1);
     mbar_init_fence();
   }
   fence_before_sync();
@@ -200,152 +203,196 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
   const uint32_t tmem = *tmem_slot;
   bool failed = false;
 
-  if (warp == FWD_LOAD_WARP) {
-    // =============================== copies ==================================================
-    // K'(j) is one contiguous image tile; V(j) arrives as D/8 boxes of 64 keys x 16 bytes, each landing on its
-    // chunk column.  A buffer is refilled as soon as the MMA that read it has completed.
-    // the two resident Q' tiles: four image tiles, one 1 KB copy per chunk column and 64 rows
-    {
-      const uint8_t* qimg = p.qimg + ((int64_t)u * (int64_t)image_tiles(p.Nq) + i0 / IMAGE_ROWS) * KBUF;
-      if (lane == 0) mbar_expect_tx(&bars[B_QFULL], 2 * TQ * KD * 2);
-      __syncwarp();
-      copy_resident_tiles(Qs, qimg, KD / 8, &bars[B_QFULL], lane);
-      copy_resident_tiles(Qs + TQ * KD * 2, qimg + 2 * KBUF, KD / 8, &bars[B_QFULL], lane);
-    }
-    // K' tiles and V tiles are streamed by two lanes on their own: a K' buffer is free as soon as the score products
-    // that read it have completed, a V buffer only after O += P V two steps later, and one lane waiting for the latter
-    // would hold back the K' copy that the next score product is waiting for.
+  if (warp == FW_KLOAD_WARP) {
+    // =============================== copies: K' ==================================================
+    // a 128-key stage is one 128-row image tile (the pre-pass interleaves pairs of its 64-row tiles): one bulk copy.
+    // (Assembled from 2 x KD / 8 copies of 1 KB the stage took longer to arrive than the whole step should last.)
     if (lane == 0) {
-      const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)image_tiles(p.Nk) * KBUF;
+      const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)(image_tiles(p.Nk) / 2) * KBUF;
       int j = 0;
       for (; j < T_tiles; ++j) {
         const int buf = j & 1;
-        if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_KFREE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        if (j >= 2 && !failed) failed = !mbar_wait(&bars[FW_KFREE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
         if (failed) break;
-        mbar_expect_tx(&bars[B_KFULL + buf], KBUF);
-        bulk_load(Ks + buf * KBUF, kimg + (int64_t)j * KBUF, KBUF, &bars[B_KFULL + buf]);
+        mbar_expect_tx(&bars[FW_KFULL + buf], KBUF);
+        bulk_load(Ks + buf * KBUF, kimg + (int64_t)j * KBUF, KBUF, &bars[FW_KFULL + buf]);
       }
-      if (failed) drain_copies(&bars[B_KFULL], 2, j - 2, j), drain_copies(&bars[B_QFULL], 1, 0, 1);
-    } else if (lane == 1) {
+      if (failed) drain_copies(&bars[FW_KFULL], 2, j - 2, j);
+    }
+    __syncwarp();
+  } else if (warp == FW_VLOAD_WARP) {
+    // =============================== copies: V ===================================================
+    if (lane == 0) {
       int j = 0;
       for (; j < T_tiles; ++j) {
-        const int buf = j & 1, n0 = j * TK;
-        if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
-        if (failed) { drain_copies(&bars[B_VFULL], 2, j - 2, j); break; }
-        mbar_expect_tx(&bars[B_VFULL + buf], VBUF);
+        const int buf = j % FW_VST, n0 = j * FW_TK;
+        if (j >= FW_VST && !failed) failed = !mbar_wait(&bars[FW_VFREE + buf], ((j - FW_VST) / FW_VST) & 1, WAIT_LIMIT);
+        if (failed) { drain_copies(&bars[FW_VFULL], FW_VST, j - FW_VST, j); break; }
+        mbar_expect_tx(&bars[FW_VFULL + buf], VBUF);
+        if (VWIDE) {
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) tma_load_4d(Vs + buf * VBUF + c * CS, &tmap_v, &bars[B_VFULL + buf], c * 8, n0, hk, b);
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(Vs + buf * VBUF + c * (FW_TK * 128), &tmap_v, &bars[FW_VFULL + buf], c * 64, n0, hk, b);
+        } else {
+#pragma unroll
+          for (int c = 0; c < D / 8; ++c) tma_load_4d(Vs + buf * VBUF + c * CSV, &tmap_v, &bars[FW_VFULL + buf], c * 8, n0, hk, b);
+        }
       }
     }
     __syncwarp();
-  } else if (warp == FWD_MMA_WARP || warp == FWD_MMA1_WARP) {
-    // =============================== MMA issue: S_t = Q'_t K'^T, one thread per row tile ==========
+  } else if (warp == FW_S_WARP) {
+    // =============================== MMA issue: S = Q' K'^T ======================================
     if (lane == 0) {
-      const int t = warp == FWD_MMA_WARP ? 0 : 1;
-      const int T_t = t == 0 ? T0 : T1;
-      const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, TQ, TK, false, false);
-      const uint32_t qs_addr = smem_u32(Qs), ks_addr = smem_u32(Ks);
-      const uint64_t ad = smem_desc(qs_addr + t * (TQ * KD * 2), TQ * 16, 128);
-      if (!mbar_wait(&bars[B_QFULL], 0, WAIT_LIMIT)) failed = true;
+      const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, TQ, FW_TK, false, false);
+      const uint32_t ks_addr = smem_u32(Ks);
+      if (!mbar_wait(&bars[FW_QFULL], 0, WAIT_LIMIT)) failed = true;
       for (int j = 0; j < T_tiles && !failed; ++j) {
         const int buf = j & 1;
-        // (also paces a thread whose row tile is finished: it arrives on KFREE of tile j only after the tile has landed,
-        // i.e. after the phase of tile j - 2 has completed)
-        failed = !mbar_wait(&bars[B_KFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
-        if (j < T_t) {
-          // score buffer j & 1 still holds P(j-2) until PV(j-2) has read it
-          if (j >= 2 && !failed) failed = !mbar_wait(&bars[B_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
-          fence_after_sync();
-          const uint32_t d = tmem + (buf * 2 + t) * 64;
-          const uint64_t bd = smem_desc(ks_addr + buf * KBUF, CS, 128);
-          uint32_t alo = desc_lo(ad), blo = desc_lo(bd);
-          mma_ss_lh(d, alo, desc_hi(ad), blo, desc_hi(bd), idesc_s, 0u);
+        failed = !mbar_wait(&bars[FW_KFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
+        // score buffer j & 1 still holds P(j-2) until PV(j-2) has read it
+        if (j >= 2 && !failed) failed = !mbar_wait(&bars[FW_PVDONE + buf], ((j - 2) >> 1) & 1, WAIT_LIMIT);
+        if (failed) break;
+        fence_after_sync();
+        const uint32_t d = tmem + FW_TS + buf * FW_TK;
+        const uint64_t bd = smem_desc(ks_addr + buf * KBUF, CSV, 128);
+        uint32_t blo = desc_lo(bd), at = tmem;
 #pragma unroll 4
-          for (int ks = 1; ks < KSTEPS; ++ks) {
-            alo += (2 * TQ * 16) >> 4, blo += (2 * CS) >> 4;
-            mma_ss_lh(d, alo, desc_hi(ad), blo, desc_hi(bd), idesc_s, 1u);
-          }
-          mma_commit(&bars[B_SFULL + buf * 2 + t]);   // this row tile's softmax may start
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+          mma_ts_lh(d, at, blo, desc_hi(bd), idesc_s, ks > 0 ? 1u : 0u);
+          at += 8, blo += (2 * CSV) >> 4;
         }
-        // one arrival per issuing thread and key tile, also for tiles this row tile does not take part in (the commit
-        // then completes at once): the K' buffer is free when both have arrived
-        mma_commit(&bars[B_KFREE + buf]);
+        mma_commit(&bars[FW_SFULL + buf]);
+        mma_commit(&bars[FW_KFREE + buf]);
       }
     }
     __syncwarp();
-  } else if (warp == FWD_PV_WARP) {
-    // =============================== MMA issue: O += P V =======================================
+  } else if (warp == FW_PV_WARP) {
+    // =============================== MMA issue: O += P V =========================================
     if (lane == 0) {
       const uint32_t idesc_o = instr_desc(TcFmt<T>::fmt, TQ, D, false, true);
       const uint32_t vs_addr = smem_u32(Vs);
       for (int j = 0; j < T_tiles && !failed; ++j) {
         const int buf = j & 1;
-        failed = !mbar_wait(&bars[B_VFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
-        for (int t = 0; t < 2; ++t) {
-          if (j >= (t == 0 ? T0 : T1)) continue;
-          if (!failed) failed = !mbar_wait(&bars[B_PFULL + buf * 2 + t], (j >> 1) & 1, WAIT_LIMIT);
-          fence_after_sync();
-          const uint32_t d = tmem + 256 + t * 128;
-          const uint32_t a = tmem + (buf * 2 + t) * 64;
-          const uint64_t bd = smem_desc(vs_addr + buf * VBUF, 128, CS);
+        failed = !mbar_wait(&bars[FW_VFULL + j % FW_VST], (j / FW_VST) & 1, WAIT_LIMIT);
+        if (!failed) failed = !mbar_wait(&bars[FW_PFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
+        if (failed) break;
+        fence_after_sync();
+        const uint32_t a = tmem + FW_TS + buf * FW_TK;
+        // B = V, MN-major: wide boxes: 64-feature blocks 16 KB apart, 8-key groups 1 KB apart, 2 KB per 16 keys;
+        // chunk columns: 8-feature chunks CSV apart, 8-key groups 128 bytes apart, 256 bytes per 16 keys
+        const uint32_t vaddr = vs_addr + (j % FW_VST) * VBUF;
+        const uint64_t bd = VWIDE ? smem_desc_sw128(vaddr, FW_TK * 128, 1024) : smem_desc(vaddr, 128, CSV);
+        constexpr uint32_t kstep = VWIDE ? (2048 >> 4) : ((2 * 128) >> 4);
+        constexpr int CPT = FW_TK / FW_NPR;   // P of keys [CPT t, CPT t + CPT) sits in the first CPT / 2 columns of part t
 #pragma unroll
-          for (int ks = 0; ks < TK / 16; ++ks)
-            mma_ts_lh(d, a + ks * 8, desc_lo(bd) + ks * ((2 * 128) >> 4), desc_hi(bd), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-          if (j == (t == 0 ? T0 : T1) - 1) mma_commit(&bars[B_ODONE + t]);
-        }
-        mma_commit(&bars[B_PVDONE + buf]);
+        for (int ks = 0; ks < FW_TK / 16; ++ks)
+          mma_ts_lh(tmem + FW_TO, a + (ks * 16 / CPT) * CPT + (ks * 16 % CPT) / 2, desc_lo(bd) + ks * kstep, desc_hi(bd), idesc_o,
+                    (j > 0 || ks > 0) ? 1u : 0u);
+        if (j == T_tiles - 1) mma_commit(&bars[FW_ODONE]);
+        mma_commit(&bars[FW_PVDONE + buf]);
+        mma_commit(&bars[FW_VFREE + j % FW_VST]);
       }
     }
     __syncwarp();
   } else {
-    // =============================== softmax ==================================================
+    // =============================== softmax: FW_NPR threads per query row =======================
     const uint8_t* maskb = p.mask ? p.mask + b * p.msb : nullptr;
-
-    const int tile = warp >> 2;
-    const int row = i0 + tid;
-    const int T_mine = tile == 0 ? T0 : T1;
+    constexpr int CPT = FW_TK / FW_NPR;              // score columns per thread (64 or 32)
+    constexpr int OC = FW_NPR == 4 ? 32 : D / 2;     // output columns per thread ...
+    const int rloc = tid & 127, part = tid >> 7;
+    const bool o_active = part * OC < D;             // ... of the threads that own any
+    const int row = i0 + rloc;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const int row_bar = 1 + (warp & 3);   // named barrier of the FW_NPR warps that share 32 rows
+    auto row_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(row_bar), "n"(32 * FW_NPR) : "memory"); };
+    {
+      // Q' = [a cos f | pass | a sin f] of this CTA's rows, expanded HERE from q and the fp16 phase tables and written
+      // straight into tensor memory (lane = row, 4 columns per 8-feature chunk): the resident operand never exists in
+      // global memory.  The threads of a row share its 16-byte groups; rows past Nq are zero.
+      constexpr int DC = D >> 3;
+      const int RC = p.r >> 3;
+      const bool live = row < p.Nq;
+      const T* qrow = static_cast<const T*>(p.q) + b * p.sq.b + h * p.sq.h + (int64_t)row * p.sq.n;
+      const int64_t trow = p.tab_slice_stride * ((p.tab_by_batch ? b : 0) * p.tab_heads + h % p.tab_heads) +
+                           (int64_t)(p.Nk - p.Nq + row) * p.r;   // bottom-right positions
+      // (a compact loop on purpose: unrolled into groups of chunks with their loads up front, this prologue came out
+      // 14-30 us slower per forward -- its code displaces the main loop's in the instruction cache)
+      for (int c = part; c < DC; c += FW_NPR) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (live) raw = __ldg(reinterpret_cast<const uint4*>(qrow + c * 8));
+        if (c < RC) {
+          uint4 cq = make_uint4(0, 0, 0, 0), sq = cq;
+          if (live) {
+            cq = __ldg(reinterpret_cast<const uint4*>(p.ch + trow + c * 8));
+            sq = __ldg(reinterpret_cast<const uint4*>(p.sh + trow + c * 8));
+          }
+          const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w}, cw[4] = {cq.x, cq.y, cq.z, cq.w}, sw[4] = {sq.x, sq.y, sq.z, sq.w};
+          uint32_t o1[4], o2[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 xv = unpack2<T>(rw[e]), cv = unpack2<__half>(cw[e]), sv2 = unpack2<__half>(sw[e]);
+            const float a0 = live ? softplus_fast(xv.x) : 0.f, a1 = live ? softplus_fast(xv.y) : 0.f;
+            o1[e] = pack2<T>(a0 * cv.x, a1 * cv.y);
+            o2[e] = pack2<T>(a0 * sv2.x, a1 * sv2.y);
+          }
+          tmem_st4(tmem + lane_base + c * 4, o1[0], o1[1], o1[2], o1[3]);
+          tmem_st4(tmem + lane_base + (DC + c) * 4, o2[0], o2[1], o2[2], o2[3]);
+        } else {
+          tmem_st4(tmem + lane_base + c * 4, raw.x, raw.y, raw.z, raw.w);
+        }
+      }
+      tmem_st_wait();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[FW_QFULL]);
+    }
     float m_run = -CUDART_INF_F, l_run = 0.f;
 
-    for (int j = 0; j < T_mine; ++j) {
-      const int buf = j & 1, n0 = j * TK;
-      // key visibility of this tile (key-padding mask, ragged end): one bit per key, the same for every row
+    for (int j = 0; j < T_tiles; ++j) {
+      const int buf = j & 1, n0 = j * FW_TK + part * CPT;   // first key of this thread's columns
+      // key visibility of this thread's columns (key-padding mask, ragged end): one bit per key, the same for every row
       uint64_t vis = ~0ull;
-      if (maskb || n0 + TK > p.Nk) {
+      if (maskb || n0 + CPT > p.Nk) {
         const int j0 = n0 + lane, j1 = j0 + 32;
         const bool ok0 = j0 < p.Nk && (!maskb || maskb[(int64_t)j0 * p.msn] != 0);
-        const bool ok1 = j1 < p.Nk && (!maskb || maskb[(int64_t)j1 * p.msn] != 0);
+        const bool ok1 = CPT == 32 || (j1 < p.Nk && (!maskb || maskb[(int64_t)j1 * p.msn] != 0));
         vis = ((uint64_t)__ballot_sync(0xffffffffu, ok1) << 32) | __ballot_sync(0xffffffffu, ok0);
       }
       if (p.causal) {
         const int lim = row - n0;  // columns <= lim are visible
         vis &= lim >= 63 ? ~0ull : (lim < 0 ? 0ull : ((2ull << lim) - 1ull));
       }
+      if (CPT == 32) vis |= 0xffffffff00000000ull;
       const bool all_vis = __all_sync(0xffffffffu, vis == ~0ull);
-      if (!failed) failed = !mbar_wait(&bars[B_SFULL + buf * 2 + tile], (j >> 1) & 1, WAIT_LIMIT);
+      if (!failed) failed = !mbar_wait(&bars[FW_SFULL + buf], (j >> 1) & 1, WAIT_LIMIT);
       fence_after_sync();
-      const uint32_t s_addr = tmem + lane_base + (buf * 2 + tile) * 64;
-      uint32_t s0[32], s1[32];
-      tmem_ld32(s_addr, s0);
-      tmem_ld32(s_addr + 32, s1);
+      const uint32_t s_addr = tmem + lane_base + FW_TS + buf * FW_TK + part * CPT;
+      uint32_t sv[CPT / 32][32];
+#pragma unroll
+      for (int q = 0; q < CPT / 32; ++q) tmem_ld32(s_addr + q * 32, sv[q]);
       tmem_ld_wait();
-      // row maximum (four independent chains)
+      // maximum of this thread's scores (four independent chains), then of the row
       float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       if (all_vis) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
-          m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
-        }
-      } else {
-        const uint32_t v0 = (uint32_t)vis, v1 = (uint32_t)(vis >> 32);
+        for (int q = 0; q < CPT / 32; ++q)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if ((v0 >> i) & 1u) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(s0[i]));
-          if ((v1 >> i) & 1u) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(s1[i]));
+          for (int i = 0; i < 32; i += 2)
+            m4[(i >> 1) & 3] = max3(m4[(i >> 1) & 3], __uint_as_float(sv[q][i]), __uint_as_float(sv[q][i + 1]));
+      } else {
+#pragma unroll
+        for (int q = 0; q < CPT / 32; ++q) {
+          const uint32_t vq = (uint32_t)(vis >> (32 * q));
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((vq >> i) & 1u) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[q][i]));
         }
       }
-      const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      xch[(buf * FW_NPR + part) * TQ + rloc] = mx;
+      row_sync();
+#pragma unroll
+      for (int t = 0; t < FW_NPR; ++t) mx = fmaxf(mx, xch[(buf * FW_NPR + t) * TQ + rloc]);
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
       // keep a stale maximum while it is within 2^8 of the true one: P stays below 256 and the
       // output accumulator needs no rescale on most steps
@@ -357,69 +404,76 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
         m_run = m_new;
       }
       if (j > 0 && __any_sync(0xffffffffu, need)) {
-        // O was last written by PV(j-1)
-        if (!failed) failed = !mbar_wait(&bars[B_PVDONE + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
+        // O was last written by PV(j-1); the threads of a row rescale OC of its columns each
+        if (!failed) failed = !mbar_wait(&bars[FW_PVDONE + (1 - buf)], ((j - 1) >> 1) & 1, WAIT_LIMIT);
         fence_after_sync();
-        const uint32_t o_addr = tmem + lane_base + 256 + tile * 128;
+        if (o_active) {
+          const uint32_t o_addr = tmem + lane_base + FW_TO + part * OC;
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t ov[32];
-          tmem_ld32(o_addr + c0, ov);
-          tmem_ld_wait();
+          for (int c0 = 0; c0 < OC; c0 += 16) {
+            uint32_t ov[16];
+            tmem_ld16(o_addr + c0, ov);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st32(o_addr + c0, ov);
+            for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st16(o_addr + c0, ov);
+          }
+          tmem_st_wait();
         }
-        tmem_st_wait();
       }
-      // P = 2^(s*c - m), written over the scores (16 packed columns per 32 scores)
+      // P = 2^(s*c - m), written over this thread's scores (CPT / 2 packed columns for its CPT scores)
       const float m_use = m_run == -CUDART_INF_F ? 0.f : m_run;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[32];
-      // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
+      uint32_t pk[CPT / 32][16];
       auto exponentials = [&](auto masked) {
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          const uint32_t vh = (uint32_t)(vis >> (32 * hh));
+        for (int q = 0; q < CPT / 32; ++q) {
+          const uint32_t vq = (uint32_t)(vis >> (32 * q));
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const uint32_t x0 = hh ? s1[2 * i] : s0[2 * i], x1 = hh ? s1[2 * i + 1] : s0[2 * i + 1];
-            float p0 = ex2_approx(fmaf(__uint_as_float(x0), p.scale_log2, -m_use));
-            float p1 = ex2_approx(fmaf(__uint_as_float(x1), p.scale_log2, -m_use));
+            float p0 = ex2_approx(fmaf(__uint_as_float(sv[q][2 * i]), p.scale_log2, -m_use));
+            float p1 = ex2_approx(fmaf(__uint_as_float(sv[q][2 * i + 1]), p.scale_log2, -m_use));
             if (decltype(masked)::value) {
-              p0 = ((vh >> (2 * i)) & 1u) ? p0 : 0.f;
-              p1 = ((vh >> (2 * i + 1)) & 1u) ? p1 : 0.f;
+              p0 = ((vq >> (2 * i)) & 1u) ? p0 : 0.f;
+              p1 = ((vq >> (2 * i + 1)) & 1u) ? p1 : 0.f;
             }
             ls4[i & 3] += p0 + p1;
-            pk[hh * 16 + i] = pack2<T>(p0, p1);
+            pk[q][i] = pack2<T>(p0, p1);
           }
         }
       };
       if (all_vis) exponentials(std::false_type());
       else exponentials(std::true_type());
       l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-      tmem_st32(s_addr, pk);
+#pragma unroll
+      for (int q = 0; q < CPT / 32; ++q) tmem_st16(s_addr + q * 16, pk[q]);
       tmem_st_wait();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[B_PFULL + buf * 2 + tile]);
+      if (lane == 0) mbar_arrive(&bars[FW_PFULL + buf]);
     }
 
     // ---- epilogue: O / l, LSE ---------------------------------------------------------------------
-    if (T_mine > 0) {
-      if (!failed) failed = !mbar_wait(&bars[B_ODONE + tile], 0, WAIT_LIMIT);
-      fence_after_sync();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      const uint32_t o_addr = tmem + lane_base + 256 + tile * 128;
-      T* orow = (T*)p.o + b * p.so.b + h * p.so.h + (int64_t)row * p.so.n;
+    row_sync();   // (every thread of the row is past its last look at the row maxima)
+    lxch[part * TQ + rloc] = l_run;
+    row_sync();
+    float l_tot = 0.f;
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t ov[32];
-        tmem_ld32(o_addr + c0, ov);
+    for (int t = 0; t < FW_NPR; ++t) l_tot += lxch[t * TQ + rloc];
+    if (T_tiles > 0 && !failed) failed = !mbar_wait(&bars[FW_ODONE], 0, WAIT_LIMIT);
+    fence_after_sync();
+    const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+    if (o_active) {
+      const uint32_t o_addr = tmem + lane_base + FW_TO + part * OC;
+      T* orow = (T*)p.o + b * p.so.b + h * p.so.h + (int64_t)row * p.so.n + part * OC;
+#pragma unroll
+      for (int c0 = 0; c0 < OC; c0 += 16) {
+        uint32_t ov[16];
+        tmem_ld16(o_addr + c0, ov);
         tmem_ld_wait();
         if (row < p.Nq) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
+          for (int i = 0; i < 16; i += 8) {
             uint4 w;
             w.x = pack2<T>(__uint_as_float(ov[i]) * inv, __uint_as_float(ov[i + 1]) * inv);
             w.y = pack2<T>(__uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
@@ -429,21 +483,33 @@ __global__ void __launch_bounds__(FWD_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, c
           }
         }
       }
-      if (row < p.Nq)
-        p.lse[(int64_t)u * p.Nq + row] = l_run > 0.f ? m_run * LN2 + logf(l_run) : -CUDART_INF_F;
     }
+    if (part == 0 && row < p.Nq) p.lse[(int64_t)u * p.Nq + row] = l_tot > 0.f ? m_run * LN2 + logf(l_tot) : -CUDART_INF_F;
   }
   if (failed) atomicOr(&g_tc_status, 1u);
   fence_before_sync();
   __syncthreads();
-  if (warp == FWD_MMA_WARP) tmem_dealloc(tmem, 512);
+  if (warp == FW_S_WARP) tmem_dealloc(tmem, 512);
 }
 
-}  // namespace pope
+template <int D, typename T>
+static cudaError_t launch_fwd_kernel(const PopeAttnArgs& a, const TcFwdP& p, cudaStream_t st) {
+  const PopeShape& s = a.shape;
+  const int KD = s.d + s.r;
+  CUtensorMap tmap_v;
+  const bool tm_ok = D % 64 == 0 ? make_wide_tmap(&tmap_v, a.v, s.dtype == POPE_BF16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, FW_TK)
+                                 : make_chunk_tmap(&tmap_v, a.v, s.dtype == POPE_BF16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, FW_TK);
+  if (!tm_ok) return cudaErrorNotSupported;
+  size_t smem = 2 * (size_t)FW_TK * KD * 2 + FW_VST * (size_t)FW_TK * D * 2 + 2 * FW_NPR * TQ * sizeof(float) + (FW_COUNT + 1) * 8 + 16 + 1024;
+  // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
+  if (smem < 120 * 1024) smem = 120 * 1024;
+  cudaError_t e = ensure_max_smem<attn_fwd_tc_kernel<D, T>>();
+  if (e != cudaSuccess) return e;
+  dim3 grid((s.Nq + TQ - 1) / TQ, s.B * s.H);
+  attn_fwd_tc_kernel<D, T><<<grid, FW_THREADS, smem, st>>>(p, tmap_v);
+  return cudaGetLastError();
+}
 
-#include "tc_attn_fwd2.inl"
-
-namespace pope {
 
 // ---- host side ---------------------------------------------------------------------------------
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -465,55 +531,40 @@ bool attn_fwd_tc_supported(const PopeAttnArgs& a) {
   return true;
 }
 
-// workspace: [fp32 and fp16 cos / sin tables][K' image tiles of all (batch, key head) units][Q' image tiles of all (batch, head) units]
+// workspace: [fp16 cos / sin tables][K' image tiles of all (batch, key head) units]
 static size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 size_t attn_fwd_tc_workspace(const PopeAttnArgs& a) {
   const PopeShape& s = a.shape;
-  return trig_tables_bytes(s.Nk, s.r, table_slices(a.embed, s.B, s.H)) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r)) +
-         image_bytes(s.B * s.H, s.Nq, s.d + s.r);
+  return trig_tables_bytes(s.Nk, s.r, table_slices(a.embed, s.B, s.H)) + up256(image_bytes(s.B * s.Hk, s.Nk, s.d + s.r));
 }
 
 template <int D, typename T>
 static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
-  const int KD = s.d + s.r;
   const bool bf16 = s.dtype == POPE_BF16;
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);
   const int slices = table_slices(a.embed, s.B, s.H), tab_heads = table_heads(a.embed, s.H), by_batch = a.embed.sf.b != 0;
   const TrigTables tt = trig_tables_at(ws, s.Nk, s.r, slices);
   uint8_t* kimg = ws + trig_tables_bytes(s.Nk, s.r, slices);
-  uint8_t* qimg = kimg + up256(image_bytes(s.B * s.Hk, s.Nk, KD));
   TcFwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
   p.scale_log2 = a.softmax_scale * LOG2E;
   p.q = a.q, p.k = a.k, p.v = a.v, p.o = a.out, p.lse = a.lse;
   p.sq = a.sq, p.sk = a.sk, p.sv = a.sv, p.so = a.so;
   p.freqs = a.embed.freqs, p.sfn = a.embed.sf.n, p.bias = a.embed.bias, p.bias_sh = a.embed.bias_stride_h;
-  p.qimg = qimg, p.kimg = kimg;
+  p.kimg = kimg;
+  p.ch = static_cast<const __half*>(tt.ch), p.sh = static_cast<const __half*>(tt.sh);
+  p.tab_slice_stride = (int64_t)s.Nk * s.r, p.tab_by_batch = by_batch, p.tab_heads = tab_heads;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
   cudaError_t e;
   if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, tt.ch, tt.sh, st, slices, tab_heads)) != cudaSuccess) return e;
+  // K' (phase bias folded in) as 128-row image tiles: the kernel streams it 128 keys at a time; Q' is expanded in the kernel
   ExpandJobs jobs;
   jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg, s.Nk, by_batch, tab_heads);
-  jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg, s.Nk, by_batch, tab_heads);
-#ifndef POPE_FWD_V1
-  jobs.job[0].tile128 = 1;   // the kernel streams K' 128 keys at a time
-#endif
-  if ((e = launch_expand_images(jobs, 2, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
-#ifndef POPE_FWD_V1
-  return launch_fwd2_kernel<D, T>(a, p, st);
-#endif
-  CUtensorMap tmap_v;
-  if (!make_chunk_tmap(&tmap_v, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, TK)) return cudaErrorNotSupported;
-  size_t smem = (size_t)2 * TQ * KD * 2 + 2 * (size_t)TK * KD * 2 + 2 * (size_t)TK * D * 2 + (B_COUNT + 1) * 8 + 16;
-  // every CTA allocates all 512 TMEM columns: ask for more than half of the SM's shared memory so
-  // that two CTAs are never co-resident
-  if (smem < 120 * 1024) smem = 120 * 1024;
-  if ((e = ensure_max_smem<attn_fwd_tc_kernel<D, T>>()) != cudaSuccess) return e;
-  dim3 grid((s.Nq + 2 * TQ - 1) / (2 * TQ), s.B * s.H);
-  attn_fwd_tc_kernel<D, T><<<grid, FWD_THREADS, smem, st>>>(p, tmap_v);
-  return cudaGetLastError();
+  jobs.job[0].tile128 = 1;
+  if ((e = launch_expand_images(jobs, 1, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+  return launch_fwd_kernel<D, T>(a, p, st);
 }
 
 template <typename T>

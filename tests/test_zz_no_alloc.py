@@ -60,8 +60,8 @@ def test_noalloc_forward_matches_regular_entry_point_twice_in_a_row():
 
 def test_noalloc_rejects_what_it_cannot_serve():
     lib = _native.load_library()
-    q, k, v, freqs, bias, mask, causal, scale = _case(4, 1, 1, 16384, 128, 128, True, False)  # 8 MiB table
-    out, lse = torch.empty_like(q), torch.empty(1, 1, 16384, device=DEV)
+    q, k, v, freqs, bias, mask, causal, scale = _case(4, 1, 1, 16640, 128, 128, True, False)  # 8.1 MiB of tables + 8.1 MiB of K' tiles
+    out, lse = torch.empty_like(q), torch.empty(1, 1, 16640, device=DEV)
     with pytest.raises(RuntimeError, match="capacity"):
         _native.attn_forward_noalloc(q, k, v, freqs, bias, mask, causal, scale, out, lse)
     q32 = torch.randn(1, 1, 128, 64, device=DEV)                     # fp32: not a tensor-core shape
