@@ -46,7 +46,7 @@ UNIT = "TFLOP/s"
 # captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); traffic is proportional to
 # the number of (batch, head) units, so a B=4 launch moves 4x these.  Constants, not live measurements.
 NCU_TRAFFIC_B1 = {
-    "fwd": {"expand_image_kernel": 49.6e6, "attn_fwd_tc_kernel": 89.0e6},
+    "fwd": {"expand_image_kernel": 18.9e6, "attn_fwd_tc_kernel": 74.8e6},
     "bwd": {"bwd_rowstat_kernel": 33.8e6, "expand_image_kernel": 118.9e6, "attn_bwd_dq_tc_kernel": 108.8e6,
             "attn_bwd_dkdv_tc_kernel": 117.0e6},
 }
@@ -732,7 +732,7 @@ def main():
                       frac_of_sustained_peak=bwd_achieved / (pk["bf16_tflops_sustained"] or pk["bf16_tflops"]),
                       forward=dict(achieved=ffl / (fwd_ms * 1e-3) / 1e12, frac=ffl / (fwd_ms * 1e-3) / 1e12 / peak,
                                    traffic=traffic["fwd"] if traffic else None,
-                                   what="forward call (tables + images + attn_fwd_tc_kernel), algorithmic flops 2*U*pairs*(2d+r)"),
+                                   what="forward call (tables + K' images + attn_fwd_tc_kernel), algorithmic flops 2*U*pairs*(2d+r); its K' image (33.5 MB at B=1) is still dirty in L2 when the pre-pass ends, which is why the pre-pass shows 19 MB"),
                       step=dict(achieved=achieved, frac=achieved / peak, frac_of_burst_peak=achieved / pk["bf16_tflops"],
                                 what="forward + backward of one step, algorithmic flops 2*U*pairs*(7d+4r)")),
         long_context=long_context,
