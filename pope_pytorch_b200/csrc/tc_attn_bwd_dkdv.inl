@@ -285,7 +285,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
   constexpr int OSTR = D * 2 + 16;             // bytes of a staged output row (16 bytes of padding: conflict-free)
   uint8_t* dk_stage = Vs;
   uint8_t* dv_stage = Vs + BQ * OSTR;
-  float* dmat = reinterpret_cast<float*>(Vs + 2 * BQ * OSTR);   // [r][128]
+  float* dmat = reinterpret_cast<float*>(Vs + 2 * BQ * OSTR);   // [128 rows][r + 1]: a thread writes its row, the column sums
+  const int DSTR = p.r + 1;                                     // read along a row; the odd stride keeps both off bank conflicts
   {
     constexpr int HW = D / 2;
     const uint32_t accv = tmem + lane_base + TK_DV, acck = tmem + lane_base + TK_DK;
@@ -327,13 +328,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
           const float sg0 = 1.f - ex2_approx(-m0 * r0 * LOG2E), sg1 = 1.f - ex2_approx(-m1 * r1 * LOG2E);
           const float d0 = h0 * kc.x - g0 * ks.x, d1 = h1 * kc.y - g1 * ks.y;
           if (dfrow && live) atomicAdd(dfrow + cbase + e, d0), atomicAdd(dfrow + cbase + e + 1, d1);
-          if (p.dbias) dmat[(cbase + e) * BQ + row] = d0, dmat[(cbase + e + 1) * BQ + row] = d1;
+          if (p.dbias) dmat[row * DSTR + cbase + e] = d0, dmat[row * DSTR + cbase + e + 1] = d1;
           wk[e >> 1] = pack2<T>((g0 * kc.x + h0 * ks.x) * r0 * sg0, (g1 * kc.y + h1 * ks.y) * r1 * sg1);
         }
       } else {
         if (p.dbias && cbase < p.r) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) dmat[(cbase + e) * BQ + row] = 0.f;
+          for (int e = 0; e < 16; ++e) dmat[row * DSTR + cbase + e] = 0.f;
         }
 #pragma unroll
         for (int e = 0; e < 16; e += 2) wk[e >> 1] = pack2<T>(__uint_as_float(gc[e]), __uint_as_float(gc[e + 1]));
@@ -358,12 +359,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       }
     }
     if (p.dbias) {
-      // column sums of the key-phase gradient: one warp per feature, lanes stride over the 128 rows
-      for (int c = warp; c < p.r; c += BWD_E_WARPS) {
-        const float* col = dmat + c * BQ;
-        float sum = (col[lane] + col[lane + 32]) + (col[lane + 64] + col[lane + 96]);
-        sum = warp_sum(sum);
-        if (lane == 0) atomicAdd(p.dbias + hk * p.dbias_sh + c, sum);
+      // column sums of the key-phase gradient: a thread per (feature, half of the rows), four running sums
+      // (one warp per feature with a shuffle reduction took 4800 clocks of this epilogue; this takes a sixth)
+      const int c = tid & 127, r0 = (tid >> 7) * (BQ / 2);
+      if (c < p.r) {
+        const float* col = dmat + r0 * DSTR + c;
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int rr = 0; rr < BQ / 2; rr += 4) {
+          s4[0] += col[rr * DSTR], s4[1] += col[(rr + 1) * DSTR], s4[2] += col[(rr + 2) * DSTR], s4[3] += col[(rr + 3) * DSTR];
+        }
+        atomicAdd(p.dbias + hk * p.dbias_sh + c, (s4[0] + s4[1]) + (s4[2] + s4[3]));
       }
     }
   }
