@@ -626,11 +626,18 @@ def main():
     h_out = [torch.empty_like(hq).pin_memory() for _ in range(4)]
     h_dbias = torch.empty(H, r).pin_memory()
 
-    # The step is cut along the batch axis and software-pipelined over three streams (host->device copies, compute,
-    # device->host copies): PCIe is full duplex, so chunk c+1 arrives and chunk c-1 leaves while chunk c computes.
+    # The step is cut into (batch entry, half of the heads) chunks and software-pipelined over three streams (host->device
+    # copies, compute, device->host copies): PCIe is full duplex, so chunk c+1 arrives and chunk c-1 leaves while chunk c
+    # computes, and a small last chunk keeps the un-overlapped tail (its compute and its copy back) short.
     # Everything still goes through the public API, one call per chunk; the phase-bias gradient is summed over chunks.
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    chunks = B
+    hsplit = 2 if H % 2 == 0 else 1
+    chunks = B * hsplit
+    hpc = H // hsplit
+
+    def chunk_of(t, c):      # (1, hpc, N, d) view of chunk c: contiguous in a (B, H, N, d) tensor
+        b_i, h0 = c // hsplit, (c % hsplit) * hpc
+        return t[b_i:b_i + 1, h0:h0 + hpc]
 
     def e2e_step():
         main = torch.cuda.current_stream()
@@ -641,7 +648,7 @@ def main():
         arrived = []
         for c in range(chunks):
             with torch.cuda.stream(s_in):
-                xs = [t[c:c + 1].to(dev, non_blocking=True) for t in (hq, hk, hv, hdo)]
+                xs = [chunk_of(t, c).to(dev, non_blocking=True) for t in (hq, hk, hv, hdo)]
                 ev_ = torch.cuda.Event()
                 ev_.record(s_in)
             arrived.append((xs, ev_))
@@ -649,16 +656,17 @@ def main():
             xs, ev_ = arrived[c]
             main.wait_event(ev_)
             dq_, dk_, dv_ = (t.requires_grad_(True) for t in xs[:3])
-            bias_p = bias.clone().requires_grad_(True)
+            h0 = (c % hsplit) * hpc
+            bias_p = bias[h0:h0 + hpc].clone().requires_grad_(True)
             out = flash_attn_with_pope(dq_, dk_, dv_, pos_emb=(freqs, bias_p), causal=True)
             out.backward(xs[3])
-            dbias_acc += bias_p.grad
+            dbias_acc[h0:h0 + hpc] += bias_p.grad
             done = torch.cuda.Event()
             done.record(main)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
                 for dst, src in zip(h_out, (out.detach(), dq_.grad, dk_.grad, dv_.grad)):
-                    dst[c:c + 1].copy_(src, non_blocking=True)
+                    chunk_of(dst, c).copy_(src, non_blocking=True)
             keep.append((xs, out, dq_, dk_, dv_, bias_p))
         main.wait_stream(s_out)
         h_dbias.copy_(dbias_acc, non_blocking=True)
@@ -740,7 +748,7 @@ def main():
         secondary=secondary,
         e2e=dict(value=e2e_value, unit=UNIT, ms_per_step=e2e_ms, h2d_bytes_per_step=4 * tensor_bytes,
                  d2h_bytes_per_step=4 * tensor_bytes + h_dbias.numel() * 4, steps=e2e_steps,
-                 api="flash_attn_with_pope(...).backward() per batch element, pipelined over copy-in / compute / copy-out streams; pinned host q,k,v,dO in; out,dq,dk,dv,dbias back to host",
+                 api="flash_attn_with_pope(...).backward() per (batch entry, half of the heads), pipelined over copy-in / compute / copy-out streams; pinned host q,k,v,dO in; out,dq,dk,dv,dbias back to host",
                  limiter="PCIe: 268 MB each way per step; the ranks of one box share the host's PCIe complex"),
         gpu_launches=launches_per_step * args.steps,
         clocks=clocks,
