@@ -492,25 +492,6 @@ __global__ void __launch_bounds__(FW_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, co
   if (warp == FW_S_WARP) tmem_dealloc(tmem, 512);
 }
 
-template <int D, typename T>
-static cudaError_t launch_fwd_kernel(const PopeAttnArgs& a, const TcFwdP& p, cudaStream_t st) {
-  const PopeShape& s = a.shape;
-  const int KD = s.d + s.r;
-  CUtensorMap tmap_v;
-  const bool tm_ok = D % 64 == 0 ? make_wide_tmap(&tmap_v, a.v, s.dtype == POPE_BF16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, FW_TK)
-                                 : make_chunk_tmap(&tmap_v, a.v, s.dtype == POPE_BF16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, FW_TK);
-  if (!tm_ok) return cudaErrorNotSupported;
-  size_t smem = 2 * (size_t)FW_TK * KD * 2 + FW_VST * (size_t)FW_TK * D * 2 + 2 * FW_NPR * TQ * sizeof(float) + (FW_COUNT + 1) * 8 + 16 + 1024;
-  // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
-  if (smem < 120 * 1024) smem = 120 * 1024;
-  cudaError_t e = ensure_max_smem<attn_fwd_tc_kernel<D, T>>();
-  if (e != cudaSuccess) return e;
-  dim3 grid((s.Nq + TQ - 1) / TQ, s.B * s.H);
-  attn_fwd_tc_kernel<D, T><<<grid, FW_THREADS, smem, st>>>(p, tmap_v);
-  return cudaGetLastError();
-}
-
-
 // ---- host side ---------------------------------------------------------------------------------
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static bool stride_ok(const PopeStride3& s) { return s.b % 8 == 0 && s.h % 8 == 0 && s.n % 8 == 0; }
@@ -557,14 +538,27 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   p.ch = static_cast<const __half*>(tt.ch), p.sh = static_cast<const __half*>(tt.sh);
   p.tab_slice_stride = (int64_t)s.Nk * s.r, p.tab_by_batch = by_batch, p.tab_heads = tab_heads;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
-  cudaError_t e;
-  if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, tt.ch, tt.sh, st, slices, tab_heads)) != cudaSuccess) return e;
+  // all host-side preparation first, then the three launches back to back (what the host does between two launches is
+  // time the GPU spends idle on small problems)
+  const int KD = s.d + s.r;
+  CUtensorMap tmap_v;
+  const bool tm_ok = D % 64 == 0 ? make_wide_tmap(&tmap_v, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, FW_TK)
+                                 : make_chunk_tmap(&tmap_v, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, FW_TK);
+  if (!tm_ok) return cudaErrorNotSupported;
+  size_t smem = 2 * (size_t)FW_TK * KD * 2 + FW_VST * (size_t)FW_TK * D * 2 + 2 * FW_NPR * TQ * sizeof(float) + (FW_COUNT + 1) * 8 + 16 + 1024;
+  // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
+  if (smem < 120 * 1024) smem = 120 * 1024;
+  cudaError_t e = ensure_max_smem<attn_fwd_tc_kernel<D, T>>();
+  if (e != cudaSuccess) return e;
   // K' (phase bias folded in) as 128-row image tiles: the kernel streams it 128 keys at a time; Q' is expanded in the kernel
   ExpandJobs jobs;
   jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg, s.Nk, by_batch, tab_heads);
   jobs.job[0].tile128 = 1;
+  if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, tt.ch, tt.sh, st, slices, tab_heads)) != cudaSuccess) return e;
   if ((e = launch_expand_images(jobs, 1, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
-  return launch_fwd_kernel<D, T>(a, p, st);
+  dim3 grid((s.Nq + TQ - 1) / TQ, s.B * s.H);
+  attn_fwd_tc_kernel<D, T><<<grid, FW_THREADS, smem, st>>>(p, tmap_v);
+  return cudaGetLastError();
 }
 
 template <typename T>

@@ -392,8 +392,7 @@ cudaError_t sim_bwd_tc(const PopeSimBwdArgs& a, cudaStream_t st) {
   sim_fwd_tc_image_bytes(s, &q_bytes);
   uint8_t* qimg = static_cast<uint8_t*>(a.workspace);
   uint8_t* kimg = qimg + q_bytes;
-  cudaError_t e = sim_launch_prepass(s, a.embed, a.q, a.sq, a.k, a.sk, qimg, kimg, 64, st);
-  if (e != cudaSuccess) return e;
+  cudaError_t e;
   TcSimBwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.d = s.d, p.r = s.r;
   p.qtiles = (s.Nq + 63) / 64, p.ktiles = (s.Nk + 63) / 64;
@@ -416,6 +415,8 @@ cudaError_t sim_bwd_tc(const PopeSimBwdArgs& a, cudaStream_t st) {
   if ((e = ensure_max_smem<sim_bwd_tc_kernel<float>>()) != cudaSuccess) return e;
   const int groups = s.H / s.Hk;
   const unsigned grid = (unsigned)(s.B * s.Hk) * (unsigned)(groups * ((s.Nq + 127) / 128) + (s.Nk + 127) / 128);
+  // (the host-side preparation is done: the two launches go out back to back)
+  if ((e = sim_launch_prepass(s, a.embed, a.q, a.sq, a.k, a.sk, qimg, kimg, 64, st)) != cudaSuccess) return e;
   sim_bwd_tc_kernel<float><<<grid, SBW_THREADS, smem, st>>>(p, tmap_q, tmap_k);
   return cudaGetLastError();
 }

@@ -475,14 +475,15 @@ static cudaError_t launch_sim_tc(const PopeSimArgs& a, cudaStream_t st) {
   p.ktiles = (s.Nk + SIM_N - 1) / SIM_N;
   p.rblocks = (qtiles + MT - 1) / MT;
   p.total_tiles = (int64_t)s.B * s.H * p.rblocks * p.ktiles;
-  cudaError_t e = sim_launch_prepass(s, a.embed, a.q, a.sq, a.k, a.sk, qimg, kimg, SIM_M, st);
-  if (e != cudaSuccess) return e;
+  // (all host-side preparation first, then the two launches back to back: what the host does between them is time
+  // the GPU spends idle on small problems)
   CUtensorMap tmap;
   memset(&tmap, 0, sizeof(tmap));
   p.use_tma = make_store_tmap(&tmap, a.sim, s.dtype, s.Nk, s.Nq, s.H, s.B, a.ss.n, a.ss.h, a.ss.b, 32) ? 1 : 0;
   const SimSmem L = sim_smem_plan(s.d + s.r, s.r, SPLIT, MT, NKB);
   // keep one CTA per SM: TMEM columns are allocated per CTA
   const size_t smem = L.total < 120 * 1024 ? 120 * 1024 : L.total;
+  cudaError_t e;
   if ((e = ensure_max_smem<sim_fwd_tc_kernel<T, SPLIT, MT, NKB>>()) != cudaSuccess) return e;
   static int sms = 0;
   if (sms == 0) {
@@ -491,6 +492,7 @@ static cudaError_t launch_sim_tc(const PopeSimArgs& a, cudaStream_t st) {
     sms = n;
   }
   const unsigned grid = (unsigned)std::min<int64_t>(sms, p.total_tiles);
+  if ((e = sim_launch_prepass(s, a.embed, a.q, a.sq, a.k, a.sk, qimg, kimg, SIM_M, st)) != cudaSuccess) return e;
   sim_fwd_tc_kernel<T, SPLIT, MT, NKB><<<grid, SIM_THREADS, smem, st>>>(p, tmap);
   return cudaGetLastError();
 }
