@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(FW_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, co
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles sit on 1 KB boundaries
   // V tiles: D a multiple of 64 -> boxes of 64 features (128-byte rows, 128-byte swizzled); else 16-byte chunk columns
   constexpr bool VWIDE = D % 64 == 0;
-  const int KD = D + p.r, KC = KD >> 3, KSTEPS = KD >> 4;
+  const int KD = D + p.r, KSTEPS = KD >> 4;
   const int KBUF = FW_TK * KD * 2;                  // one K' stage: [KD/8 chunks][128 keys][16 B]
   constexpr int VBUF = FW_TK * D * 2;               // one V stage:  [D/8 chunks][128 keys][16 B]
   constexpr int CSV = FW_TK * 16;                   // chunk stride of both
