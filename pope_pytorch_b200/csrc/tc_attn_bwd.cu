@@ -13,6 +13,7 @@
 // phase bias of the keys is part of the K' images.  A streamed tile in shared memory serves two MMAs: as the
 // K-major B operand of the score product and, re-described as MN-major, as the B operand of the gradient
 // product -- the 8x16-byte core-matrix layout is symmetric under that exchange.
+#include <cstring>
 #include <mutex>
 #include <type_traits>
 
@@ -76,9 +77,13 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 // ================================================================================================
 constexpr int DQ_NST = 3;
 
-template <int D, typename T>
-__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+// VW: V tiles come straight from the caller's V as tensor-map boxes of 64 features (128-byte rows, 128-byte swizzled,
+// read through swizzled K-major descriptors) and dO rows straight from the caller's dO; otherwise both come from the
+// re-laid image tiles of the pre-pass (head widths that are no multiple of 64, strides a tensor map cannot describe).
+template <int D, typename T, bool VW>
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p, const __grid_constant__ CUtensorMap tmap_v) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles sit on 1 KB boundaries
   const int KD = D + p.r, KSTEPS = KD >> 4;
   const int KBUF = (KD / 8) * BCS;             // one K' image tile
   constexpr int VBUF = (D / 8) * BCS;          // one V image tile
@@ -140,7 +145,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         if (failed) { drain_copies(&bars[BB_FULL], DQ_NST, j - DQ_NST, j); break; }
         mbar_expect_tx(&bars[BB_FULL + st], KBUF + VBUF);
         bulk_load(Ks + st * KBUF, kimg + (int64_t)(n0 / BT) * KBUF, KBUF, &bars[BB_FULL + st]);
-        bulk_load(Vs + st * VBUF, vimg + (int64_t)(n0 / BT) * VBUF, VBUF, &bars[BB_FULL + st]);
+        if (VW) {
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) tma_load_4d(Vs + st * VBUF + c * (BT * 128), &tmap_v, &bars[BB_FULL + st], c * 64, n0, hk, b);
+        } else {
+          bulk_load(Vs + st * VBUF, vimg + (int64_t)(n0 / BT) * VBUF, VBUF, &bars[BB_FULL + st]);
+        }
       }
       if (failed) atomicOr(p.status, 1u);
     }
@@ -187,10 +197,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
           failed = !mbar_wait(&bars[BB_FULL + st], (j / DQ_NST) & 1, WAIT_LIMIT);
           if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
           fence_after_sync();
-          const uint64_t vd = smem_desc(vs_addr + st * VBUF, BCS, 128);
+          // B = V tile, K-major: image: chunk columns BCS apart; boxes: 64-feature blocks of 64 x 128 bytes, 32 bytes per step
+          const uint64_t vd = VW ? smem_desc_sw128(vs_addr + st * VBUF, 16, 1024) : smem_desc(vs_addr + st * VBUF, BCS, 128);
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks)
-            mma_ts_lh(tmem + TC_DP, tmem + TC_DO + ks * 8, desc_lo(vd) + ks * ((2 * BCS) >> 4), desc_hi(vd), idesc_s, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t koff = VW ? (uint32_t)(((ks >> 2) * (BT * 128) + (ks & 3) * 32) >> 4) : (uint32_t)(ks * ((2 * BCS) >> 4));
+            mma_ts_lh(tmem + TC_DP, tmem + TC_DO + ks * 8, desc_lo(vd) + koff, desc_hi(vd), idesc_s, ks > 0);
+          }
           mma_commit(&bars[BB_DPDONE]);
         }
         if (j >= 1) {   // dQ' += dS K'(j-1): dS from TMEM; the K' tile re-described as an MN-major B operand
@@ -230,13 +243,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     // zero there): for a fixed chunk the 32 lanes of a warp (32 consecutive rows) read 512 contiguous bytes, where
     // the row-major dO itself would be touched in 32 different lines per load.
     const uint8_t* gtile = p.gimg + ((int64_t)u * (int64_t)image_tiles(p.Nq) + i0 / BT + (row >> 6)) * VBUF + (row & 63) * 16;
+    // (VW: the row itself; a warp-wide 16-byte load then touches 32 rows, which costs this one-time 32 KB read little)
+    const T* grow_ = static_cast<const T*>(p.dout) + b * p.sdo.b + h * p.sdo.h + (int64_t)gi * p.sdo.n;
 #pragma unroll
     for (int g = 0; g < D / 32; ++g) {
       if ((g & 1) != half) continue;
       uint32_t w[16];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        const uint4 v4 = __ldg(reinterpret_cast<const uint4*>(gtile + (g * 4 + q4) * BCS));
+        uint4 v4 = make_uint4(0, 0, 0, 0);
+        if (!VW) v4 = __ldg(reinterpret_cast<const uint4*>(gtile + (g * 4 + q4) * BCS));
+        else if (gi < p.Nq) v4 = __ldg(reinterpret_cast<const uint4*>(grow_ + (g * 4 + q4) * 8));
         w[q4 * 4] = v4.x, w[q4 * 4 + 1] = v4.y, w[q4 * 4 + 2] = v4.z, w[q4 * 4 + 3] = v4.w;
       }
       tmem_st16(tmem + lane_base + TC_DO + g * 16, w);

@@ -21,9 +21,11 @@ enum { KB_QFULL = 0,     // [3] Q' tile j (and its lse / delta rows) has landed 
        KB_COUNT = 20 };
 constexpr int KQ_NST = 3, KG_NST = 2;
 
-template <int D, typename T>
-__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+template <int D, typename T, bool VW>
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p, const __grid_constant__ CUtensorMap tmap_v,
+                                                                          const __grid_constant__ CUtensorMap tmap_g) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles sit on 1 KB boundaries
   const int KD = D + p.r, KSTEPS = KD >> 4;
   uint8_t* Ks = smem;                          // [KD/8][128][16 B]  resident K' (phase fk + bias)
   uint8_t* Vs = Ks + BQ * KD * 2;              // [D/8][128][16 B]   resident V
@@ -82,7 +84,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
         if (lane == 0) mbar_expect_tx(&bars[KB_RESIDENT], BQ * KD * 2 + BQ * D * 2);
         __syncwarp();
         copy_resident_tiles(Ks, p.kimg + t0 * KBUF, KD / 8, &bars[KB_RESIDENT], lane);
-        copy_resident_tiles(Vs, p.vimg + t0 * VBUF, D / 8, &bars[KB_RESIDENT], lane);
+        if (!VW) copy_resident_tiles(Vs, p.vimg + t0 * VBUF, D / 8, &bars[KB_RESIDENT], lane);
+        else if (lane < D / 64) tma_load_4d(Vs + lane * (BQ * 128), &tmap_v, &bars[KB_RESIDENT], lane * 64, j0, hk, b);
       }
     }
     if (lane == 0) {
@@ -98,7 +101,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
         if (j >= KG_NST && !failed) failed = !mbar_wait(&bars[KB_ACCG + sg], ((j - KG_NST) / KG_NST) & 1, WAIT_LIMIT);
         if (failed) { drain_copies(&bars[KB_QFULL], KQ_NST, j + 1 - KQ_NST, j + 1), drain_copies(&bars[KB_GFULL], KG_NST, j - KG_NST, j); break; }
         mbar_expect_tx(&bars[KB_GFULL + sg], VBUF);
-        bulk_load(Gb + sg * VBUF, p.gimg + t * VBUF, VBUF, &bars[KB_GFULL + sg]);
+        if (VW) {
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) tma_load_4d(Gb + sg * VBUF + c * (BT * 128), &tmap_g, &bars[KB_GFULL + sg], c * 64, m0, h, b);
+        } else {
+          bulk_load(Gb + sg * VBUF, p.gimg + t * VBUF, VBUF, &bars[KB_GFULL + sg]);
+        }
       }
       if (failed) atomicOr(p.status, 1u);
     }
@@ -114,7 +122,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
     if (lane == 0 && T_tiles > 0) {
       const uint32_t idesc_s = instr_desc(TcFmt<T>::fmt, BQ, BT, false, false);
       const uint32_t ks_addr = smem_u32(Ks), vs_addr = smem_u32(Vs), qb_addr = smem_u32(Qb), gb_addr = smem_u32(Gb);
-      const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128), va = smem_desc(vs_addr, BQ * 16, 128);
+      // V and the dO tiles: image layout (chunk columns) or 128-byte swizzled boxes (64-feature blocks, 32 bytes per k-step)
+      const uint64_t ka = smem_desc(ks_addr, BQ * 16, 128);
+      const uint64_t va = VW ? smem_desc_sw128(vs_addr, 16, 1024) : smem_desc(vs_addr, BQ * 16, 128);
       if (!mbar_wait(&bars[KB_RESIDENT], 0, WAIT_LIMIT)) failed = true;
       for (int j = 0; j < T_tiles && !failed; ++j) {
         const int sq = j % KQ_NST, sg = j % KG_NST;
@@ -139,11 +149,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
         if (!failed) failed = !mbar_wait(&bars[KB_CONS_S], j & 1, WAIT_LIMIT);
         fence_after_sync();
         {
-          const uint64_t gb = smem_desc(gb_addr + sg * VBUF, BCS, 128);
+          const uint64_t gb = VW ? smem_desc_sw128(gb_addr + sg * VBUF, 16, 1024) : smem_desc(gb_addr + sg * VBUF, BCS, 128);
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks)
-            mma_ss_lh(tmem + TK_SD, desc_lo(va) + ks * ((2 * BQ * 16) >> 4), desc_hi(va), desc_lo(gb) + ks * ((2 * BCS) >> 4),
-                      desc_hi(gb), idesc_s, ks > 0);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t aoff = VW ? (uint32_t)(((ks >> 2) * (BQ * 128) + (ks & 3) * 32) >> 4) : (uint32_t)(ks * ((2 * BQ * 16) >> 4));
+            const uint32_t boff = VW ? (uint32_t)(((ks >> 2) * (BT * 128) + (ks & 3) * 32) >> 4) : (uint32_t)(ks * ((2 * BCS) >> 4));
+            mma_ss_lh(tmem + TK_SD, desc_lo(va) + aoff, desc_hi(va), desc_lo(gb) + boff, desc_hi(gb), idesc_s, ks > 0);
+          }
           mma_commit(&bars[KB_DPDONE]);
           mbar_arrive(&bars[KB_ISS_DP + (j & 1)]);
         }
@@ -164,10 +176,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
         if (j < T_tiles && !failed) failed = !mbar_wait(&bars[KB_ISS_S + (j & 1)], (j >> 1) & 1, WAIT_LIMIT);
         fence_after_sync();
         {
-          const uint64_t gd = smem_desc(gb_addr + pg * VBUF, 128, BCS);
+          // the dO tile re-described as an MN-major B operand (boxes: 64-feature blocks 8 KB apart, 8-row groups 1 KB
+          // apart, 2 KB per 16 query rows)
+          const uint64_t gd = VW ? smem_desc_sw128(gb_addr + pg * VBUF, BT * 128, 1024) : smem_desc(gb_addr + pg * VBUF, 128, BCS);
+          constexpr uint32_t gstep = VW ? (2048 >> 4) : ((2 * 128) >> 4);
 #pragma unroll
           for (int ks = 0; ks < BT / 16; ++ks)
-            mma_ts_lh(tmem + TK_DV, tmem + TK_P + ks * 8, desc_lo(gd) + ks * ((2 * 128) >> 4), desc_hi(gd), idesc_v,
+            mma_ts_lh(tmem + TK_DV, tmem + TK_P + ks * 8, desc_lo(gd) + ks * gstep, desc_hi(gd), idesc_v,
                       (j > 1 || ks > 0) ? 1u : 0u);
           mma_commit(&bars[KB_ACCG + pg]);
         }
@@ -510,6 +525,18 @@ class ForkGuard {
   std::unique_lock<std::mutex> lock_;
 };
 
+template <int D, typename T, bool VW>
+static cudaError_t launch_bwd_kernels(const TcBwdP& p, const PopeShape& s, size_t smem_q, size_t smem_k, const CUtensorMap& tv64,
+                                      const CUtensorMap& tv128, const CUtensorMap& tg64, cudaStream_t st, cudaStream_t sk) {
+  cudaError_t e;
+  if ((e = ensure_max_smem<attn_bwd_dq_tc_kernel<D, T, VW>>()) != cudaSuccess) return e;
+  if ((e = ensure_max_smem<attn_bwd_dkdv_tc_kernel<D, T, VW>>()) != cudaSuccess) return e;
+  attn_bwd_dq_tc_kernel<D, T, VW><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), BWD_THREADS, smem_q, st>>>(p, tv64);
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  attn_bwd_dkdv_tc_kernel<D, T, VW><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, sk>>>(p, tv128, tg64);
+  return cudaGetLastError();
+}
+
 template <int D, typename T>
 static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   const PopeShape& s = a.shape;
@@ -525,6 +552,13 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   uint8_t* gimg = vimg + up256(image_bytes(s.B * s.Hk, s.Nk, s.d));
   float* rowstat = reinterpret_cast<float*>(gimg + up256(image_bytes(s.B * s.H, s.Nq, s.d)));
   cudaError_t e;
+  // V and dO straight from the caller's tensors (tensor-map boxes of 64 features) when the head width is a multiple of
+  // 64 and the tensors can be described; else re-laid image tiles from the pre-pass
+  CUtensorMap tv64, tv128, tg64;
+  memset(&tv64, 0, sizeof(tv64)), memset(&tv128, 0, sizeof(tv128)), memset(&tg64, 0, sizeof(tg64));
+  const bool wide = D % 64 == 0 && make_wide_tmap(&tv64, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, BT) &&
+                    make_wide_tmap(&tv128, a.v, bf16, s.d, s.Nk, s.Hk, s.B, a.sv.n, a.sv.h, a.sv.b, BQ) &&
+                    make_wide_tmap(&tg64, a.dout, bf16, s.d, s.Nq, s.H, s.B, a.sdo.n, a.sdo.h, a.sdo.b, BT);
   // Two independent strands run on two streams: a library-owned side stream forks from the caller's stream, takes the
   // row statistics while the caller's stream builds tables and images, and later the dk/dv kernel while the caller's
   // stream runs the dq kernel (its CTAs fill the SMs which the dq kernel's last partial wave leaves idle); the
@@ -538,13 +572,14 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   if (fork && (e = cudaEventRecord(fk->stats, sk)) != cudaSuccess) return e;
   if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, tt.ch, tt.sh, st, slices, tab_heads)) != cudaSuccess) return e;
-  // K' (phase bias folded in), Q', and V / dO as the same tiles without rotated features (a pure re-layout)
+  // K' (phase bias folded in), Q', and -- unless the kernels read them directly -- V / dO as the same tiles without
+  // rotated features (a pure re-layout)
   ExpandJobs jobs;
   jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg, s.Nk, by_batch, tab_heads);
   jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg, s.Nk, by_batch, tab_heads);
   jobs.job[2] = expand_job(a.v, a.sv, s.B, s.Hk, s.Nk, 0, 0, nullptr, 0, vimg);
   jobs.job[3] = expand_job(a.dout, a.sdo, s.B, s.H, s.Nq, 0, 0, nullptr, 0, gimg);
-  if ((e = launch_expand_images(jobs, 4, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+  if ((e = launch_expand_images(jobs, wide ? 2 : 4, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
   TcBwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
   p.scale = a.softmax_scale, p.scale_log2 = a.softmax_scale * LOG2E;
@@ -558,23 +593,20 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   p.status = tc_status_ptr();
   if (!p.status) return cudaErrorInvalidSymbol;
   const size_t stage = (size_t)BT * KD * 2 + (size_t)BT * D * 2;
-  size_t smem_q = (size_t)BQ * KD * 2 + DQ_NST * stage + (BB_COUNT + 1) * 8 + 16;
+  size_t smem_q = (size_t)BQ * KD * 2 + DQ_NST * stage + (BB_COUNT + 1) * 8 + 16 + 1024;
   size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + KQ_NST * (size_t)BT * KD * 2 + KG_NST * (size_t)BT * D * 2 + KQ_NST * 512 +
-                  (KB_COUNT + 1) * 8 + 16;   // 231.2 KB at d = r = 128
+                  (KB_COUNT + 1) * 8 + 16 + 1024;   // 232.2 KB at d = r = 128 (1 KB of it to put the base on a 1 KB boundary)
   // every CTA allocates all 512 TMEM columns: keep two CTAs from sharing an SM
   if (smem_q < 120 * 1024) smem_q = 120 * 1024;
   if (smem_k < 120 * 1024) smem_k = 120 * 1024;
-  if ((e = ensure_max_smem<attn_bwd_dq_tc_kernel<D, T>>()) != cudaSuccess) return e;
-  if ((e = ensure_max_smem<attn_bwd_dkdv_tc_kernel<D, T>>()) != cudaSuccess) return e;
   if (fork) {   // images -> side stream (dk/dv); row statistics -> caller's stream (dq reads delta)
     if ((e = cudaEventRecord(fk->ready, st)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(fk->side, fk->ready, 0)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(st, fk->stats, 0)) != cudaSuccess) return e;
   }
-  attn_bwd_dq_tc_kernel<D, T><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), BWD_THREADS, smem_q, st>>>(p);
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  attn_bwd_dkdv_tc_kernel<D, T><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, sk>>>(p);
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  e = wide ? launch_bwd_kernels<D, T, (D % 64 == 0)>(p, s, smem_q, smem_k, tv64, tv128, tg64, st, sk)
+           : launch_bwd_kernels<D, T, false>(p, s, smem_q, smem_k, tv64, tv128, tg64, st, sk);
+  if (e != cudaSuccess) return e;
   return fk.join();
 }
 

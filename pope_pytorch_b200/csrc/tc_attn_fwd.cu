@@ -93,7 +93,7 @@ bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, in
 }
 
 // 16-bit rows cut into boxes of 64 features (128 bytes) x box_rows rows, 128-byte swizzled
-static bool make_wide_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
+bool make_wide_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
                            int64_t sh, int64_t sb, int box_rows) {
   return tmap_4d(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, d, rows, heads,
                  batch, sn, sh, sb, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
