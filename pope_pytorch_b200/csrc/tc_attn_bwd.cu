@@ -39,6 +39,7 @@ struct TcBwdP {
   int64_t msb, msn;
   float *dfreqs, *dbias;
   unsigned int* status;
+  int img_maps;          // 1: the resident 128-row operand arrives by one tensor-map copy of its image
 };
 
 constexpr int BQ = 128;  // resident rows per CTA
@@ -81,7 +82,8 @@ constexpr int DQ_NST = 3;
 // read through swizzled K-major descriptors) and dO rows straight from the caller's dO; otherwise both come from the
 // re-laid image tiles of the pre-pass (head widths that are no multiple of 64, strides a tensor map cannot describe).
 template <int D, typename T, bool VW>
-__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p, const __grid_constant__ CUtensorMap tmap_v) {
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p, const __grid_constant__ CUtensorMap tmap_v,
+                                                                        const __grid_constant__ CUtensorMap tmap_qimg) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles sit on 1 KB boundaries
   const int KD = D + p.r, KSTEPS = KD >> 4;
@@ -132,7 +134,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
       const uint8_t* qimg = p.qimg + ((int64_t)u * (int64_t)image_tiles(p.Nq) + i0 / BT) * KBUF;
       if (lane == 0) mbar_expect_tx(&bars[BB_RESIDENT], BQ * KD * 2);
       __syncwarp();
-      copy_resident_tiles(Qs, qimg, KD / 8, &bars[BB_RESIDENT], lane);
+      // one tensor-map copy of (1 KB, 2 image tiles, all chunks) when the image has a map, else 2 x KD / 8 copies of 1 KB
+      if (p.img_maps) {
+        if (lane == 0) tma_load_4d(Qs, &tmap_qimg, &bars[BB_RESIDENT], 0, (int)((int64_t)u * (int64_t)image_tiles(p.Nq) + i0 / BT), 0, 0);
+      } else {
+        copy_resident_tiles(Qs, qimg, KD / 8, &bars[BB_RESIDENT], lane);
+      }
     }
     if (lane == 0) {
       const int64_t ktiles = (int64_t)image_tiles(p.Nk);

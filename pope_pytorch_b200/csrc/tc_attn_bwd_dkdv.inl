@@ -23,7 +23,8 @@ constexpr int KQ_NST = 3, KG_NST = 2;
 
 template <int D, typename T, bool VW>
 __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP p, const __grid_constant__ CUtensorMap tmap_v,
-                                                                          const __grid_constant__ CUtensorMap tmap_g) {
+                                                                          const __grid_constant__ CUtensorMap tmap_g,
+                                                                          const __grid_constant__ CUtensorMap tmap_kimg) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzled tiles sit on 1 KB boundaries
   const int KD = D + p.r, KSTEPS = KD >> 4;
@@ -83,7 +84,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dkdv_tc_kernel(TcBwdP
       if (T_tiles > 0) {   // (a CTA without any visible query row would leave with these copies in flight)
         if (lane == 0) mbar_expect_tx(&bars[KB_RESIDENT], BQ * KD * 2 + BQ * D * 2);
         __syncwarp();
-        copy_resident_tiles(Ks, p.kimg + t0 * KBUF, KD / 8, &bars[KB_RESIDENT], lane);
+        if (p.img_maps) {
+          if (lane == 31) tma_load_4d(Ks, &tmap_kimg, &bars[KB_RESIDENT], 0, (int)t0, 0, 0);
+        } else {
+          copy_resident_tiles(Ks, p.kimg + t0 * KBUF, KD / 8, &bars[KB_RESIDENT], lane);
+        }
         if (!VW) copy_resident_tiles(Vs, p.vimg + t0 * VBUF, D / 8, &bars[KB_RESIDENT], lane);
         else if (lane < D / 64) tma_load_4d(Vs + lane * (BQ * 128), &tmap_v, &bars[KB_RESIDENT], lane * 64, j0, hk, b);
       }
@@ -527,13 +532,14 @@ class ForkGuard {
 
 template <int D, typename T, bool VW>
 static cudaError_t launch_bwd_kernels(const TcBwdP& p, const PopeShape& s, size_t smem_q, size_t smem_k, const CUtensorMap& tv64,
-                                      const CUtensorMap& tv128, const CUtensorMap& tg64, cudaStream_t st, cudaStream_t sk) {
+                                      const CUtensorMap& tv128, const CUtensorMap& tg64, const CUtensorMap& tqi,
+                                      const CUtensorMap& tki, cudaStream_t st, cudaStream_t sk) {
   cudaError_t e;
   if ((e = ensure_max_smem<attn_bwd_dq_tc_kernel<D, T, VW>>()) != cudaSuccess) return e;
   if ((e = ensure_max_smem<attn_bwd_dkdv_tc_kernel<D, T, VW>>()) != cudaSuccess) return e;
-  attn_bwd_dq_tc_kernel<D, T, VW><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), BWD_THREADS, smem_q, st>>>(p, tv64);
+  attn_bwd_dq_tc_kernel<D, T, VW><<<dim3((s.Nq + BQ - 1) / BQ, s.B * s.H), BWD_THREADS, smem_q, st>>>(p, tv64, tqi);
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  attn_bwd_dkdv_tc_kernel<D, T, VW><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, sk>>>(p, tv128, tg64);
+  attn_bwd_dkdv_tc_kernel<D, T, VW><<<dim3((s.Nk + BQ - 1) / BQ, s.B * s.Hk), BWD_THREADS, smem_k, sk>>>(p, tv128, tg64, tki);
   return cudaGetLastError();
 }
 
@@ -592,6 +598,10 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   p.dfreqs = s.r > 0 ? a.dfreqs : nullptr, p.dbias = s.r > 0 ? a.dbias : nullptr;
   p.status = tc_status_ptr();
   if (!p.status) return cudaErrorInvalidSymbol;
+  CUtensorMap tqi, tki;
+  memset(&tqi, 0, sizeof(tqi)), memset(&tki, 0, sizeof(tki));
+  p.img_maps = make_image_tmap(&tqi, qimg, (int64_t)s.B * s.H * (int64_t)image_tiles(s.Nq), KD / 8) &&
+               make_image_tmap(&tki, kimg, (int64_t)s.B * s.Hk * (int64_t)image_tiles(s.Nk), KD / 8);
   const size_t stage = (size_t)BT * KD * 2 + (size_t)BT * D * 2;
   size_t smem_q = (size_t)BQ * KD * 2 + DQ_NST * stage + (BB_COUNT + 1) * 8 + 16 + 1024;
   size_t smem_k = (size_t)BQ * KD * 2 + BQ * D * 2 + KQ_NST * (size_t)BT * KD * 2 + KG_NST * (size_t)BT * D * 2 + KQ_NST * 512 +
@@ -604,8 +614,8 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
     if ((e = cudaStreamWaitEvent(fk->side, fk->ready, 0)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(st, fk->stats, 0)) != cudaSuccess) return e;
   }
-  e = wide ? launch_bwd_kernels<D, T, (D % 64 == 0)>(p, s, smem_q, smem_k, tv64, tv128, tg64, st, sk)
-           : launch_bwd_kernels<D, T, false>(p, s, smem_q, smem_k, tv64, tv128, tg64, st, sk);
+  e = wide ? launch_bwd_kernels<D, T, (D % 64 == 0)>(p, s, smem_q, smem_k, tv64, tv128, tg64, tqi, tki, st, sk)
+           : launch_bwd_kernels<D, T, false>(p, s, smem_q, smem_k, tv64, tv128, tg64, tqi, tki, st, sk);
   if (e != cudaSuccess) return e;
   return fk.join();
 }

@@ -99,6 +99,18 @@ bool make_wide_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int
                  batch, sn, sh, sb, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+// An operand image ([tile][chunk][64 rows x 16 B]) seen as (1 KB run, tile, chunk): a box of (1 KB, 2 tiles, all chunks)
+// lands in shared memory as [chunk][128 rows][16 B], i.e. a resident 128-row operand arrives by ONE copy.
+bool make_image_tmap(CUtensorMap* out, const void* img, int64_t ntiles, int chunks) {
+  TmapEncodeFn encode = tmap_encoder();
+  if (!encode || (reinterpret_cast<uintptr_t>(img) & 15) != 0 || chunks < 1 || chunks > 256 || ntiles < 2) return false;
+  cuuint64_t dims[4] = {128, (cuuint64_t)ntiles, (cuuint64_t)chunks, 1};                    // 128 x 8 bytes = one 1 KB run
+  cuuint64_t strides[3] = {(cuuint64_t)chunks * 1024, 1024, (cuuint64_t)ntiles * chunks * 1024};
+  cuuint32_t box[4] = {128, 2, (cuuint32_t)chunks, 1}, estr[4] = {1, 1, 1, 1};
+  return encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, 4, const_cast<void*>(img), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool make_load_tmap_f32(CUtensorMap* out, const void* base, int cols, int rows, int heads, int batch, int64_t sn, int64_t sh,
                         int64_t sb, int box_rows) {
   return tmap_4d(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, cols, rows, heads, batch, sn, sh, sb, 32, box_rows,

@@ -110,6 +110,8 @@ inline ExpandJob expand_job(const void* x, const PopeStride3& sx, int batch, int
 // 16-bit (feature, row, head, batch) view cut into boxes of 64 features (128-byte rows) x box_rows rows, 128-byte swizzled
 bool make_wide_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
                     int64_t sh, int64_t sb, int box_rows);
+// an operand image as (1 KB run, tile, chunk): box = (1 KB, 2 tiles, all chunks) = one resident 128-row operand
+bool make_image_tmap(CUtensorMap* out, const void* img, int64_t ntiles, int chunks);
 // ch / sh = fp16 cos / sin of the phase table, [positions][r].  All jobs share d and the dtype; one launch.
 cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const void* ch, const void* sh,
                                  cudaStream_t st);
