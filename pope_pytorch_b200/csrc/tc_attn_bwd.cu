@@ -322,74 +322,72 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     warp_arrive(&bars[BB_GRAD], lane);
   }
   // ---- epilogue: dq = (dQc cos + dQs sin) sigmoid(q), dphase = a (dQs cos - dQc sin) ---------------
-  // TMEM hands every thread one ROW of dQ', but q, the phase tables and dq are row-major in global memory: read by
-  // rows, a warp-wide 16-byte access touches 32 different lines.  So the accumulator is transposed through the (now
-  // dead) shared memory first, and the chain rule runs with consecutive threads on consecutive 8-feature groups of
-  // one row: every global access is a contiguous 256 or 512 bytes per warp.
+  // Everything the chain rule needs is in the resident Q' tile: with qc = a cos f, qs = a sin f (a = softplus(q)),
+  //   a = sqrt(qc^2 + qs^2),  sigmoid(q) = 1 - exp(-a),  dq = (dQc qc + dQs qs) / a * sigmoid(q),
+  //   dphase = a (dQs cos f - dQc sin f) = dQs qc - dQc qs,
+  // so the epilogue reads neither q nor the phase tables from global memory.  The 16-bit rounding of Q' costs cos f a
+  // relative 2^-8 sin^2 f at most.  A thread works on its own row (TMEM hands it that row, and the Q' tile is read
+  // conflict-free by rows); the dq rows then go through a row-major staging tile behind Q' (the dead stages) so that
+  // they leave in fully coalesced 16-byte pieces.  (Transposing the fp32 accumulator through shared memory first and
+  // running the chain rule on row-major groups took 8600 clocks of an 11 000-clock epilogue.)
   if (!failed) failed = !mbar_wait(&bars[BB_ACC + (T_tiles - 1) % DQ_NST], ((T_tiles - 1) / DQ_NST) & 1, WAIT_LIMIT);
   fence_after_sync();
+  asm volatile("bar.sync 1, 256;" ::: "memory");   // every MMA is done: the stages are dead
+  constexpr int OSTR = D * 2 + 16;                 // bytes of a staged output row (16 bytes of padding: conflict-free)
+  uint8_t* dq_stage = Ks;
   {
-    const int ASTR = KD * 4 + 16;            // bytes of one staged fp32 row (16 bytes of padding: conflict-free)
-    uint8_t* accs = Ks;                      // [128 rows][KD fp32]: 133 KB at KD = 256, over the (dead) stages; Q' stays
-    constexpr int HW = D / 2;                // columns of each part copied by this thread: [half*HW, half*HW + HW)
+    constexpr int HW = D / 2;
     const uint32_t acc = tmem + lane_base + TC_DQ;
+    float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + h * p.sdf.h + (int64_t)(qoff + gi) * p.sdf.n : nullptr;
+    const bool live = gi < p.Nq;
 #pragma unroll
     for (int c0 = 0; c0 < HW; c0 += 16) {
       const int cbase = half * HW + c0;
       uint32_t gc[16], gs[16];
+      const bool rotd = cbase < p.r;   // r is a multiple of 16: the 16-wide group is rotated as a whole
       tmem_ld16(acc + cbase, gc);
-      const bool rot = cbase < p.r;  // r is a multiple of 16: the 16-wide group is rotated as a whole
-      if (rot) tmem_ld16(acc + D + cbase, gs);
+      if (rotd) tmem_ld16(acc + D + cbase, gs);
       tmem_ld_wait();
-      uint4* dc = reinterpret_cast<uint4*>(accs + row * ASTR + cbase * 4);
+      uint32_t wq[8];
+      if (rotd) {
+        uint32_t cw[8], sw[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) dc[e] = make_uint4(gc[4 * e], gc[4 * e + 1], gc[4 * e + 2], gc[4 * e + 3]);
-      if (rot) {
-        uint4* dsn = reinterpret_cast<uint4*>(accs + row * ASTR + (D + cbase) * 4);
+        for (int i = 0; i < 2; ++i) {
+          const uint4 qcw = *reinterpret_cast<const uint4*>(Qs + (cbase / 8 + i) * (BQ * 16) + row * 16);
+          const uint4 qsw = *reinterpret_cast<const uint4*>(Qs + (D / 8 + cbase / 8 + i) * (BQ * 16) + row * 16);
+          cw[4 * i] = qcw.x, cw[4 * i + 1] = qcw.y, cw[4 * i + 2] = qcw.z, cw[4 * i + 3] = qcw.w;
+          sw[4 * i] = qsw.x, sw[4 * i + 1] = qsw.y, sw[4 * i + 2] = qsw.z, sw[4 * i + 3] = qsw.w;
+        }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dsn[e] = make_uint4(gs[4 * e], gs[4 * e + 1], gs[4 * e + 2], gs[4 * e + 3]);
-      }
-    }
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    constexpr int GPR = D / 8;               // 8-feature groups per row
-    T* dqbase = (T*)p.dq + b * p.sdq.b + h * p.sdq.h;
-    // Everything the chain rule needs is in the resident Q' tile: with qc = a cos f, qs = a sin f (a = softplus(q)),
-    //   a = sqrt(qc^2 + qs^2),  sigmoid(q) = 1 - exp(-a),  dq = (dQc qc + dQs qs) / a * sigmoid(q),
-    //   dphase = a (dQs cos f - dQc sin f) = dQs qc - dQc qs,
-    // so the epilogue reads neither q nor the phase tables from global memory (those loads took 11 K of its 15 K
-    // clocks).  The 16-bit rounding of Q' costs cos f a relative 2^-8 sin^2 f at most.
-    for (int idx = tid; idx < BQ * GPR; idx += 256) {
-      const int rr = idx / GPR, g = idx - rr * GPR, cb = g * 8, gr = i0 + rr;
-      if (gr >= p.Nq) continue;
-      const float4 a0 = *reinterpret_cast<const float4*>(accs + rr * ASTR + cb * 4);
-      const float4 a1 = *reinterpret_cast<const float4*>(accs + rr * ASTR + cb * 4 + 16);
-      const float gcv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-      uint32_t outw[4];
-      if (cb < p.r) {   // r is a multiple of 16: an 8-wide group is rotated as a whole
-        const float4 b0 = *reinterpret_cast<const float4*>(accs + rr * ASTR + (D + cb) * 4);
-        const float4 b1 = *reinterpret_cast<const float4*>(accs + rr * ASTR + (D + cb) * 4 + 16);
-        const float gsv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-        const uint4 qcw = *reinterpret_cast<const uint4*>(Qs + g * (BQ * 16) + rr * 16);
-        const uint4 qsw = *reinterpret_cast<const uint4*>(Qs + (D / 8 + g) * (BQ * 16) + rr * 16);
-        const uint32_t cw[4] = {qcw.x, qcw.y, qcw.z, qcw.w}, sw[4] = {qsw.x, qsw.y, qsw.z, qsw.w};
-        float* dfrow = p.dfreqs ? p.dfreqs + b * p.sdf.b + h * p.sdf.h + (int64_t)(qoff + gr) * p.sdf.n + cb : nullptr;
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
+        for (int e = 0; e < 16; e += 2) {
           const float2 qc = unpack2<T>(cw[e >> 1]), qs = unpack2<T>(sw[e >> 1]);
+          const float g0 = __uint_as_float(gc[e]), g1 = __uint_as_float(gc[e + 1]);
+          const float h0 = __uint_as_float(gs[e]), h1 = __uint_as_float(gs[e + 1]);
           const float m0 = qc.x * qc.x + qs.x * qs.x, m1 = qc.y * qc.y + qs.y * qs.y;   // a^2
           const float r0 = m0 > 0.f ? rsqrtf(m0) : 0.f, r1 = m1 > 0.f ? rsqrtf(m1) : 0.f;
           const float sg0 = 1.f - ex2_approx(-m0 * r0 * LOG2E), sg1 = 1.f - ex2_approx(-m1 * r1 * LOG2E);
-          if (dfrow) {
-            atomicAdd(dfrow + e, gsv[e] * qc.x - gcv[e] * qs.x);
-            atomicAdd(dfrow + e + 1, gsv[e + 1] * qc.y - gcv[e + 1] * qs.y);
+          if (dfrow && live) {
+            atomicAdd(dfrow + cbase + e, h0 * qc.x - g0 * qs.x);
+            atomicAdd(dfrow + cbase + e + 1, h1 * qc.y - g1 * qs.y);
           }
-          outw[e >> 1] = pack2<T>((gcv[e] * qc.x + gsv[e] * qs.x) * r0 * sg0, (gcv[e + 1] * qc.y + gsv[e + 1] * qs.y) * r1 * sg1);
+          wq[e >> 1] = pack2<T>((g0 * qc.x + h0 * qs.x) * r0 * sg0, (g1 * qc.y + h1 * qs.y) * r1 * sg1);
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < 8; e += 2) outw[e >> 1] = pack2<T>(gcv[e], gcv[e + 1]);
+        for (int e = 0; e < 16; e += 2) wq[e >> 1] = pack2<T>(__uint_as_float(gc[e]), __uint_as_float(gc[e + 1]));
       }
-      *reinterpret_cast<uint4*>(dqbase + (int64_t)gr * p.sdq.n + cb) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+      *reinterpret_cast<uint4*>(dq_stage + row * OSTR + cbase * 2) = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+      *reinterpret_cast<uint4*>(dq_stage + row * OSTR + cbase * 2 + 16) = make_uint4(wq[4], wq[5], wq[6], wq[7]);
+    }
+  }
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  {
+    constexpr int GPR = D / 8;   // 16-byte groups per row
+    T* dqbase = (T*)p.dq + b * p.sdq.b + h * p.sdq.h;
+    for (int idx = tid; idx < BQ * GPR; idx += 256) {
+      const int rr = idx / GPR, g = idx - rr * GPR;
+      if (i0 + rr < p.Nq)
+        *reinterpret_cast<uint4*>(dqbase + (int64_t)(i0 + rr) * p.sdq.n + g * 8) = *reinterpret_cast<const uint4*>(dq_stage + rr * OSTR + g * 16);
     }
   }
   if (failed) atomicOr(p.status, 1u);
