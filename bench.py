@@ -46,9 +46,9 @@ UNIT = "TFLOP/s"
 # captures summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); traffic is proportional to
 # the number of (batch, head) units, so a B=4 launch moves 4x these.  Constants, not live measurements.
 NCU_TRAFFIC_B1 = {
-    "fwd": {"expand_image_kernel": 18.9e6, "attn_fwd_tc_kernel": 74.8e6},
-    "bwd": {"bwd_rowstat_kernel": 33.8e6, "expand_image_kernel": 118.9e6, "attn_bwd_dq_tc_kernel": 108.8e6,
-            "attn_bwd_dkdv_tc_kernel": 117.0e6},
+    "fwd": {"expand_image_kernel": 18.9e6, "attn_fwd_tc_kernel": 71.2e6},
+    "bwd": {"bwd_rowstat_kernel": 33.8e6, "expand_image_kernel": 45.9e6, "attn_bwd_dq_tc_kernel": 106.1e6,
+            "attn_bwd_dkdv_tc_kernel": 113.9e6},
 }
 
 
