@@ -9,8 +9,8 @@
 // sweeps the keys 64 at a time; a key-side CTA keeps 128 key rows resident and sweeps the query rows of all grouped
 // query heads.  The CTAs of a head run in the same wave and sweep in opposite directions from their diagonal block, so
 // the second read of every block of G is served by L2 (DRAM traffic 1.2 x G instead of 2 x).  Per step
-//   loader warp   : two lanes, each streaming on its own: the 32 KB tile of G by tensor-map copies (boxes of 32 fp32
-//                   columns, 128-byte swizzled; rows and columns past the end arrive as zeros), and the matching 64-row
+//   loader warps  : two, one thread of each streaming on its own: the 32 KB tile of G by tensor-map copies (boxes of 32
+//                   fp32 columns, 128-byte swizzled; rows and columns past the end arrive as zeros), and the matching 64-row
 //                   tile of the OTHER operand's expanded image (hi | lo, built by the pre-pass in the forward kernel's
 //                   file with 64-row tiles) by one bulk copy
 //   8 worker warps: a thread per row pulls its 32 values out of the staging tile, splits each into two bf16 numbers
@@ -27,8 +27,8 @@
 
 namespace pope {
 
-constexpr int SBW_THREADS = 352;     // 8 worker warps, two MMA-issuing warps (even / odd steps), the loader warp
-constexpr int SBW_MMA_WARP = 8, SBW_LOAD_WARP = 9, SBW_MMA2_WARP = 10;
+constexpr int SBW_THREADS = 384;     // 8 worker warps, two MMA-issuing warps (even / odd steps), two loader warps
+constexpr int SBW_MMA_WARP = 8, SBW_LOAD_WARP = 9, SBW_MMA2_WARP = 10, SBW_IMG_WARP = 11;
 constexpr int SBW_STG = 32 * 1024;   // one staged G tile (fp32) and one converted G tile (hi | lo bf16)
 constexpr int SBW_GST = 3;           // staging buffers of G: two tiles in flight while one is converted
 constexpr int SBW_CS_HALF = 64 * 16; // chunk stride of a 64-row operand image tile
@@ -107,7 +107,7 @@ __device__ __forceinline__ void sim_bwd_side(const TcSimBwdP& p, const CUtensorM
   const uint32_t tmem = *tmem_slot;
   bool failed = false;
 
-  if (warp == SBW_LOAD_WARP) {
+  if (warp == SBW_LOAD_WARP || warp == SBW_IMG_WARP) {
     // =============================== copies =====================================================
     // Swept rows m0 .. m0 + 63 of step s.  The sweep starts at the CTA's own diagonal block and the two sides walk in
     // opposite directions: query block i reads key step (2 i + t) and key block j reads query step (2 j + 1 - t) at time
@@ -120,10 +120,12 @@ __device__ __forceinline__ void sim_bwd_side(const TcSimBwdP& p, const CUtensorM
       hq = KEY_SIDE ? g * p.Hk + hk : ho;   // query head of this G tile
       return st * 64;
     };
-    // Two lanes stream on their own: the G tiles (three staging buffers, freed as soon as the workers have read them)
-    // and the operand image tiles (two buffers, freed by the MMAs two steps later); one lane doing both would hold
-    // back the next G copy while it waits for an image buffer.
-    if (lane == 0) {
+    // Two threads stream on their own: the G tiles (three staging buffers, freed as soon as the workers have read them)
+    // and the operand image tiles (two buffers, freed by the MMAs two steps later); one thread doing both would hold
+    // back the next G copy while it waits for an image buffer.  They sit in DIFFERENT warps: as two lanes of one warp
+    // the one parked in its barrier wait kept the other from running (its copy went out ~900 clocks after the barrier
+    // it was waiting for had completed).
+    if (warp == SBW_LOAD_WARP && lane == 0) {
       int s = 0;
       for (; s < S; ++s) {
         int hq;
@@ -138,7 +140,7 @@ __device__ __forceinline__ void sim_bwd_side(const TcSimBwdP& p, const CUtensorM
       }
       // a wait gave up: let the copies in flight land before the CTA may leave
       if (failed) drain_copies(&bars[WB_GFULL], SBW_GST, s - SBW_GST, s);
-    } else if (lane == 1) {
+    } else if (warp == SBW_IMG_WARP && lane == 0) {
       int s = 0;
       for (; s < S; ++s) {
         int hq;
