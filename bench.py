@@ -329,7 +329,7 @@ def run_case(a):
     dev = torch.device("cuda")
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
     g = torch.Generator().manual_seed(0)
-    nq = 1 if a.case == "decode" else a.N
+    nq = 1 if a.case in ("decode", "decode_paged") else a.N
     q = torch.randn(a.B, a.H, nq, a.d, generator=g).to(dtype).to(dev)
     k, v = (torch.randn(a.B, a.H, a.N, a.d, generator=g).to(dtype).to(dev) for _ in range(2))
     do = torch.randn(a.B, a.H, nq, a.d, generator=g).to(dtype).to(dev)
@@ -337,7 +337,13 @@ def run_case(a):
     freqs, bias = emb.freqs.contiguous(), emb.bias.detach().contiguous()
     scale = a.d ** -0.5
     causal = a.causal and a.case != "decode"
-    out = lse = dsim = None
+    out = lse = dsim = cache = None
+    if a.case == "decode_paged":
+        from pope_pytorch_b200 import PagedKVCache
+        pages = a.B * (a.N // 256 + 2)
+        cache = PagedKVCache(a.B, a.H, a.d, num_pages=pages, page_size=256, dtype=dtype, device=dev)
+        cache.alloc.free = torch.randperm(pages, generator=g).tolist()
+        cache.append(k, v)
     if a.case in ("fwd", "bwd", "step", "decode"):
         out, lse = _native.attn_forward(q, k, v, freqs, bias, None, causal, scale)
     if a.case == "sim_bwd":
@@ -352,6 +358,8 @@ def run_case(a):
         elif a.case == "step":
             out, lse = _native.attn_forward(q, k, v, freqs, bias, None, causal, scale)
             _native.attn_backward(do, q, k, v, out, lse, freqs, bias, None, causal, scale, False, True)
+        elif a.case == "decode_paged":
+            out = cache.decode(q, (freqs, bias), softmax_scale=scale)
         elif a.case == "sim":
             _native.sim_forward(q, k, freqs, bias)
         else:
@@ -453,6 +461,29 @@ def secondary_workloads(dev, pk, PoPE, AxialPoPE, _native):
         return dict(**med_best(ts), algorithmic_bytes=nbytes, algorithmic_gb_s=gbs, frac_of_hbm_peak=gbs / pk["hbm_gbs"],
                     path=_native.last_path(), l2="K + V = 4.3 GB per iteration, far beyond L2")
     guarded("decode_bf16_8x32x32768x128_r64", decode)
+
+    def decode_paged():
+        # the same decode over a paged cache: 8 sequences of 32768 keys in 256-key pages handed out in a scrambled order
+        from pope_pytorch_b200 import PagedKVCache
+        g = torch.Generator().manual_seed(1005)
+        cache = PagedKVCache(8, 32, 128, num_pages=8 * 129, page_size=256, max_seq_len=32768 + 256, dtype=torch.bfloat16, device=dev)
+        cache.alloc.free = torch.randperm(8 * 129, generator=g).tolist()
+        for c0 in range(0, 32768, 8192):
+            k, v = (torch.randn(8, 32, 8192, 128, device=dev).bfloat16() for _ in range(2))
+            cache.append(k, v)
+        k1, v1 = (torch.randn(8, 32, 1, 128, device=dev).bfloat16() for _ in range(2))
+        q = torch.randn(8, 32, 1, 128, device=dev).bfloat16()
+        emb = PoPE(64, heads=32).to(dev)(32768 + 64)
+        f, b = emb.freqs.contiguous(), emb.bias.detach().contiguous()
+        ts = event_times(lambda: cache.decode(q, (f, b)), 10)
+        nbytes = 2 * 8 * 32 * 32768 * 128 * 2
+        gbs = nbytes / statistics.median(ts) / 1e6
+        path = _native.last_path()
+        ta = event_times(lambda: cache.append(k1, v1), 10)     # ten single-token appends (the cache grows to 32778)
+        return dict(**med_best(ts), algorithmic_bytes=nbytes, algorithmic_gb_s=gbs, frac_of_hbm_peak=gbs / pk["hbm_gbs"], path=path,
+                    append_one_token_ms=statistics.median(ta), page_size=256, status=_native.device_status(),
+                    l2="K + V = 4.3 GB per iteration, far beyond L2")
+    guarded("decode_paged_bf16_8x32x32768x128_r64", decode_paged)
     return sec
 
 
@@ -496,7 +527,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads and the reference Triton leg")
-    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "step", "sim", "sim_bwd", "decode", "reference_triton"])
+    ap.add_argument("--case", default=None, choices=["fwd", "bwd", "step", "sim", "sim_bwd", "decode", "decode_paged", "reference_triton"])
     ap.add_argument("--B", type=int, default=1)
     ap.add_argument("--H", type=int, default=16)
     ap.add_argument("--N", type=int, default=4096)

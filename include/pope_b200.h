@@ -47,7 +47,7 @@
 extern "C" {
 #endif
 
-#define POPE_B200_ABI_VERSION 2
+#define POPE_B200_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define POPE_API __attribute__((visibility("default")))
@@ -69,7 +69,7 @@ typedef enum PopeStatus {
 typedef enum PopeDtype { POPE_F32 = 0, POPE_BF16 = 1, POPE_F16 = 2 } PopeDtype;
 
 typedef enum PopeOp {
-  POPE_OP_SIM_FWD = 0, POPE_OP_SIM_BWD = 1, POPE_OP_ATTN_FWD = 2, POPE_OP_ATTN_BWD = 3
+  POPE_OP_SIM_FWD = 0, POPE_OP_SIM_BWD = 1, POPE_OP_ATTN_FWD = 2, POPE_OP_ATTN_BWD = 3, POPE_OP_DECODE_PAGED = 4
 } PopeOp;
 
 /* Element strides of the batch, head and row axes (innermost axis is contiguous). */
@@ -220,6 +220,61 @@ typedef struct PopeApplyBwdArgs {
   float* dbias; int64_t dbias_stride_h;
 } PopeApplyBwdArgs;
 
+/* ---- decode over a paged key / value cache ------------------------------------------------------
+ * (No counterpart in the reference, which recomputes attention over full K and V every step; this is
+ * the step either side of the decode path in a serving loop: append the new token's k and v to a cache,
+ * then attend the new query over everything cached.)
+ *
+ * Layout.  Keys and values live in fixed-size pages, k_pages / v_pages = [num_pages][Hk][page_size][d]
+ * contiguous, dtype of q (bf16 or fp16); page_size is a multiple of 64.  page_table[b * max_pages_per_seq + i]
+ * is the physical page that holds keys [i * page_size, (i + 1) * page_size) of sequence b; seq_lens[b] is
+ * the number of keys sequence b holds.  Key j of a sequence sits at position j (row j of freqs); raw k is
+ * cached, the transform is applied as the keys stream through shared memory, so a cache entry never
+ * depends on the phase bias.  Which physical page a sequence gets next is the caller's policy: the
+ * library only reads the table.  A page index outside [0, num_pages) is never dereferenced: it is
+ * clamped, bit 1 of the device status word (pope_b200_device_status) is set and the results of that call
+ * are invalid. */
+typedef struct PopePagedKV {
+  void* k_pages;
+  void* v_pages;
+  const int32_t* page_table;   /* (B, max_pages_per_seq), device */
+  int32_t* seq_lens;           /* (B), device; read by decode, read and advanced by append */
+  int32_t num_pages, page_size, max_pages_per_seq, reserved0;
+} PopePagedKV;
+
+/* Append n_new rows per sequence: k, v (B, Hk, n_new, d) with element strides, written at positions
+ * [seq_lens[b], seq_lens[b] + n_new) of sequence b; the table must already map those positions.  With
+ * `advance` nonzero seq_lens[b] += n_new afterwards (a second tiny launch on the same stream). */
+typedef struct PopeKvAppendArgs {
+  uint32_t struct_bytes;
+  int32_t dtype;               /* PopeDtype: POPE_BF16 or POPE_F16 */
+  int32_t B, Hk, d, n_new;
+  int32_t advance, reserved0;
+  PopePagedKV kv;
+  const void* k; PopeStride3 sk;
+  const void* v; PopeStride3 sv;
+} PopeKvAppendArgs;
+
+/* One query row per (batch, head) against the cached keys of its sequence: out = softmax(q' K'^T scale) V
+ * with the query at the LAST cached position, seq_lens[b] - 1 (PoPE_pytorch/pope.py:64 and
+ * triton_pope_flash_attn.py:54-55: positions are bottom-right aligned), no causal mask needed.
+ * shape.Nq = 1; shape.Nk = an upper bound of every seq_lens[b] (it sizes the key split and the phase
+ * table; freqs must have at least that many rows and no batch / head axes).  A sequence without keys
+ * gives out = 0, lse = -inf.  lse (B, H) fp32 may be NULL.  Workspace: pope_b200_workspace_bytes(
+ * POPE_OP_DECODE_PAGED, &args).  Kernel: the streaming decode kernel (copy-engine ring of 64-key tiles,
+ * key ranges split over CTAs, split combine), tile addresses taken from the page table. */
+typedef struct PopePagedDecodeArgs {
+  uint32_t struct_bytes;
+  float softmax_scale;
+  PopeShape shape;
+  PopeEmbed embed;
+  PopePagedKV kv;
+  const void* q; PopeStride3 sq;   /* (B, H, 1, d): batch and head strides are used */
+  void* out;     PopeStride3 so;
+  float* lse;
+  void* workspace; size_t workspace_bytes;
+} PopePagedDecodeArgs;
+
 POPE_API int pope_b200_abi_version(void);
 POPE_API const char* pope_b200_status_str(int status);
 
@@ -228,8 +283,9 @@ POPE_API const char* pope_b200_status_str(int status);
 POPE_API const char* pope_b200_last_path(void);
 
 /* Sticky device-side status of the tensor-core kernels on the current device: 0 = healthy,
- * bit 0 = a bounded wait inside a kernel gave up (its results are then invalid).  Diagnostic:
- * this call synchronises the device. */
+ * bit 0 = a bounded wait inside a kernel gave up (its results are then invalid), bit 1 = a paged-cache call
+ * met a page index or a position outside the cache (clamped / skipped; its results are invalid).
+ * Diagnostic: this call synchronises the device. */
 POPE_API int pope_b200_device_status(void);
 
 /* Reset that word to 0 on the current device (synchronises the device).  POPE_OK or POPE_ERR_CUDA. */
@@ -252,6 +308,8 @@ POPE_API int pope_b200_attn_fwd(const PopeAttnArgs* args, void* stream);
 POPE_API int pope_b200_attn_bwd(const PopeAttnBwdArgs* args, void* stream);
 POPE_API int pope_b200_apply_qk_fwd(const PopeApplyArgs* args, void* stream);
 POPE_API int pope_b200_apply_qk_bwd(const PopeApplyBwdArgs* args, void* stream);
+POPE_API int pope_b200_kv_append(const PopeKvAppendArgs* args, void* stream);
+POPE_API int pope_b200_attn_decode_paged(const PopePagedDecodeArgs* args, void* stream);
 
 /* ---- attention forward for callers that cannot allocate -----------------------------------------
  * (No counterpart in the reference: its wrappers always allocate through torch.)

@@ -3,6 +3,7 @@
 from .pope import FactoredPolarEmbed, PoPE, PolarEmbedReturn, apply_pope_to_qk
 from .pope_nd import AxialPoPE
 from .attention import compute_attn_similarity, compute_attn_similarity_non_fused, flash_attn_with_pope
+from .kv_cache import PagedKVCache
 
 __all__ = ["PoPE", "AxialPoPE", "PolarEmbedReturn", "FactoredPolarEmbed", "apply_pope_to_qk", "compute_attn_similarity",
-           "compute_attn_similarity_non_fused", "flash_attn_with_pope"]
+           "compute_attn_similarity_non_fused", "flash_attn_with_pope", "PagedKVCache"]

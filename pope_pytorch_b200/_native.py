@@ -19,7 +19,7 @@ import torch
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG_DIR, "libpope_b200.so")
 
-OP_SIM_FWD, OP_SIM_BWD, OP_ATTN_FWD, OP_ATTN_BWD = 0, 1, 2, 3
+OP_SIM_FWD, OP_SIM_BWD, OP_ATTN_FWD, OP_ATTN_BWD, OP_DECODE_PAGED = 0, 1, 2, 3, 4
 _DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 
 
@@ -73,7 +73,9 @@ class AttnBwdArgs(C.Structure):
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
-ABI_VERSION = 2
+ABI_VERSION = 3
+
+
 class ApplyArgs(C.Structure):
     _fields_ = [("struct_bytes", C.c_uint32), ("reserved0", C.c_int32), ("shape", Shape), ("embed", Embed),
                 ("q", C.c_void_p), ("sq", Stride3), ("k", C.c_void_p), ("sk", Stride3),
@@ -88,9 +90,26 @@ class ApplyBwdArgs(C.Structure):
                 ("dfreqs", C.c_void_p), ("sdf", Stride3), ("dbias", C.c_void_p), ("dbias_stride_h", C.c_int64)]
 
 
+class PagedKV(C.Structure):
+    _fields_ = [("k_pages", C.c_void_p), ("v_pages", C.c_void_p), ("page_table", C.c_void_p), ("seq_lens", C.c_void_p),
+                ("num_pages", C.c_int32), ("page_size", C.c_int32), ("max_pages_per_seq", C.c_int32), ("reserved0", C.c_int32)]
+
+
+class KvAppendArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("dtype", C.c_int32), ("B", C.c_int32), ("Hk", C.c_int32), ("d", C.c_int32),
+                ("n_new", C.c_int32), ("advance", C.c_int32), ("reserved0", C.c_int32), ("kv", PagedKV),
+                ("k", C.c_void_p), ("sk", Stride3), ("v", C.c_void_p), ("sv", Stride3)]
+
+
+class PagedDecodeArgs(C.Structure):
+    _fields_ = [("struct_bytes", C.c_uint32), ("softmax_scale", C.c_float), ("shape", Shape), ("embed", Embed), ("kv", PagedKV),
+                ("q", C.c_void_p), ("sq", Stride3), ("out", C.c_void_p), ("so", Stride3), ("lse", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
 EXPORTS = ("pope_b200_abi_version", "pope_b200_apply_qk_fwd", "pope_b200_apply_qk_bwd", "pope_b200_status_str", "pope_b200_last_path", "pope_b200_device_status",
            "pope_b200_clear_device_status", "pope_b200_selftest_bounded_wait",
-           "pope_b200_workspace_bytes", "pope_b200_attn_fwd_noalloc",
+           "pope_b200_workspace_bytes", "pope_b200_attn_fwd_noalloc", "pope_b200_kv_append", "pope_b200_attn_decode_paged",
            "pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd")
 
 _lib = None
@@ -105,7 +124,7 @@ def _bind(lib):
     lib.pope_b200_workspace_bytes.restype = C.c_size_t
     lib.pope_b200_workspace_bytes.argtypes = [C.c_int, C.c_void_p]
     for name in ("pope_b200_sim_fwd", "pope_b200_sim_bwd", "pope_b200_attn_fwd", "pope_b200_attn_bwd",
-                 "pope_b200_apply_qk_fwd", "pope_b200_apply_qk_bwd"):
+                 "pope_b200_apply_qk_fwd", "pope_b200_apply_qk_bwd", "pope_b200_kv_append", "pope_b200_attn_decode_paged"):
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [C.c_void_p, C.c_void_p]

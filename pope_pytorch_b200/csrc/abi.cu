@@ -102,6 +102,11 @@ size_t pope_b200_workspace_bytes(int op, const void* args) {
       if (!force_simt() && pope::attn_bwd_tc_supported(a)) return pope::attn_bwd_tc_workspace(a);
       return pope::attn_bwd_simt_workspace(a);
     }
+    case POPE_OP_DECODE_PAGED: {
+      const PopePagedDecodeArgs& a = *static_cast<const PopePagedDecodeArgs*>(args);
+      if (a.struct_bytes != sizeof(PopePagedDecodeArgs) || check_shape(a.shape) != POPE_OK) return 0;
+      return pope::decode_paged_supported(a) ? pope::decode_paged_workspace(a) : 0;
+    }
     default: return 0;
   }
 }
@@ -206,6 +211,49 @@ int pope_b200_apply_qk_bwd(const PopeApplyBwdArgs* a, void* stream) {
   if ((rc = check_device()) != POPE_OK) return rc;
   if (pope::apply_qk_bwd(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
   g_last_path = "simt";
+  return POPE_OK;
+}
+
+static int check_paged(const PopePagedKV& kv, int B) {
+  if (!kv.k_pages || !kv.v_pages || !kv.page_table || !kv.seq_lens) return POPE_ERR_BAD_ARG;
+  if (kv.num_pages <= 0 || kv.page_size <= 0 || kv.max_pages_per_seq <= 0 || B <= 0) return POPE_ERR_BAD_ARG;
+  if (kv.page_size % 64 != 0) return POPE_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(kv.k_pages) & 15) != 0 || (reinterpret_cast<uintptr_t>(kv.v_pages) & 15) != 0) return POPE_ERR_MISALIGNED;
+  return POPE_OK;
+}
+
+int pope_b200_kv_append(const PopeKvAppendArgs* a, void* stream) {
+  if (!a || a->struct_bytes != sizeof(PopeKvAppendArgs)) return POPE_ERR_BAD_ARG;
+  if (a->B <= 0 || a->Hk <= 0 || a->d <= 0 || a->n_new < 0 || !a->k || !a->v) return POPE_ERR_BAD_ARG;
+  if (a->dtype != POPE_BF16 && a->dtype != POPE_F16) return POPE_ERR_UNSUPPORTED;
+  if (a->d % 8 != 0 || a->Hk > 65535 || a->B > 65535) return POPE_ERR_UNSUPPORTED;
+  int rc = check_paged(a->kv, a->B);
+  if (rc != POPE_OK) return rc;
+  auto rows16 = [](const void* ptr, const PopeStride3& st) {
+    return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && st.b % 8 == 0 && st.h % 8 == 0 && st.n % 8 == 0;
+  };
+  if (!rows16(a->k, a->sk) || !rows16(a->v, a->sv)) return POPE_ERR_MISALIGNED;
+  if (a->n_new == 0) return POPE_OK;
+  if ((rc = check_device()) != POPE_OK) return rc;
+  if (pope::kv_append(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = "kv_append";
+  return POPE_OK;
+}
+
+int pope_b200_attn_decode_paged(const PopePagedDecodeArgs* a, void* stream) {
+  if (!a || a->struct_bytes != sizeof(PopePagedDecodeArgs)) return POPE_ERR_BAD_ARG;
+  int rc = check_shape(a->shape);
+  if (rc == POPE_OK) rc = check_embed(a->shape, a->embed);
+  if (rc == POPE_OK) rc = check_paged(a->kv, a->shape.B);
+  if (rc != POPE_OK) return rc;
+  if (!a->q || !a->out) return POPE_ERR_BAD_ARG;
+  if (!pope::decode_paged_supported(*a)) return POPE_ERR_UNSUPPORTED;
+  const size_t need = pope::decode_paged_workspace(*a);
+  if (!a->workspace || a->workspace_bytes < need) return POPE_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return POPE_ERR_MISALIGNED;
+  if ((rc = check_device()) != POPE_OK) return rc;
+  if (pope::decode_paged(*a, static_cast<cudaStream_t>(stream)) != cudaSuccess) return POPE_ERR_CUDA;
+  g_last_path = "decode_stream_paged";
   return POPE_OK;
 }
 

@@ -16,6 +16,11 @@
 //
 // Semantics: PoPE_pytorch/triton_pope_flash_attn.py:52-57,73-80 (transform), :89-91 (mask, True = keep), :96-117
 // (softmax, empty rows); the query sits at the LAST table row (PoPE_pytorch/pope.py:64).
+//
+// Paged cache: the same kernel with K and V in fixed-size pages ([page][key head][page_size][d], page_size a multiple of
+// the 64-key tile, so a tile never straddles pages): the page indices of the CTA's key range are read into shared
+// memory once, the loader takes each tile's address from them, and every sequence has its own length (the query sits
+// at its last cached position).  kv_append_kernel writes new rows into the pages.
 #include <algorithm>
 
 #include "kernels.h"
@@ -37,6 +42,11 @@ struct DecodeStreamP {
   int64_t msb, msn;
   float *part_o, *part_ml;
   unsigned int* status;
+  // paged cache (page_table != nullptr): k / v point at the page pools, sk.h / sv.h = page_size * d, sk.n = sv.n = d
+  const int32_t* page_table;
+  const int32_t* seq_lens;
+  int page_size, max_pages, num_pages, npg_smem;
+  int64_t page_stride;       // elements per page
 };
 
 template <typename T> __device__ __forceinline__ void unpack8(const uint4& w, float (&x)[8]) {
@@ -71,13 +81,16 @@ __global__ void __launch_bounds__(32 * (NW + 1), MINB) attn_decode_stream_kernel
   float* red_ml = red_o + DS_WORKERS * D;                                           // [DS_WORKERS][2]
   uint64_t* full = reinterpret_cast<uint64_t*>(red_ml + 2 * DS_WORKERS);            // [nstages] tile landed
   uint64_t* empty = full + p.nstages;                                               // [nstages] all workers done with it
+  int* pages_s = reinterpret_cast<int*>(empty + p.nstages);                         // [npg_smem] pages of this CTA's key range
 
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int u = blockIdx.y, b = u / p.H, h = u % p.H, hk = h % p.Hk;
   const T* kbase = (const T*)p.k + b * p.sk.b + hk * p.sk.h;
   const T* vbase = (const T*)p.v + b * p.sv.b + hk * p.sv.h;
-  const int kb = blockIdx.x * p.split_len, ke = min(p.Nk, kb + p.split_len);
-  const int T_tiles = (ke - kb + TILE - 1) / TILE;
+  // keys of this sequence (paged cache: its own length, at most the bound the split was planned for)
+  const int nk = p.seq_lens ? max(0, min(p.seq_lens[b], p.Nk)) : p.Nk;
+  const int kb = blockIdx.x * p.split_len, ke = min(nk, kb + p.split_len);
+  const int T_tiles = ke > kb ? (ke - kb + TILE - 1) / TILE : 0;
 
   if (tid == 0) {
     for (int s = 0; s < p.nstages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], DS_WORKERS);
@@ -90,11 +103,23 @@ __global__ void __launch_bounds__(32 * (NW + 1), MINB) attn_decode_stream_kernel
     float c = x, s = 0.f;
     if (tid < r) {
       float sn, cs;
-      sincosf(p.freqs[(int64_t)(p.Nk - 1) * p.sfn + tid] - p.bias[hk * p.bias_sh + tid], &sn, &cs);
+      sincosf(p.freqs[(int64_t)(max(nk, 1) - 1) * p.sfn + tid] - p.bias[hk * p.bias_sh + tid], &sn, &cs);
       const float a = softplus_f(x);
       c = a * cs, s = a * sn;
     }
     qcs[tid] = c, qcs[D + tid] = s;
+  }
+  if (p.page_table) {
+    // page indices of [kb, ke); an index outside the pool is never dereferenced (clamped, status bit 1)
+    for (int i = tid; i < p.npg_smem; i += blockDim.x) {
+      const int lp = kb / p.page_size + i;
+      int pg = 0;
+      if ((int64_t)lp * p.page_size < ke) {
+        pg = lp < p.max_pages ? p.page_table[(int64_t)b * p.max_pages + lp] : -1;   // a length past the table's reach
+        if (pg < 0 || pg >= p.num_pages) pg = 0, atomicOr(p.status, 2u);
+      }
+      pages_s[i] = pg;
+    }
   }
   __syncthreads();
   bool failed = false;
@@ -108,16 +133,21 @@ __global__ void __launch_bounds__(32 * (NW + 1), MINB) attn_decode_stream_kernel
       if (failed) { drain_copies(full, p.nstages, jt - p.nstages, jt); break; }
       if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)(2 * n * D * 2 + 2 * n * r * 2));
       __syncwarp();
+      const T *kt = kbase + (int64_t)key0 * p.sk.n, *vt = vbase + (int64_t)key0 * p.sv.n;
+      if (p.page_table) {   // the tile lies inside one page
+        const int64_t off = (int64_t)pages_s[key0 / p.page_size - kb / p.page_size] * p.page_stride + (int64_t)hk * p.sk.h +
+                            (int64_t)(key0 % p.page_size) * p.sk.n;
+        kt = (const T*)p.k + off, vt = (const T*)p.v + off;
+      }
       if (p.k_rows_contiguous) {
-        if (lane == 0) bulk_load(st, kbase + (int64_t)key0 * p.sk.n, n * D * 2, &full[s]);
+        if (lane == 0) bulk_load(st, kt, n * D * 2, &full[s]);
       } else {
-        for (int i = lane; i < n; i += 32) bulk_load(st + i * D * 2, kbase + (int64_t)(key0 + i) * p.sk.n, D * 2, &full[s]);
+        for (int i = lane; i < n; i += 32) bulk_load(st + i * D * 2, kt + (int64_t)i * p.sk.n, D * 2, &full[s]);
       }
       if (p.v_rows_contiguous) {
-        if (lane == 1) bulk_load(st + kbytes, vbase + (int64_t)key0 * p.sv.n, n * D * 2, &full[s]);
+        if (lane == 1) bulk_load(st + kbytes, vt, n * D * 2, &full[s]);
       } else {
-        for (int i = lane; i < n; i += 32)
-          bulk_load(st + kbytes + i * D * 2, vbase + (int64_t)(key0 + i) * p.sv.n, D * 2, &full[s]);
+        for (int i = lane; i < n; i += 32) bulk_load(st + kbytes + i * D * 2, vt + (int64_t)i * p.sv.n, D * 2, &full[s]);
       }
       if (r > 0) {
         if (lane == 2) bulk_load(st + 2 * kbytes, p.ch + (int64_t)key0 * r, n * r * 2, &full[s]);
@@ -299,7 +329,7 @@ size_t decode_stream_workspace(const PopeAttnArgs& a) {
 cudaError_t launch_split_combine(const PopeAttnArgs& a, int nsplit, float* part_o, float* part_ml, cudaStream_t st);
 
 template <typename T, int D, int LPK, int KPL, int NW, int MINB>
-static cudaError_t launch_decode_stream(const PopeAttnArgs& a, cudaStream_t st) {
+static cudaError_t launch_decode_stream(const PopeAttnArgs& a, cudaStream_t st, const PopePagedKV* kv) {
   constexpr int DS_WORKERS = NW, DS_THREADS = 32 * (NW + 1);
   const PopeShape& s = a.shape;
   DecodeStreamP p = {};
@@ -311,6 +341,12 @@ static cudaError_t launch_decode_stream(const PopeAttnArgs& a, cudaStream_t st) 
   p.k_rows_contiguous = a.sk.n == s.d, p.v_rows_contiguous = a.sv.n == s.d;
   p.freqs = a.embed.freqs, p.bias = a.embed.bias, p.sfn = a.embed.sf.n, p.bias_sh = a.embed.bias_stride_h;
   p.mask = a.mask, p.msb = a.mask_stride_b, p.msn = a.mask_stride_n;
+  if (kv) {
+    p.page_table = kv->page_table, p.seq_lens = kv->seq_lens;
+    p.page_size = kv->page_size, p.max_pages = kv->max_pages_per_seq, p.num_pages = kv->num_pages;
+    p.page_stride = (int64_t)s.Hk * kv->page_size * s.d;
+    p.npg_smem = p.split_len / kv->page_size + 2;
+  }
   const size_t slots = (size_t)s.B * s.H * p.nsplit;
   p.part_o = static_cast<float*>(a.workspace);
   p.part_ml = p.part_o + slots * p.HDP;
@@ -323,7 +359,7 @@ static cudaError_t launch_decode_stream(const PopeAttnArgs& a, cudaStream_t st) 
   if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, ch, sh, st)) != cudaSuccess) return e;
   constexpr int TILE = DS_WORKERS * KPL * 32 / LPK;
   const size_t stage = (size_t)TILE * (2 * D * 2 + 2 * s.r * 2);
-  const size_t fixed = (2 * D + DS_WORKERS * D + 2 * DS_WORKERS) * sizeof(float) + 2 * 8 * 8 + 64;
+  const size_t fixed = (2 * D + DS_WORKERS * D + 2 * DS_WORKERS) * sizeof(float) + 2 * 8 * 8 + 64 + (size_t)p.npg_smem * sizeof(int);
   // two CTAs per SM: the ring of each takes what half of the shared memory leaves, at most 3 stages
   // Measured on B200 (8 x 32 x 32768 x 128, r = 64): two keys per lane and two resident CTAs per SM reach 4.67 TB/s;
   // a deeper ring in one CTA per SM is slower (2.06 ms against 0.92 ms): the workers, not the copies, need the overlap.
@@ -340,16 +376,111 @@ static cudaError_t launch_decode_stream(const PopeAttnArgs& a, cudaStream_t st) 
 }
 
 template <typename T>
-static cudaError_t decode_stream_d(const PopeAttnArgs& a, cudaStream_t st) {
+static cudaError_t decode_stream_d(const PopeAttnArgs& a, cudaStream_t st, const PopePagedKV* kv) {
   switch (a.shape.d) {
-    case 64: return launch_decode_stream<T, 64, 8, 2, 8, 1>(a, st);
-    case 96: return launch_decode_stream<T, 96, 4, 1, 8, 1>(a, st);
-    default: return launch_decode_stream<T, 128, 8, 2, 8, 1>(a, st);
+    case 64: return launch_decode_stream<T, 64, 8, 2, 8, 1>(a, st, kv);
+    case 96: return launch_decode_stream<T, 96, 4, 1, 8, 1>(a, st, kv);
+    default: return launch_decode_stream<T, 128, 8, 2, 8, 1>(a, st, kv);
   }
 }
 
 cudaError_t decode_stream(const PopeAttnArgs& a, cudaStream_t st) {
-  return a.shape.dtype == POPE_BF16 ? decode_stream_d<__nv_bfloat16>(a, st) : decode_stream_d<__half>(a, st);
+  return a.shape.dtype == POPE_BF16 ? decode_stream_d<__nv_bfloat16>(a, st, nullptr) : decode_stream_d<__half>(a, st, nullptr);
+}
+
+// ---- paged cache ---------------------------------------------------------------------------------
+// The paged call as the contiguous call sees it: K / V = the page pools, head stride inside a page, rows contiguous.
+static PopeAttnArgs paged_as_attn(const PopePagedDecodeArgs& g, float* lse) {
+  PopeAttnArgs a = {};
+  a.struct_bytes = sizeof(PopeAttnArgs);
+  a.causal = 0, a.softmax_scale = g.softmax_scale;
+  a.shape = g.shape, a.embed = g.embed;
+  a.q = g.q, a.sq = g.sq, a.out = g.out, a.so = g.so, a.lse = lse;
+  a.k = g.kv.k_pages, a.v = g.kv.v_pages;
+  a.sk.b = 0, a.sk.h = (int64_t)g.kv.page_size * g.shape.d, a.sk.n = g.shape.d;
+  a.sv = a.sk;
+  a.workspace = g.workspace, a.workspace_bytes = g.workspace_bytes;
+  return a;
+}
+
+static size_t paged_lse_bytes(const PopeShape& s) { return ((size_t)s.B * s.H * sizeof(float) + 255) & ~(size_t)255; }
+
+bool decode_paged_supported(const PopePagedDecodeArgs& g) {
+  const PopeShape& s = g.shape;
+  if (s.Nq != 1 || (s.dtype != POPE_BF16 && s.dtype != POPE_F16)) return false;
+  if (s.d != 64 && s.d != 96 && s.d != 128) return false;
+  if (s.r % 8 != 0) return false;
+  if (s.r > 0 && (g.embed.sf.b != 0 || g.embed.sf.h != 0)) return false;
+  if (g.kv.page_size < 64 || g.kv.page_size % 64 != 0) return false;
+  return true;
+}
+
+size_t decode_paged_workspace(const PopePagedDecodeArgs& g) {
+  return decode_stream_workspace(paged_as_attn(g, nullptr)) + paged_lse_bytes(g.shape);
+}
+
+cudaError_t decode_paged(const PopePagedDecodeArgs& g, cudaStream_t st) {
+  // the row statistics of the split combine go to the caller's lse or, without one, to the end of the workspace
+  float* lse = g.lse;
+  if (!lse) lse = reinterpret_cast<float*>(static_cast<uint8_t*>(g.workspace) + decode_stream_workspace(paged_as_attn(g, nullptr)));
+  const PopeAttnArgs a = paged_as_attn(g, lse);
+  return g.shape.dtype == POPE_BF16 ? decode_stream_d<__nv_bfloat16>(a, st, &g.kv) : decode_stream_d<__half>(a, st, &g.kv);
+}
+
+struct KvAppendP {
+  int Hk, d, n_new, page_size, max_pages, num_pages;
+  int64_t page_stride;
+  const void *k, *v;
+  Strides sk, sv;
+  void *k_pages, *v_pages;
+  const int32_t* page_table;
+  int32_t* seq_lens;
+  unsigned int* status;
+};
+
+// One thread per 16 bytes of a new row of k and of v.  A position past the table or a page index outside the pool is
+// skipped and reported through status bit 1.
+template <typename T>
+__global__ void __launch_bounds__(256) kv_append_kernel(KvAppendP p) {
+  const int cpr = p.d >> 3;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= p.n_new * cpr) return;
+  const int i = idx / cpr, c = idx - i * cpr, hk = blockIdx.y, b = blockIdx.z;
+  const int pos = p.seq_lens[b] + i, lp = pos / p.page_size;
+  if (pos < 0 || lp >= p.max_pages) { atomicOr(p.status, 2u); return; }
+  const int pg = p.page_table[(int64_t)b * p.max_pages + lp];
+  if (pg < 0 || pg >= p.num_pages) { atomicOr(p.status, 2u); return; }
+  const int64_t dst = (int64_t)pg * p.page_stride + ((int64_t)hk * p.page_size + pos % p.page_size) * p.d + c * 8;
+  const T* krow = static_cast<const T*>(p.k) + b * p.sk.b + hk * p.sk.h + (int64_t)i * p.sk.n + c * 8;
+  const T* vrow = static_cast<const T*>(p.v) + b * p.sv.b + hk * p.sv.h + (int64_t)i * p.sv.n + c * 8;
+  *reinterpret_cast<uint4*>(static_cast<T*>(p.k_pages) + dst) = __ldg(reinterpret_cast<const uint4*>(krow));
+  *reinterpret_cast<uint4*>(static_cast<T*>(p.v_pages) + dst) = __ldg(reinterpret_cast<const uint4*>(vrow));
+}
+
+__global__ void kv_advance_kernel(int32_t* seq_lens, int B, int n_new) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) seq_lens[b] += n_new;
+}
+
+cudaError_t kv_append(const PopeKvAppendArgs& g, cudaStream_t st) {
+  KvAppendP p = {};
+  p.Hk = g.Hk, p.d = g.d, p.n_new = g.n_new;
+  p.page_size = g.kv.page_size, p.max_pages = g.kv.max_pages_per_seq, p.num_pages = g.kv.num_pages;
+  p.page_stride = (int64_t)g.Hk * g.kv.page_size * g.d;
+  p.k = g.k, p.v = g.v, p.sk = Strides(g.sk), p.sv = Strides(g.sv);
+  p.k_pages = g.kv.k_pages, p.v_pages = g.kv.v_pages, p.page_table = g.kv.page_table, p.seq_lens = g.kv.seq_lens;
+  p.status = tc_status_ptr();
+  if (!p.status) return cudaErrorInvalidSymbol;
+  const dim3 grid((unsigned)((g.n_new * (g.d / 8) + 255) / 256), (unsigned)g.Hk, (unsigned)g.B);
+  // (both 16-bit types move as raw 16-byte groups)
+  kv_append_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if (g.advance) {
+    kv_advance_kernel<<<(g.B + 255) / 256, 256, 0, st>>>(g.kv.seq_lens, g.B, g.n_new);
+    e = cudaGetLastError();
+  }
+  return e;
 }
 
 }  // namespace pope

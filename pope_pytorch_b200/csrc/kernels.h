@@ -25,6 +25,11 @@ cudaError_t apply_qk_bwd(const PopeApplyBwdArgs& a, cudaStream_t st);
 bool decode_stream_supported(const PopeAttnArgs& a);
 size_t decode_stream_workspace(const PopeAttnArgs& a);
 cudaError_t decode_stream(const PopeAttnArgs& a, cudaStream_t st);
+// the same kernel over a paged key / value cache, and the append into the pages
+bool decode_paged_supported(const PopePagedDecodeArgs& a);
+size_t decode_paged_workspace(const PopePagedDecodeArgs& a);
+cudaError_t decode_paged(const PopePagedDecodeArgs& a, cudaStream_t st);
+cudaError_t kv_append(const PopeKvAppendArgs& a, cudaStream_t st);
 bool sim_fwd_tc_supported(const PopeSimArgs& a);
 size_t sim_fwd_tc_workspace(const PopeSimArgs& a);
 cudaError_t sim_fwd_tc(const PopeSimArgs& a, cudaStream_t st);

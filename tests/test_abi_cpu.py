@@ -44,6 +44,9 @@ def test_struct_layout_matches_c(tmp_path):
         "PopeAttnBwdArgs": (N.AttnBwdArgs, ["dout", "lse", "mask_stride_n", "dq", "dv", "dfreqs", "dbias", "workspace"]),
         "PopeApplyArgs": (N.ApplyArgs, ["shape", "embed", "q", "k", "q_out", "sqo", "k_out", "sko"]),
         "PopeApplyBwdArgs": (N.ApplyBwdArgs, ["dq_out", "dk_out", "dq", "dk", "dfreqs", "dbias", "dbias_stride_h"]),
+        "PopePagedKV": (N.PagedKV, ["k_pages", "v_pages", "page_table", "seq_lens", "num_pages", "page_size", "max_pages_per_seq"]),
+        "PopeKvAppendArgs": (N.KvAppendArgs, ["dtype", "B", "n_new", "advance", "kv", "k", "sk", "v", "sv"]),
+        "PopePagedDecodeArgs": (N.PagedDecodeArgs, ["softmax_scale", "shape", "embed", "kv", "q", "out", "so", "lse", "workspace_bytes"]),
     }
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for cname, (_, fl) in fields.items():
@@ -87,6 +90,37 @@ def test_bad_arguments_are_rejected_without_a_device(lib):
     s.shape = N.Shape(1, 2, 2, 4, 4, 32, 16, 0)
     assert lib.pope_b200_sim_fwd(C.addressof(s), None) == bad            # r > 0 without freqs
     assert lib.pope_b200_sim_bwd(None, None) == bad and lib.pope_b200_attn_bwd(None, None) == bad
+
+
+def test_paged_cache_arguments_are_checked_without_a_device(lib):
+    bad, unsupported = -1, -2
+    assert lib.pope_b200_kv_append(None, None) == bad and lib.pope_b200_attn_decode_paged(None, None) == bad
+    k = N.KvAppendArgs()
+    k.struct_bytes = C.sizeof(N.KvAppendArgs)
+    k.dtype, k.B, k.Hk, k.d, k.n_new = 1, 2, 2, 64, 4
+    assert lib.pope_b200_kv_append(C.addressof(k), None) == bad            # null tensors
+    buf = (C.c_char * 4096)()
+    ptr = (C.addressof(buf) + 255) & ~255
+    k.k, k.v = ptr, ptr
+    k.sk = k.sv = N.Stride3(512, 256, 64)
+    assert lib.pope_b200_kv_append(C.addressof(k), None) == bad            # no cache
+    k.kv = N.PagedKV(ptr, ptr, ptr, ptr, 4, 100, 2, 0)
+    assert lib.pope_b200_kv_append(C.addressof(k), None) == unsupported    # page size not a multiple of 64
+    k.kv = N.PagedKV(ptr, ptr, ptr, ptr, 4, 128, 2, 0)
+    k.dtype = 0
+    assert lib.pope_b200_kv_append(C.addressof(k), None) == unsupported    # fp32 cache
+    k.dtype, k.sk = 1, N.Stride3(512, 256, 60)
+    assert lib.pope_b200_kv_append(C.addressof(k), None) == -3             # rows off 16-byte boundaries
+    d = N.PagedDecodeArgs()
+    d.struct_bytes = C.sizeof(N.PagedDecodeArgs)
+    d.shape = N.Shape(2, 4, 2, 1, 4096, 128, 0, 1)
+    d.kv = N.PagedKV(ptr, ptr, ptr, ptr, 64, 256, 16, 0)
+    assert lib.pope_b200_workspace_bytes(N.OP_DECODE_PAGED, C.addressof(d)) > 0
+    assert lib.pope_b200_attn_decode_paged(C.addressof(d), None) == bad    # no q / out
+    d.q, d.out = ptr, ptr
+    assert lib.pope_b200_attn_decode_paged(C.addressof(d), None) == -4     # no workspace
+    d.shape = N.Shape(2, 4, 2, 1, 4096, 80, 0, 1)
+    assert lib.pope_b200_attn_decode_paged(C.addressof(d), None) == unsupported
 
 
 def test_workspace_query_needs_no_device(lib):
