@@ -433,6 +433,43 @@ def secondary_workloads(dev, pk, PoPE, AxialPoPE, _native):
                     path=_native.last_path())
     guarded("config2_fwd_2x8x1024x64_r32_causal_padding", config2)
 
+    def config2_graph():
+        # the same shape, forward + backward as ONE isolated call (idle GPU, warm L2): eager launches against the replay
+        # of a CUDA graph that captured them (3 + 5 launches, the backward's side stream forked and joined inside)
+        g = torch.Generator().manual_seed(1002)
+        q, k, v, do = (torch.randn(2, 8, 1024, 64, generator=g).bfloat16().to(dev) for _ in range(4))
+        emb = PoPE(32, heads=8).to(dev)(1024)
+        f, b = emb.freqs.contiguous(), emb.bias.detach().contiguous()
+        lens = torch.randint(512, 1025, (2,), generator=g)
+        mask = (torch.arange(1024)[None, :] < lens[:, None]).to(dev)
+
+        def step():
+            out, lse = _native.attn_forward(q, k, v, f, b, mask, True, 0.125)
+            return _native.attn_backward(do, q, k, v, out, lse, f, b, mask, True, 0.125, False, True)
+
+        def isolated(fn, iters=30):
+            ts = []
+            for _ in range(iters):
+                torch.cuda.synchronize()
+                a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a_.record(); fn(); b_.record(); torch.cuda.synchronize()
+                ts.append(a_.elapsed_time(b_))
+            return ts
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        te, tg = isolated(step), isolated(graph.replay)
+        return dict(eager_ms=statistics.median(te), graph_replay_ms=statistics.median(tg), eager_ms_best=min(te),
+                    graph_replay_ms_best=min(tg), iters=30, status=_native.device_status(),
+                    note="one fwd+bwd call on an idle GPU: launch-bound eager, the captured graph removes the host launches")
+    guarded("config2_fwd_bwd_isolated_call_eager_vs_cuda_graph", config2_graph)
+
     def config4():
         g = torch.Generator().manual_seed(1004)
         q, k, v, do = (torch.randn(2, 8, 2048, 96, generator=g).bfloat16().to(dev) for _ in range(4))

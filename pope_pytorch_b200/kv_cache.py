@@ -137,7 +137,7 @@ class PagedKVCache:
         self._push_table(self.alloc.reserve(n_new))
         a = N.KvAppendArgs(C.sizeof(N.KvAppendArgs), N._DTYPES[self.dtype], self.batch, self.kv_heads, self.head_dim, n_new, 1, 0,
                            self._kv_struct(), k.data_ptr(), N._s3(k), v.data_ptr(), N._s3(v))
-        with torch.cuda.device(self.device):
+        with N._on_device(self.device):
             N._check(lib.pope_b200_kv_append(C.addressof(a), N._stream_ptr(k)), "pope_b200_kv_append")
         self.alloc.advance(n_new)
 
@@ -155,7 +155,7 @@ class PagedKVCache:
         self._push_table(self.alloc.reserve(n_new, rows=[b]))
         a = N.KvAppendArgs(C.sizeof(N.KvAppendArgs), N._DTYPES[self.dtype], 1, self.kv_heads, self.head_dim, n_new, 1, 0,
                            self._kv_struct(b), k.data_ptr(), N._s3(k), v.data_ptr(), N._s3(v))
-        with torch.cuda.device(self.device):
+        with N._on_device(self.device):
             N._check(lib.pope_b200_kv_append(C.addressof(a), N._stream_ptr(k)), "pope_b200_kv_append")
         self.alloc.advance(n_new, rows=[b])
 
@@ -182,7 +182,7 @@ class PagedKVCache:
         a = N.PagedDecodeArgs(C.sizeof(N.PagedDecodeArgs), float(scale), shape, N._embed_struct(freqs, bias, r), self._kv_struct(),
                               q.data_ptr(), N._s3(q), out.data_ptr(), N._s3(out), lse.data_ptr(), None, 0)
         ws = N._workspace(N.OP_DECODE_PAGED, a, self.device)
-        with torch.cuda.device(self.device):
+        with N._on_device(self.device):
             N._check(lib.pope_b200_attn_decode_paged(C.addressof(a), N._stream_ptr(q)), "pope_b200_attn_decode_paged")
         del ws
         return (out, lse) if return_lse else out
