@@ -68,7 +68,8 @@ static TmapEncodeFn tmap_encoder() {
 // (feature, row, head, batch) view of a strided tensor.  A size-1 axis may come with any stride: it gets a valid
 // dummy (multiple of 16 bytes, increasing); an axis with more entries must come with a usable stride.
 static bool tmap_4d(CUtensorMap* out, CUtensorMapDataType dt, int esz, const void* base, int cols, int rows, int heads,
-                    int batch, int64_t sn, int64_t sh, int64_t sb, int box_cols, int box_rows, CUtensorMapSwizzle swz) {
+                    int batch, int64_t sn, int64_t sh, int64_t sb, int box_cols, int box_rows, CUtensorMapSwizzle swz,
+                    CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_128B) {
   TmapEncodeFn encode = tmap_encoder();
   if (!encode) return false;
   cuuint64_t dims[4] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)batch};
@@ -82,8 +83,8 @@ static bool tmap_4d(CUtensorMap* out, CUtensorMapDataType dt, int esz, const voi
     if (strides[i] % 16 != 0) return false;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
   cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1}, estr[4] = {1, 1, 1, 1};
-  return encode(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
-                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, promo,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 bool make_chunk_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int rows, int heads, int batch, int64_t sn,
@@ -113,8 +114,10 @@ bool make_image_tmap(CUtensorMap* out, const void* img, int64_t ntiles, int chun
 
 bool make_load_tmap_f32(CUtensorMap* out, const void* base, int cols, int rows, int heads, int batch, int64_t sn, int64_t sh,
                         int64_t sb, int box_rows) {
+  // (a tile row is 2 or 4 neighbouring boxes of 128 bytes: 256-byte promotion fetches the neighbour along; -0.8 % on the
+  // similarity backward)
   return tmap_4d(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, base, cols, rows, heads, batch, sn, sh, sb, 32, box_rows,
-                 CU_TENSOR_MAP_SWIZZLE_128B);
+                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 }
 
 bool make_store_tmap(CUtensorMap* out, const void* base, int dtype, int cols, int rows, int heads, int batch, int64_t sn,
