@@ -136,3 +136,38 @@ def test_similarity_tc_matches_exact_family(n, d, r, dtype):
     assert path_tc == "tcgen05" and path_ex == "simt" and _native.device_status() == 0
     tol = 1e-4 if dtype == torch.float32 else 1e-2
     assert float((s_tc.float() - s_ex.float()).abs().max()) <= tol * float(s_ex.float().abs().max())
+
+
+@pytest.mark.parametrize("b,h,hk,nq,nk,d,r,causal,masked,dtype", [
+    (2, 8, 8, 1024, 1024, 64, 32, True, True, torch.bfloat16),
+    (2, 8, 2, 1024, 1024, 96, 96, False, False, torch.bfloat16),
+    (1, 4, 4, 777, 1500, 128, 64, True, True, torch.float16),
+])
+def test_tensor_core_step_is_bitwise_reproducible(b, h, hk, nq, nk, d, r, causal, masked, dtype):
+    """out, lse, dq, dk, dv carry no atomics and no order-dependent reduction: repeated calls agree to the bit (a race
+    between the roles of a kernel would show up here); the phase-bias gradient is summed by fp32 atomics and may differ
+    in the last bits."""
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(b, h, nq, d, generator=g).to(dtype).to(DEV)
+    k, v = (torch.randn(b, hk, nk, d, generator=g).to(dtype).to(DEV) for _ in range(2))
+    do = torch.randn(b, h, nq, d, generator=g).to(dtype).to(DEV)
+    f = PoPE(r, heads=hk).to(DEV)(nk).freqs.detach().contiguous()
+    bias = (-torch.rand(hk, r, generator=g) * 6).to(DEV)
+    mask = None
+    if masked:
+        mask = torch.rand(b, nk, generator=g) > 0.3
+        mask[:, 0] = True
+        mask = mask.to(DEV)
+    ref = None
+    for _ in range(8):
+        out, lse = _native.attn_forward(q, k, v, f, bias, mask, causal, d ** -0.5)
+        assert _native.last_path() == "tcgen05"
+        dq, dk, dv, _, db = _native.attn_backward(do, q, k, v, out, lse, f, bias, mask, causal, d ** -0.5, False, True)
+        cur = (out, lse, dq, dk, dv)
+        if ref is None:
+            ref, db_ref = [t.clone() for t in cur], db.clone()
+            continue
+        for name, a, c in zip(("out", "lse", "dq", "dk", "dv"), cur, ref):
+            assert torch.equal(a, c), name
+        assert float((db - db_ref).abs().max()) <= 1e-5 * float(db_ref.abs().max())
+    assert _native.device_status() == 0
