@@ -67,6 +67,14 @@ __device__ __forceinline__ void drain_copies(uint64_t* full, int nst, int first,
   for (int t = first < 0 ? 0 : first; t < end; ++t) mbar_wait(&full[t % nst], (uint32_t)(t / nst) & 1u, 1u << 12);
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched with launch_dependent() (tc_common.cuh) may start while the kernel before it on the stream still
+// runs: its CTAs do their setup and call pdl_wait() before they touch anything that kernel wrote -- the wait returns once
+// that whole grid has completed and its writes are visible (at once for a kernel launched the ordinary way).
+// pdl_trigger() in the earlier kernel lets the next one start as soon as every CTA of this one has called it or exited.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA: tiled bulk tensor load into this CTA's shared memory (no multicast) -------------------
 // `tmap` is the address of a CUtensorMap kernel parameter (__grid_constant__).  The innermost coordinate
 // times the element size must be a multiple of 16 bytes.  Rows outside the tensor arrive as zeros.

@@ -589,7 +589,7 @@ static cudaError_t launch_bwd_tc(const PopeAttnBwdArgs& a, cudaStream_t st) {
   jobs.job[1] = expand_job(a.q, a.sq, s.B, s.H, s.Nq, s.r, s.Nk - s.Nq, nullptr, 0, qimg, s.Nk, by_batch, tab_heads);
   jobs.job[2] = expand_job(a.v, a.sv, s.B, s.Hk, s.Nk, 0, 0, nullptr, 0, vimg);
   jobs.job[3] = expand_job(a.dout, a.sdo, s.B, s.H, s.Nq, 0, 0, nullptr, 0, gimg);
-  if ((e = launch_expand_images(jobs, wide ? 2 : 4, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+  if ((e = launch_expand_images(jobs, wide ? 2 : 4, s.d, bf16, tt.ch, tt.sh, st, s.r > 0)) != cudaSuccess) return e;
   TcBwdP p = {};
   p.H = s.H, p.Hk = s.Hk, p.Nq = s.Nq, p.Nk = s.Nk, p.r = s.r, p.causal = a.causal;
   p.scale = a.softmax_scale, p.scale_log2 = a.softmax_scale * LOG2E;

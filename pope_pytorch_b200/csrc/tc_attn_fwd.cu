@@ -223,6 +223,7 @@ __global__ void __launch_bounds__(FW_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, co
     // a 128-key stage is one 128-row image tile (the pre-pass interleaves pairs of its 64-row tiles): one bulk copy.
     // (Assembled from 2 x KD / 8 copies of 1 KB the stage took longer to arrive than the whole step should last.)
     if (lane == 0) {
+      pdl_wait();   // the image pre-pass has completed
       const uint8_t* kimg = p.kimg + (int64_t)(b * p.Hk + hk) * (int64_t)(image_tiles(p.Nk) / 2) * KBUF;
       int j = 0;
       for (; j < T_tiles; ++j) {
@@ -320,6 +321,7 @@ __global__ void __launch_bounds__(FW_THREADS, 1) attn_fwd_tc_kernel(TcFwdP p, co
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int row_bar = 1 + (warp & 3);   // named barrier of the FW_NPR warps that share 32 rows
     auto row_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(row_bar), "n"(32 * FW_NPR) : "memory"); };
+    pdl_wait();   // the phase tables read below come from the kernels before this one
     {
       // Q' = [a cos f | pass | a sin f] of this CTA's rows, expanded HERE from q and the fp16 phase tables and written
       // straight into tensor memory (lane = row, 4 columns per 8-feature chunk): the resident operand never exists in
@@ -570,10 +572,11 @@ static cudaError_t launch_fwd_tc(const PopeAttnArgs& a, cudaStream_t st) {
   jobs.job[0] = expand_job(a.k, a.sk, s.B, s.Hk, s.Nk, s.r, 0, a.embed.bias, a.embed.bias_stride_h, kimg, s.Nk, by_batch, tab_heads);
   jobs.job[0].tile128 = 1;
   if (s.r > 0 && (e = launch_trig_tables(a.embed, s.Nk, s.r, nullptr, nullptr, tt.ch, tt.sh, st, slices, tab_heads)) != cudaSuccess) return e;
-  if ((e = launch_expand_images(jobs, 1, s.d, bf16, tt.ch, tt.sh, st)) != cudaSuccess) return e;
+  // tables -> images -> attention: the second and third kernel start as programmatic dependents of the one before (each
+  // waits for it before its first read of that kernel's output); the first launch of the chain is an ordinary one
+  if ((e = launch_expand_images(jobs, 1, s.d, bf16, tt.ch, tt.sh, st, s.r > 0)) != cudaSuccess) return e;
   dim3 grid((s.Nq + TQ - 1) / TQ, s.B * s.H);
-  attn_fwd_tc_kernel<D, T><<<grid, FW_THREADS, smem, st>>>(p, tmap_v);
-  return cudaGetLastError();
+  return launch_dependent(attn_fwd_tc_kernel<D, T>, grid, dim3(FW_THREADS), smem, st, p, tmap_v);
 }
 
 template <typename T>

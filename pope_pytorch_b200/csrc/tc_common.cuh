@@ -7,6 +7,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <utility>
 
 #include <cuda.h>   // CUtensorMap (types only; the encoder is fetched through the runtime's driver entry point)
 
@@ -113,8 +114,24 @@ bool make_wide_tmap(CUtensorMap* out, const void* base, bool is_bf16, int d, int
 // an operand image as (1 KB run, tile, chunk): box = (1 KB, 2 tiles, all chunks) = one resident 128-row operand
 bool make_image_tmap(CUtensorMap* out, const void* img, int64_t ntiles, int chunks);
 // ch / sh = fp16 cos / sin of the phase table, [positions][r].  All jobs share d and the dtype; one launch.
+// `dependent`: launch it as a programmatic dependent of the kernel before it on the stream (only when that kernel is one
+// of this library's: the kernel waits for it before its first read)
 cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const void* ch, const void* sh,
-                                 cudaStream_t st);
+                                 cudaStream_t st, bool dependent = false);
+
+// Launch `kernel` so that its CTAs may start while the previous kernel on `st` still runs (programmatic stream
+// serialization); the kernel calls pdl_wait() before it reads what that kernel wrote.  Use it only behind a kernel of
+// this library that was itself ordered after everything earlier on the stream.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 // fp32 cos / sin of freqs[pos][c] into ctab / stab ([n][r] each); launch_trig_tables also writes fp16 copies (ch, sh).
 // Where a phase comes from: the caller's table, or (factored form) position x inverse frequency, one fp32 multiply.
 struct PhaseSrc {

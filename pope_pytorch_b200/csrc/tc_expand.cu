@@ -31,6 +31,8 @@ __global__ void __launch_bounds__(256, 3) expand_image_kernel(ExpandJobs jobs, c
                                                             const __half* __restrict__ stab) {
   // (ctab / stab are advanced to the unit's table slice below)
   extern __shared__ __align__(16) uint8_t stage[];
+  pdl_trigger();   // the attention kernel behind this one may set itself up
+  pdl_wait();      // the phase tables (the kernel before this one) are complete
   const ExpandJob& jb = jobs.job[blockIdx.z];
   const int tid = threadIdx.x, u = blockIdx.y;
   const int tiles = (int)image_tiles(jb.rows);   // a multiple of EXPAND_TPC
@@ -139,7 +141,7 @@ __global__ void __launch_bounds__(256, 3) expand_image_kernel(ExpandJobs jobs, c
 
 template <typename T>
 static cudaError_t launch_expand_t(const ExpandJobs& jobs, int njobs, int d, const __half* ctab, const __half* stab,
-                                   cudaStream_t st) {
+                                   cudaStream_t st, bool dependent) {
   int tiles = 0, units = 0, rmax = 0;
   for (int i = 0; i < njobs; ++i) {
     tiles = std::max(tiles, (int)image_tiles(jobs.job[i].rows));
@@ -148,6 +150,14 @@ static cudaError_t launch_expand_t(const ExpandJobs& jobs, int njobs, int d, con
   }
   const dim3 grid((unsigned)(tiles / EXPAND_TPC), (unsigned)units, (unsigned)njobs);
   const size_t smem = (size_t)((d + rmax) / 8) * CS64 + 2 * (size_t)rmax * sizeof(float);
+  if (dependent) {
+    switch (d) {
+      case 64: return launch_dependent(expand_image_kernel<T, 64>, grid, dim3(256), smem, st, jobs, ctab, stab);
+      case 96: return launch_dependent(expand_image_kernel<T, 96>, grid, dim3(256), smem, st, jobs, ctab, stab);
+      case 128: return launch_dependent(expand_image_kernel<T, 128>, grid, dim3(256), smem, st, jobs, ctab, stab);
+      default: return cudaErrorInvalidValue;
+    }
+  }
   switch (d) {
     case 64: expand_image_kernel<T, 64><<<grid, 256, smem, st>>>(jobs, ctab, stab); break;
     case 96: expand_image_kernel<T, 96><<<grid, 256, smem, st>>>(jobs, ctab, stab); break;
@@ -158,12 +168,12 @@ static cudaError_t launch_expand_t(const ExpandJobs& jobs, int njobs, int d, con
 }
 
 cudaError_t launch_expand_images(const ExpandJobs& jobs, int njobs, int d, bool is_bf16, const void* ch, const void* sh,
-                                 cudaStream_t st) {
+                                 cudaStream_t st, bool dependent) {
   if (njobs < 1 || njobs > 4) return cudaErrorInvalidValue;
   const __half* ctab = static_cast<const __half*>(ch);
   const __half* stab = static_cast<const __half*>(sh);
-  return is_bf16 ? launch_expand_t<__nv_bfloat16>(jobs, njobs, d, ctab, stab, st)
-                 : launch_expand_t<__half>(jobs, njobs, d, ctab, stab, st);
+  return is_bf16 ? launch_expand_t<__nv_bfloat16>(jobs, njobs, d, ctab, stab, st, dependent)
+                 : launch_expand_t<__half>(jobs, njobs, d, ctab, stab, st, dependent);
 }
 
 }  // namespace pope

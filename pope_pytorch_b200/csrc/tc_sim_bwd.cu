@@ -141,6 +141,7 @@ __device__ __forceinline__ void sim_bwd_side(const TcSimBwdP& p, const CUtensorM
       // a wait gave up: let the copies in flight land before the CTA may leave
       if (failed) drain_copies(&bars[WB_GFULL], SBW_GST, s - SBW_GST, s);
     } else if (warp == SBW_IMG_WARP && lane == 0) {
+      pdl_wait();   // the image pre-pass has completed (the G copies of the other loader do not depend on it)
       int s = 0;
       for (; s < S; ++s) {
         int hq;
@@ -419,8 +420,7 @@ cudaError_t sim_bwd_tc(const PopeSimBwdArgs& a, cudaStream_t st) {
   const unsigned grid = (unsigned)(s.B * s.Hk) * (unsigned)(groups * ((s.Nq + 127) / 128) + (s.Nk + 127) / 128);
   // (the host-side preparation is done: the two launches go out back to back)
   if ((e = sim_launch_prepass(s, a.embed, a.q, a.sq, a.k, a.sk, qimg, kimg, 64, st)) != cudaSuccess) return e;
-  sim_bwd_tc_kernel<float><<<grid, SBW_THREADS, smem, st>>>(p, tmap_q, tmap_k);
-  return cudaGetLastError();
+  return launch_dependent(sim_bwd_tc_kernel<float>, dim3(grid), dim3(SBW_THREADS), smem, st, p, tmap_q, tmap_k);
 }
 
 }  // namespace pope

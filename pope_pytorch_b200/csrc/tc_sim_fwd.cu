@@ -56,6 +56,7 @@ constexpr int SIM_THREADS = 320;
 // the operand-image pre-pass, whose result is rounded to 8 or 11 bits anyway.
 // grid.y = table slice (batch entry x head of a batched caller table)
 __global__ void pope_trig_table_f32_kernel(PhaseSrc src, int n, int r, float* ctab, float* stab, __half* ch, __half* sh) {
+  pdl_trigger();   // the kernel behind this one may set itself up; it waits for this grid before it reads the tables
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)n * r) return;
   const int pos = idx / r, c = idx % r, slice = blockIdx.y;
@@ -150,6 +151,7 @@ __global__ void __launch_bounds__(256) sim_prepass_kernel(const T* __restrict__ 
                                                           int Nk, int d, int r, int qtiles, int ktiles, int tile_rows,
                                                           uint8_t* __restrict__ qimg, uint8_t* __restrict__ kimg) {
   const int tid = threadIdx.x, u = blockIdx.y;
+  pdl_trigger();   // the similarity kernel behind this one may set itself up; it waits for this grid before it reads the images
   const int bpt = tile_rows / 32;   // blocks per tile
   const bool is_q = (int)blockIdx.x < bpt * qtiles;
   const int blk = is_q ? blockIdx.x : blockIdx.x - bpt * qtiles, tile = blk / bpt, quarter = blk % bpt;
@@ -262,6 +264,7 @@ __global__ void __launch_bounds__(SIM_THREADS, 1) sim_fwd_tc_kernel(TcSimP p, co
   if (warp == SIM_LOAD_WARP) {
     // =============================== copies: one K' tile per step ==============================
     if (lane == 0) {
+      pdl_wait();   // the image pre-pass has completed (this thread is the only reader of its output)
       int t = 0;
       for (; t < ntiles && !failed; ++t) {
         const int64_t g = g_begin + t, rbg = g / p.ktiles;
@@ -493,8 +496,8 @@ static cudaError_t launch_sim_tc(const PopeSimArgs& a, cudaStream_t st) {
   }
   const unsigned grid = (unsigned)std::min<int64_t>(sms, p.total_tiles);
   if ((e = sim_launch_prepass(s, a.embed, a.q, a.sq, a.k, a.sk, qimg, kimg, SIM_M, st)) != cudaSuccess) return e;
-  sim_fwd_tc_kernel<T, SPLIT, MT, NKB><<<grid, SIM_THREADS, smem, st>>>(p, tmap);
-  return cudaGetLastError();
+  // (launched as a programmatic dependent of the pre-pass: 25.6 -> 22.4 us at (1, 8, 1024, 64))
+  return launch_dependent(sim_fwd_tc_kernel<T, SPLIT, MT, NKB>, dim3(grid), dim3(SIM_THREADS), smem, st, p, tmap);
 }
 
 template <typename T, bool SPLIT>
