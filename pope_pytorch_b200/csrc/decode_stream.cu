@@ -126,6 +126,8 @@ __global__ void __launch_bounds__(32 * (NW + 1), MINB) attn_decode_stream_kernel
 
   if (w == DS_WORKERS) {
     // =============================== loader =====================================================
+    pdl_trigger();   // the split combine behind this kernel may set itself up
+    pdl_wait();      // the fp16 phase table (the kernel before this one) is complete
     for (int jt = 0; jt < T_tiles && !failed; ++jt) {
       const int s = jt % p.nstages, key0 = kb + jt * TILE, n = min(TILE, ke - key0);
       uint8_t* st = smem + (size_t)s * stage_bytes;
@@ -370,8 +372,15 @@ static cudaError_t launch_decode_stream(const PopeAttnArgs& a, cudaStream_t st, 
   p.nstages = nst;
   const size_t smem = nst * stage + fixed;
   if ((e = ensure_max_smem<attn_decode_stream_kernel<T, D, LPK, KPL, NW, MINB>>()) != cudaSuccess) return e;
-  attn_decode_stream_kernel<T, D, LPK, KPL, NW, MINB><<<dim3(p.nsplit, s.B * s.H), DS_THREADS, smem, st>>>(p);
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  // behind the table kernel the decode kernel starts as its programmatic dependent (its loader waits for the table);
+  // without rotated features it is the first launch of the call and an ordinary one
+  if (s.r > 0) {
+    e = launch_dependent(attn_decode_stream_kernel<T, D, LPK, KPL, NW, MINB>, dim3(p.nsplit, s.B * s.H), dim3(DS_THREADS), smem, st, p);
+  } else {
+    attn_decode_stream_kernel<T, D, LPK, KPL, NW, MINB><<<dim3(p.nsplit, s.B * s.H), DS_THREADS, smem, st>>>(p);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) return e;
   return launch_split_combine(a, p.nsplit, p.part_o, p.part_ml, st);
 }
 

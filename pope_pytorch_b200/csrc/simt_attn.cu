@@ -204,6 +204,9 @@ __global__ void __launch_bounds__(256) attn_fwd_simt_kernel(AttnP p) {
 // Merge the per-split partial results: one warp per (unit, row).
 template <typename T>
 __global__ void attn_fwd_combine_kernel(AttnP p, int HDP) {
+  // (behind the streaming decode kernel this one is launched as its programmatic dependent: wait for that grid before the
+  // partials are read; after an ordinary launch the wait returns at once)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t rowid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (rowid >= (int64_t)p.B * p.H * p.Nq) return;
@@ -561,12 +564,17 @@ cudaError_t launch_split_combine(const PopeAttnArgs& a, int nsplit, float* part_
   const int HDP = simt_dch(s.d) * 32;
   const int64_t rows = (int64_t)s.B * s.H * s.Nq;
   const unsigned blocks = (unsigned)((rows + 7) / 8);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks), cfg.blockDim = dim3(256), cfg.dynamicSmemBytes = 0, cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
   switch (s.dtype) {
-    case POPE_F32: attn_fwd_combine_kernel<float><<<blocks, 256, 0, st>>>(c, HDP); break;
-    case POPE_BF16: attn_fwd_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(c, HDP); break;
-    default: attn_fwd_combine_kernel<__half><<<blocks, 256, 0, st>>>(c, HDP); break;
+    case POPE_F32: return cudaLaunchKernelEx(&cfg, attn_fwd_combine_kernel<float>, c, HDP);
+    case POPE_BF16: return cudaLaunchKernelEx(&cfg, attn_fwd_combine_kernel<__nv_bfloat16>, c, HDP);
+    default: return cudaLaunchKernelEx(&cfg, attn_fwd_combine_kernel<__half>, c, HDP);
   }
-  return cudaGetLastError();
 }
 
 template <typename T>
