@@ -66,7 +66,8 @@ enum { BB_FULL = 0,      // [3] streamed tile j has landed in its stage (transac
        BB_ISSUED = 10,   // [2] the score products of tile j have been ISSUED (slot j & 1): what is issued after this
                          //     executes behind them in the tensor pipe
        BB_DPDONE = 12,   // tcgen05.commit: dP of the current tile is in TMEM (dq kernel: issued by the second warp)
-       BB_COUNT = 13 };
+       BB_CONS_DP = 13,  // 8 warps: dP copied to registers (dq kernel: BB_CONSUMED then covers S alone)
+       BB_COUNT = 14 };
 
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -108,6 +109,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     for (int i = 0; i < DQ_NST; ++i) mbar_init(&bars[BB_FULL + i], 1), mbar_init(&bars[BB_ACC + i], 1);
     mbar_init(&bars[BB_SCORES], 1);
     mbar_init(&bars[BB_CONSUMED], BWD_E_WARPS), mbar_init(&bars[BB_GRAD], BWD_E_WARPS);
+    mbar_init(&bars[BB_CONS_DP], BWD_E_WARPS);
     mbar_init(&bars[BB_RESIDENT], 1 + BWD_E_WARPS);
     mbar_init(&bars[BB_ISSUED], 1), mbar_init(&bars[BB_ISSUED + 1], 1);
     mbar_init(&bars[BB_DPDONE], 1);
@@ -202,7 +204,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
         if (j < T_tiles) {   // dP(j): dO from TMEM, the V tile from shared memory
           const int st = j % DQ_NST;
           failed = !mbar_wait(&bars[BB_FULL + st], (j / DQ_NST) & 1, WAIT_LIMIT);
-          if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONSUMED], (j - 1) & 1, WAIT_LIMIT);
+          if (j >= 1 && !failed) failed = !mbar_wait(&bars[BB_CONS_DP], (j - 1) & 1, WAIT_LIMIT);
           fence_after_sync();
           // B = V tile, K-major: image: chunk columns BCS apart; boxes: 64-feature blocks of 64 x 128 bytes, 32 bytes per step
           const uint64_t vd = VW ? smem_desc_sw128(vs_addr + st * VBUF, 16, 1024) : smem_desc(vs_addr + st * VBUF, BCS, 128);
@@ -286,16 +288,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_dq_tc_kernel(TcBwdP p
     }
     if (lse2 == -CUDART_INF_F) vis = 0u;
     const bool all_vis = __all_sync(0xffffffffu, vis == 0xffffffffu);   // interior tile: no masking work
+    // S first: the next S = Q' K'^T (16 instructions, the long product) starts as soon as these columns are free; dP
+    // (its own columns, its own barrier) follows
     if (!failed) failed = !mbar_wait(&bars[BB_SCORES], j & 1, WAIT_LIMIT);
-    if (!failed) failed = !mbar_wait(&bars[BB_DPDONE], j & 1, WAIT_LIMIT);
     fence_after_sync();
     uint32_t sv[32], dv[32];
     tmem_ld32(tmem + lane_base + TC_S + half * 32, sv);
-    tmem_ld32(tmem + lane_base + TC_DP + half * 32, dv);
     tmem_ld_wait();
-    // every score of this tile is in registers: the next score products may overwrite them
     fence_before_sync();
     warp_arrive(&bars[BB_CONSUMED], lane);
+    if (!failed) failed = !mbar_wait(&bars[BB_DPDONE], j & 1, WAIT_LIMIT);
+    fence_after_sync();
+    tmem_ld32(tmem + lane_base + TC_DP + half * 32, dv);
+    tmem_ld_wait();
+    fence_before_sync();
+    warp_arrive(&bars[BB_CONS_DP], lane);
     uint32_t pk[16];
     // two copies of the loop: interior tiles (the common case) carry no masking arithmetic at all
     auto elementwise = [&](auto masked) {
